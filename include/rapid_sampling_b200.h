@@ -1,0 +1,116 @@
+/*
+ * rapid_sampling_b200.h -- C ABI of the B200 (sm_100a) token sampler.
+ *
+ * Plain pointers and sizes only; every pointer named "device" must be device memory of the
+ * CUDA device that is current on the calling thread.  `stream` is a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).  All sampling calls are asynchronous on `stream`.
+ *
+ * Each entry point names the reference interface it replaces (paths are those of the
+ * reference project's files).
+ */
+#ifndef RAPID_SAMPLING_B200_H
+#define RAPID_SAMPLING_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes (0 = success).  The reference throws std::invalid_argument for the first four
+ * conditions (sampling.cu:452, :461, :467, :474 and :976, :986, :992, :999). */
+enum {
+    RS_OK = 0,
+    RS_ERR_DTYPE = -1,       /* reserved for the tensor shim: logits are not fp32               */
+    RS_ERR_VOCAB = -2,       /* V <= 0, V > 1048576 or V % 4 != 0                               */
+    RS_ERR_BATCH = -3,       /* B <= 0 or T <= 0                                                */
+    RS_ERR_TEMPERATURE = -4, /* temperature outside [0.001, 1000]                               */
+    RS_ERR_POINTER = -5,     /* NULL or misaligned pointer (rows and states need 16 B alignment) */
+    RS_ERR_WORKSPACE = -6,   /* workspace smaller than rs_workspace_bytes()                      */
+    RS_ERR_CUDA = -7,        /* a CUDA runtime call failed; see rs_last_cuda_error()             */
+    RS_ERR_TIMEOUT = -8,     /* device status: a bounded on-chip wait gave up                    */
+    RS_ERR_LIMIT = -9        /* size beyond what this entry point supports                       */
+};
+
+/* Bytes per row of the RNG state tensor: layout-compatible with curandStatePhilox4_32_10_t
+ * (the reference's RAND, sampling.cu:9): ctr[4] | cached block[4] | key[2] | pos | 5 zero words. */
+#define RS_STATE_BYTES 64
+
+/* Per-row values captured by rs_sample_debug(); all are the kernel's own fp32/u32 values. */
+typedef struct rs_trace {
+    float maxu, denom, pmin, pmax, threshold, comp, sgtp, sum_p, randp, sum_o, rand2;
+    uint32_t left, seqk, sgtk, rounds, idxt, early_exit, rnd[4];
+    int32_t token;
+} rs_trace;
+
+/*
+ * Replaces setup_rand(seed, B) (sampling.cpp:6, sampling.cu:136-144): fills B states so that
+ * row b is subsequence (first_row + b) of `seed`, offset 0.  The reference always uses
+ * first_row = 0; a batch shard passes its global row offset so that sharded and unsharded runs
+ * draw the same numbers.  states_device: B * RS_STATE_BYTES bytes, 16-byte aligned.
+ */
+int rs_setup_rand(void* states_device, uint64_t seed, int64_t B, int64_t first_row, void* stream);
+
+/* Device scratch a call with this shape may need (rows too large for on-chip storage fall back
+ * to a B*V fp32 scratch, the counterpart of the reference's `probs`, sampling.cu:488, :1014),
+ * plus a status word.  Never 0. */
+size_t rs_workspace_bytes(int64_t B, int64_t V);
+
+/*
+ * Replaces batch_sampling_temperature_topk_topp (sampling.cpp:8, sampling.cu:968-1044) when
+ * penalties_device == NULL, and batch_sampling_repetition_temperature_topk_topp
+ * (sampling.cpp:7, sampling.cu:440-515) otherwise.
+ *
+ * logits_device   fp32 (B, T, V) contiguous; only position T-1 of each row is read
+ *                 (sampling.cu:176, :202).  Pass T = 1 for (B, V) / (V,) input.
+ * penalties_device fp32 (B, V), updated in place with decay and the hit (sampling.cu:427-437), or NULL.
+ * states_device   B * RS_STATE_BYTES bytes; each row consumes one 4-word block (sampling.cu:383).
+ * out_device      int32[B] sampled ids (the reference returns an int32 tensor, sampling.cu:498, :1024).
+ * temperature, top_k, top_p  checked and remapped exactly as sampling.cu:474-486 / :999-1010.
+ * workspace_device / workspace_bytes  at least rs_workspace_bytes(B, V), 256-byte aligned.
+ */
+int rs_sample(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device,
+              void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
+              double presence_penalty, double repetition_penalty, double penalty_decay,
+              void* workspace_device, size_t workspace_bytes, void* stream);
+
+/* Same call, additionally writing the probabilities the cutoff search ran on (fp32 (B, V), may be
+ * NULL) and one rs_trace per row (may be NULL).  No reference counterpart: test instrumentation
+ * of the same kernels (the reference's equivalents are its commented-out printf macros,
+ * sampling.cu:146-147). */
+int rs_sample_debug(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                    void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
+                    double presence_penalty, double repetition_penalty, double penalty_decay,
+                    void* workspace_device, size_t workspace_bytes, void* stream,
+                    float* probs_device, rs_trace* trace_device);
+
+/*
+ * Host-buffer convenience around rs_sample for callers that hold logits in (pinned) host memory:
+ * copies logits[:, T-1, :] to `staging_device` (B*V floats), samples, copies the ids back to
+ * out_host and synchronises `stream`.  Penalties and states stay on the device.
+ */
+int rs_sample_host(const float* logits_host, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                   void* states_device, int32_t* out_host, double temperature, int64_t top_k, double top_p,
+                   double presence_penalty, double repetition_penalty, double penalty_decay,
+                   float* staging_device, int32_t* out_device, void* workspace_device, size_t workspace_bytes,
+                   void* stream);
+
+/* Reads the device status word of `workspace_device` (synchronises `stream`): RS_OK or RS_ERR_TIMEOUT. */
+int rs_device_status(void* workspace_device, void* stream);
+
+/* Forces the thread-block-cluster width (1, 2, 4, 8 or 16) used per row; 0 restores the automatic
+ * choice.  Benchmarking aid; returns the previous value. */
+int rs_set_cluster_override(int cluster_ctas);
+
+/* Number of sampler kernels launched through this library since it was loaded. */
+uint64_t rs_kernel_launch_count(void);
+
+const char* rs_status_string(int status);
+const char* rs_last_cuda_error(void);
+const char* rs_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RAPID_SAMPLING_B200_H */

@@ -1,0 +1,53 @@
+"""rapid_sampling_b200 -- B200 (sm_100a) drop-in for the reference sampler's torch extension.
+
+Exports the reference module's three functions (``sampling.cpp:5-9``) with the same names and
+positional order::
+
+    states = setup_rand(seed, B)
+    ids = batch_sampling_temperature_topk_topp(logits, states, temperature, top_k, top_p)
+    ids = batch_sampling_repetition_temperature_topk_topp(logits, penalties, states, presence_penalty,
+                                                          repetition_penalty, penalty_decay,
+                                                          temperature, top_k, top_p)
+
+The functions live in a compiled PyTorch extension built in-tree by ``rapid_sampling_b200._build``.
+There is no CPU or eager fallback: importing the functions without the built extension raises.
+"""
+import importlib
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_ext = None
+
+
+def _load_ext():
+    global _ext
+    if _ext is None:
+        import torch  # noqa: F401  libtorch must be loaded before the extension
+        try:
+            _ext = importlib.import_module("rapid_sampling_b200._rs_torch")
+        except ImportError as e:
+            raise ImportError("rapid_sampling_b200: the compiled extension is missing (%s). Build it with "
+                              "`python -m rapid_sampling_b200._build`; there is no CPU fallback." % e) from e
+    return _ext
+
+
+def setup_rand(seed, B):
+    return _load_ext().setup_rand(seed, B)
+
+
+def batch_sampling_temperature_topk_topp(logits, states, temperature, top_k, top_p):
+    return _load_ext().batch_sampling_temperature_topk_topp(logits, states, temperature, top_k, top_p)
+
+
+def batch_sampling_repetition_temperature_topk_topp(logits, penalties, states, presence_penalty, repetition_penalty,
+                                                    penalty_decay, temperature, top_k, top_p):
+    return _load_ext().batch_sampling_repetition_temperature_topk_topp(
+        logits, penalties, states, presence_penalty, repetition_penalty, penalty_decay, temperature, top_k, top_p)
+
+
+def kernel_launch_count():
+    return _load_ext().kernel_launch_count()
+
+
+__all__ = ["setup_rand", "batch_sampling_temperature_topk_topp", "batch_sampling_repetition_temperature_topk_topp",
+           "kernel_launch_count"]

@@ -1,0 +1,59 @@
+"""ctypes view of the C ABI declared in ``include/rapid_sampling_b200.h``.
+
+This is the boundary a non-Python host would bind; the parity tests call the kernels through it.
+Loading fails loudly when the CUDA library has not been built -- there is no CPU fallback.
+"""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "librapid_sampling_b200.so")
+
+RS_OK = 0
+RS_ERR_DTYPE, RS_ERR_VOCAB, RS_ERR_BATCH, RS_ERR_TEMPERATURE = -1, -2, -3, -4
+RS_ERR_POINTER, RS_ERR_WORKSPACE, RS_ERR_CUDA, RS_ERR_TIMEOUT, RS_ERR_LIMIT = -5, -6, -7, -8, -9
+RS_STATE_BYTES = 64
+
+SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host",
+           "rs_device_status", "rs_set_cluster_override", "rs_kernel_launch_count", "rs_status_string",
+           "rs_last_cuda_error", "rs_version"]
+
+
+class Trace(C.Structure):
+    _fields_ = [(n, C.c_float) for n in
+                ("maxu", "denom", "pmin", "pmax", "threshold", "comp", "sgtp", "sum_p", "randp", "sum_o", "rand2")] + \
+               [(n, C.c_uint32) for n in ("left", "seqk", "sgtk", "rounds", "idxt", "early_exit")] + \
+               [("rnd", C.c_uint32 * 4), ("token", C.c_int32)]
+
+
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError("%s is missing: build it with `python -m rapid_sampling_b200._build` "
+                          "(there is no CPU fallback)" % LIB_PATH)
+    L = C.CDLL(LIB_PATH)
+    vp, i64, dbl = C.c_void_p, C.c_int64, C.c_double
+    L.rs_setup_rand.argtypes = [vp, C.c_uint64, i64, i64, vp]
+    L.rs_workspace_bytes.argtypes = [i64, i64]
+    L.rs_workspace_bytes.restype = C.c_size_t
+    common = [vp, i64, i64, i64, vp, vp, vp, dbl, i64, dbl, dbl, dbl, dbl]
+    L.rs_sample.argtypes = common + [vp, C.c_size_t, vp]
+    L.rs_sample_debug.argtypes = common + [vp, C.c_size_t, vp, vp, vp]
+    L.rs_sample_host.argtypes = common + [vp, vp, vp, C.c_size_t, vp]
+    L.rs_device_status.argtypes = [vp, vp]
+    L.rs_set_cluster_override.argtypes = [C.c_int]
+    L.rs_kernel_launch_count.restype = C.c_uint64
+    for f in ("rs_status_string", "rs_last_cuda_error", "rs_version"):
+        getattr(L, f).restype = C.c_char_p
+    L.rs_status_string.argtypes = [C.c_int]
+    _lib = L
+    return L
+
+
+def status_string(rc):
+    return load().rs_status_string(rc).decode()

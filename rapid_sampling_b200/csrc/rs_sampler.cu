@@ -1,0 +1,782 @@
+// Token sampler for B200 (sm_100a): penalties/temperature -> softmax -> top-k/top-p cutoff ->
+// one sampled id per row, bit-compatible with the reference kernels (sampling.cu:172-438,
+// :517-752, :757-964) but organised differently:
+//
+//   * a row is handled by a thread-block CLUSTER of C CTAs (C = 1..16).  The reference's 1024
+//     threads become 1024 "virtual lanes"; CTA c plays lanes [c*1024/C, (c+1)*1024/C).  Lane t
+//     still owns float4 groups t, t+1024, ... so every fp32 sum keeps the reference's order.
+//   * the row is read from HBM ONCE, by 1-D bulk async copies (one per 16 KiB stripe) into the
+//     cluster's shared memory, and all later passes (exp, normalise, search rounds, recount)
+//     run on chip.  The reference re-reads a global scratch copy ~18 times from one SM.
+//   * search rounds drop, in place and order-preserving, every element below the current
+//     lower bound, so later rounds touch only the surviving candidates.
+//   * warp partials cross CTAs through small distributed-shared-memory mailboxes (remote
+//     stores + one cluster barrier per exchange); every CTA combines the 32 partials itself
+//     in the reference's order, so all CTAs take identical decisions without a broadcast.
+//   * rows too large for the cluster's shared memory use the same code on a global scratch row.
+//
+// No tensor cores: nothing here is a contraction.  The bound is HBM bandwidth (4 bytes per
+// logit, 12 with penalties) for large batches and launch + barrier latency for tiny ones.
+#include "rs_device.cuh"
+#include "../../include/rapid_sampling_b200.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <initializer_list>
+#include <mutex>
+
+namespace rs {
+
+enum Kind : int { kTopP = 0, kGeneral = 1, kRepetition = 2 };
+
+struct Params {
+    const float* logits;     // already offset to position T-1 of row 0
+    long long row_stride;    // elements between consecutive rows (T*V)
+    float* penalties;        // (B,V) or null
+    unsigned char* states;   // B*64
+    int* out;                // B
+    float* scratch;          // B*V floats (global-row variant only)
+    float* dbg_probs;        // optional (B,V)
+    rs_trace* dbg_trace;     // optional B
+    int* status;             // device status word
+    int B, V, kind, top_k;
+    float scale, top_p, presence, repetition, decay;
+};
+
+// shared-memory map (bytes)
+constexpr int kMboxOff = 0;        // 2 buffers x 32 entries x 32 B
+constexpr int kMboxBuf = 1024;
+constexpr int kMiscOff = 2048;     // mbarrier, small scalars, 32 warp totals
+constexpr int kSlabOff = 2560;
+constexpr uint32_t kWaitPolls = 1u << 22;
+
+__host__ __device__ constexpr int slab_bytes(int V, int C) { return ((V / 4 + 1023) / 1024) * (1024 / C) * 16; }
+
+template <int C, bool SMEM>
+struct Row {
+    static constexpr int L = kLanes / C;
+    float4* slab;
+    int t, tg;
+    __device__ __forceinline__ float4 ld(int s) const { return SMEM ? slab[s * L + t] : slab[s * kLanes + tg]; }
+    __device__ __forceinline__ void st(int s, float4 v) const {
+        if (SMEM) slab[s * L + t] = v; else slab[s * kLanes + tg] = v;
+    }
+};
+
+// Probability of one element, exactly as the streaming passes compute it.
+__device__ __forceinline__ float scaled_logit(float l, float pen, bool rep, float scale) {
+    return rep ? sanitize((sanitize(l) - pen) * scale) : sanitize(l * scale);
+}
+
+// One search pass over this lane's candidate list: counts and ordered masses at three pivots;
+// optionally keeps only elements >= keepf (in place, order preserved, tail padded with -1).
+template <int C, bool SMEM, bool COMPACT>
+__device__ __forceinline__ void search_pass(const Row<C, SMEM>& row, int& n, float py, float pz, float pw, float keepf,
+                                            uint32_t cnt[3], float mass[3]) {
+    uint32_t cy = 0, cz = 0, cw = 0;
+    float my = 0.f, mz = 0.f, mw = 0.f;
+    const int slots = (n + 3) >> 2;
+    float b0 = -1.f, b1 = -1.f, b2 = -1.f, b3 = -1.f;
+    int q = 0;
+#pragma unroll 2
+    for (int s = 0; s < slots; s++) {
+        const float4 v = row.ld(s);
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float p = e[j];
+            if (p >= py) { cy++; my += p; }
+            if (p >= pz) { cz++; mz += p; }
+            if (p >= pw) { cw++; mw += p; }
+            if (COMPACT) {
+                if (p >= keepf) {
+                    const int m = q & 3;
+                    b0 = (m == 0) ? p : b0;
+                    b1 = (m == 1) ? p : b1;
+                    b2 = (m == 2) ? p : b2;
+                    b3 = (m == 3) ? p : b3;
+                    q++;
+                    if ((q & 3) == 0) {
+                        row.st((q >> 2) - 1, make_float4(b0, b1, b2, b3));
+                        b0 = b1 = b2 = b3 = -1.f;
+                    }
+                }
+            }
+        }
+    }
+    if (COMPACT) {
+        if (q & 3) row.st(q >> 2, make_float4(b0, b1, b2, b3));
+        n = q;
+    }
+    cnt[0] = cy; cnt[1] = cz; cnt[2] = cw;
+    mass[0] = my; mass[1] = mz; mass[2] = mw;
+}
+
+template <int C, bool SMEM>
+__global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
+    constexpr int L = kLanes / C;
+    constexpr int WPC = L / 32;  // warps per CTA
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int t = threadIdx.x, lane = t & 31, wl = t >> 5;
+    const uint32_t crank = (C == 1) ? 0u : cluster_ctarank();
+    const int b = blockIdx.x / C;
+    const int tg = (int)crank * L + t;  // virtual lane
+    const int wg = tg >> 5;             // virtual warp
+    const int V = p.V, V4 = V >> 2;
+    const int Kt = (tg < V4) ? ((V4 - tg + kLanes - 1) >> 10) : 0;
+    const bool rep = (p.kind == kRepetition);
+    const bool use_cnt = (p.kind != kTopP);
+    const float* lrow = p.logits + (long long)b * p.row_stride;
+    float* prow = rep ? p.penalties + (long long)b * V : nullptr;
+
+    float4* mbox = reinterpret_cast<float4*>(smem + kMboxOff);
+    uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + kMiscOff);
+    int* s_idxt = reinterpret_cast<int*>(smem + kMiscOff + 8);
+    int* s_token = reinterpret_cast<int*>(smem + kMiscOff + 12);
+    float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
+    Row<C, SMEM> row;
+    row.slab = SMEM ? reinterpret_cast<float4*>(smem + kSlabOff) : reinterpret_cast<float4*>(p.scratch + (long long)b * V);
+    row.t = t;
+    row.tg = tg;
+
+    const uint32_t mbox_a = smem_addr(mbox);
+    int phase = 0;
+    // Posts this warp's 32-byte entry into every CTA's mailbox (values are warp-uniform).
+    auto post = [&](uint4 a, uint4 c2) {
+        if (C == 1) {
+            if (lane == 0) {
+                reinterpret_cast<uint4*>(mbox)[phase * 64 + wg * 2] = a;
+                reinterpret_cast<uint4*>(mbox)[phase * 64 + wg * 2 + 1] = c2;
+            }
+        } else if (lane < C) {
+            const uint32_t dst = map_to_cta(mbox_a + phase * kMboxBuf + wg * 32, (uint32_t)lane);
+            st_cluster_v4(dst, a);
+            st_cluster_v4(dst + 16, c2);
+        }
+    };
+    auto exchange_sync = [&]() {
+        if (C == 1) __syncthreads();
+        else { cluster_arrive(); cluster_wait(); }
+    };
+    const float4* mb;  // mailbox buffer to read after a sync
+
+    // ---- load: bulk async copies of this CTA's stripes; RNG state read meanwhile -------------
+    if (SMEM) {
+        if (t == 0) {
+            mbar_init(smem_addr(mbar), 1);
+            fence_mbar_init();
+            *s_idxt = 0;
+            *s_token = 0;
+        }
+        __syncthreads();
+        if (wl == 0) {
+            const int kfull = V4 >> 10, rem = V4 & 1023;
+            const int vl = min(max(rem - (int)crank * L, 0), L);
+            const uint32_t bar = smem_addr(mbar);
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)(kfull * L + vl) * 16u);
+            __syncwarp();
+            const float4* src = reinterpret_cast<const float4*>(lrow) + crank * L;
+            const uint32_t dst = smem_addr(row.slab);
+            for (int k = lane; k < kfull; k += 32) bulk_g2s(dst + k * L * 16, src + k * kLanes, L * 16, bar);
+            if (lane == 0 && vl > 0) bulk_g2s(dst + kfull * L * 16, src + kfull * kLanes, vl * 16, bar);
+        }
+    } else {
+        if (t == 0) { *s_idxt = 0; *s_token = 0; }
+        __syncthreads();
+    }
+    if (C > 1) cluster_arrive();  // peers must be running before their mailboxes are written
+
+    RngWords rng;
+    {
+        const uint4* st = reinterpret_cast<const uint4*>(p.states + (long long)b * RS_STATE_BYTES);
+        rng.ctr = st[0]; rng.block = st[1]; rng.key_pos = st[2];
+    }
+    uint32_t rnd4[4], r0, r1;
+    rng_peek2(rng, r0, r1, rnd4);
+    const float ux = u01(r0), uy = u01(r1);
+
+    if (SMEM) {
+        if (!mbar_wait_bounded(smem_addr(mbar), 0, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
+    }
+
+    // ---- pass 1: x = sanitised scaled logit, row max (sampling.cu:208-227, :547-559) ---------
+    float mx = -INFINITY;
+#pragma unroll 2
+    for (int s = 0; s < Kt; s++) {
+        float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
+        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rep) q4 = reinterpret_cast<const float4*>(prow)[s * kLanes + tg];
+        v.x = scaled_logit(v.x, q4.x, rep, p.scale);
+        v.y = scaled_logit(v.y, q4.y, rep, p.scale);
+        v.z = scaled_logit(v.z, q4.z, rep, p.scale);
+        v.w = scaled_logit(v.w, q4.w, rep, p.scale);
+        mx = fmaxf(fmaxf(fmaxf(mx, v.x), fmaxf(v.y, v.z)), v.w);
+        row.st(s, v);
+    }
+    mx = warp_max(mx);
+    if (C > 1) cluster_wait();
+    post(make_uint4(__float_as_uint(mx), 0, 0, 0), make_uint4(0, 0, 0, 0));
+    exchange_sync();
+    mb = mbox + phase * 64;
+    phase ^= 1;
+    mx = warp_max(mb[lane * 2].x);
+
+    // ---- pass 2: e = exp2f(x - max), ordered denominator (sampling.cu:560-572) ---------------
+    float acc = 0.f, emin = INFINITY, emax = -INFINITY;
+#pragma unroll 2
+    for (int s = 0; s < Kt; s++) {
+        float4 v = row.ld(s);
+        v.x = exp2f(v.x - mx);
+        v.y = exp2f(v.y - mx);
+        v.z = exp2f(v.z - mx);
+        v.w = exp2f(v.w - mx);
+        float em = 0.f;
+        em += v.x; em += v.y; em += v.z; em += v.w;
+        acc += em;
+        emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
+        emax = fmaxf(fmaxf(emax, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+        row.st(s, v);
+    }
+    acc = warp_tree_sum(acc);
+    emin = warp_min(emin);
+    emax = warp_max(emax);
+    post(make_uint4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), 0), make_uint4(0, 0, 0, 0));
+    exchange_sync();
+    mb = mbox + phase * 64;
+    phase ^= 1;
+    float denom;
+    {
+        const float4 e = mb[lane * 2];
+        denom = warp_tree_sum(e.x);  // tree over the 32 warp partials (sampling.cu:29-33)
+        emin = warp_min(e.y);
+        emax = warp_max(e.z);
+    }
+
+    // ---- pass 3: p = e / denom (sampling.cu:573-590); division is monotone, so the row's
+    // min/max probability are the quotients of the min/max numerators ---------------------------
+    const float pmin = emin / denom, pmax = emax / denom;
+    float* dprow = p.dbg_probs ? p.dbg_probs + (long long)b * V : nullptr;
+#pragma unroll 2
+    for (int s = 0; s < Kt; s++) {
+        float4 v = row.ld(s);
+        v.x = v.x / denom;
+        v.y = v.y / denom;
+        v.z = v.z / denom;
+        v.w = v.w / denom;
+        row.st(s, v);
+        if (dprow) reinterpret_cast<float4*>(dprow)[s * kLanes + tg] = v;
+    }
+
+    // ---- cutoff search (sampling.cu:593-654, :829-878) ---------------------------------------
+    uint32_t left = __float_as_uint(pmin), right = __float_as_uint(pmax) + 1u;
+    uint32_t cnt_x = (uint32_t)V;
+    float mass_x = 1.0f;
+    int n = Kt * 4;                      // live elements of this lane's list
+    uint32_t list_total = (uint32_t)V;   // live elements over the whole row
+    uint32_t list_left = left;           // the list holds exactly the elements >= list_left
+    uint32_t rounds = 0;
+    const uint32_t top_k = (uint32_t)p.top_k;
+    const float top_p = p.top_p;
+    while (rounds < 64u) {
+        const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
+        if (!(go && left < right - 1u)) break;
+        rounds++;
+        const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
+        uint32_t cnt[3];
+        float mass[3];
+        const bool compact = (left != list_left) && (cnt_x * 2u <= list_total);
+        if (compact) {
+            search_pass<C, SMEM, true>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw),
+                                       __uint_as_float(left), cnt, mass);
+            list_total = cnt_x;
+            list_left = left;
+        } else {
+            search_pass<C, SMEM, false>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw), 0.f, cnt,
+                                        mass);
+        }
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            cnt[i] = warp_sum_u32(cnt[i]);
+            mass[i] = warp_tree_sum(mass[i]);
+        }
+        post(make_uint4(cnt[0], cnt[1], cnt[2], 0),
+             make_uint4(__float_as_uint(mass[0]), __float_as_uint(mass[1]), __float_as_uint(mass[2]), 0));
+        exchange_sync();
+        mb = mbox + phase * 64;
+        phase ^= 1;
+        {
+            const uint4 c4 = reinterpret_cast<const uint4*>(mb)[lane * 2];
+            cnt[0] = warp_sum_u32(c4.x);
+            cnt[1] = warp_sum_u32(c4.y);
+            cnt[2] = warp_sum_u32(c4.z);
+            // thread 0 of the reference adds the 32 warp values in order (sampling.cu:34-42)
+            float4 m4 = mb[1];
+            float s0 = m4.x, s1 = m4.y, s2 = m4.z;
+#pragma unroll
+            for (int w = 1; w < kWarps; w++) {
+                m4 = mb[w * 2 + 1];
+                s0 += m4.x; s1 += m4.y; s2 += m4.z;
+            }
+            mass[0] = s0; mass[1] = s1; mass[2] = s2;
+        }
+        const bool ok0 = (use_cnt ? cnt[0] < top_k : true) && mass[0] < top_p;
+        const bool ok1 = (use_cnt ? cnt[1] < top_k : true) && mass[1] < top_p;
+        const bool ok2 = (use_cnt ? cnt[2] < top_k : true) && mass[2] < top_p;
+        if (ok0) { right = py; }
+        else if (ok1) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; }
+        else if (ok2) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; }
+        else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
+    }
+    const bool early_exit = left < right - 1u;
+    const float thr = __uint_as_float(left);
+
+    // ---- recount at the threshold (sampling.cu:657-680) --------------------------------------
+    float gtp = 0.f;
+    uint32_t eqk = 0, gtk = 0;
+    {
+        const int slots = (n + 3) >> 2;
+#pragma unroll 2
+        for (int s = 0; s < slots; s++) {
+            const float4 v = row.ld(s);
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (e[j] == thr) eqk++;
+                if (e[j] > thr) { gtk++; gtp += e[j]; }
+            }
+        }
+    }
+    // The reference takes the three totals from block scans; lane 31 of a descending-offset scan
+    // holds the same tree value as the butterfly, and the warp values are then added in order.
+    {
+        const float wsum = warp_tree_sum(gtp);
+        const uint32_t weq = warp_sum_u32(eqk), wgt = warp_sum_u32(gtk);
+        post(make_uint4(__float_as_uint(wsum), weq, wgt, 0), make_uint4(0, 0, 0, 0));
+    }
+    exchange_sync();
+    mb = mbox + phase * 64;
+    phase ^= 1;
+    float sgtp;
+    uint32_t seqk, sgtk;
+    {
+        const uint4 c4 = reinterpret_cast<const uint4*>(mb)[lane * 2];
+        seqk = warp_sum_u32(c4.y);
+        sgtk = warp_sum_u32(c4.z);
+        float s0 = mb[0].x;
+#pragma unroll
+        for (int w = 1; w < kWarps; w++) s0 += mb[w * 2].x;
+        sgtp = s0;
+    }
+
+    // ---- compensation factor for the boundary ties (sampling.cu:690-696, :903-908) -----------
+    float comp = 1.0f;
+    if (seqk > 0) {
+        comp = fminf(sanitize((top_p - sgtp) / (thr * seqk)), comp);
+        if (use_cnt) comp = fminf(sanitize(float(top_k - sgtk) / seqk), comp);
+        comp = fmaxf(comp, 0.0f);
+    }
+
+    // ---- lane pick (sampling.cu:699-723) -----------------------------------------------------
+    const float actual_p = gtp + (thr * eqk) * comp;
+    const float incl = warp_scan_desc(actual_p, lane);
+    {
+        const float wt = __shfl_sync(0xffffffffu, incl, 31);
+        post(make_uint4(__float_as_uint(wt), 0, 0, 0), make_uint4(0, 0, 0, 0));
+    }
+    exchange_sync();
+    mb = mbox + phase * 64;
+    phase ^= 1;
+    float pre_prev = 0.f, sum_p;   // prefix of the warps before mine; total
+    int own_w = -1;                // first warp whose inclusive prefix reaches randp
+    float randp;
+    {
+        // sequential prefix over the warp totals (sampling.cu:85-92)
+        float s0 = mb[0].x;
+        float pre[kWarps];
+        pre[0] = s0;
+#pragma unroll
+        for (int w = 1; w < kWarps; w++) { s0 += mb[w * 2].x; pre[w] = s0; }
+        sum_p = s0;
+        randp = sum_p * ux;
+#pragma unroll
+        for (int w = kWarps - 1; w >= 0; w--) {
+            if (randp <= pre[w]) own_w = w;
+            if (w == wg - 1) pre_prev = pre[w];
+        }
+    }
+    const float cumu_p = (wg > 0) ? incl + pre_prev : incl;
+    bool u = (randp <= cumu_p);
+    bool u_prev = __shfl_up_sync(0xffffffffu, u, 1);
+    if (lane == 0) u_prev = (wg > 0) ? (randp <= pre_prev) : false;
+    // Exactly one lane sees the 0 -> 1 transition (the scan is non-decreasing); with no
+    // transition at all the reference keeps its initial value, lane 0.
+    const int owner_cta = (own_w < 0) ? 0 : own_w / WPC;
+    const bool is_owner = ((int)crank == owner_cta);
+    if (u != u_prev) *s_idxt = tg;
+
+    if (crank == 0 && t == 0) {  // advance the stored RNG state by one 4-word block
+        const uint4 nctr = ctr_next(rng.ctr);
+        uint4* st = reinterpret_cast<uint4*>(p.states + (long long)b * RS_STATE_BYTES);
+        st[0] = nctr;
+        st[1] = philox4x32_10(nctr, rng.key_pos.x, rng.key_pos.y);
+    }
+
+    // ---- element pick inside the chosen lane (sampling.cu:725-751), owner CTA only -----------
+    int token = -1;
+    if (is_owner) {
+        __syncthreads();
+        const int idxt = *s_idxt;
+        float oincl[C];
+        int idn_of[C];
+#pragma unroll
+        for (int it = 0; it < C; it++) {
+            const int vt = it * L + t;  // thread index of the reference block
+            const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
+            float o0 = 0.f;
+            if (idn < V) {
+                const float x = scaled_logit(lrow[idn], rep ? prow[idn] : 0.f, rep, p.scale);
+                o0 = exp2f(x - mx) / denom;
+            }
+            const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
+            oincl[it] = warp_scan_desc(o, lane);
+            idn_of[it] = idn;
+            if (lane == 31) s_wtot[vt >> 5] = oincl[it];
+        }
+        __syncthreads();
+        float opre[C];
+        float s0 = 0.f;
+#pragma unroll
+        for (int it = 0; it < C; it++) opre[it] = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            s0 = (w == 0) ? s_wtot[0] : s0 + s_wtot[w];
+#pragma unroll
+            for (int it = 0; it < C; it++)
+                if (w == it * WPC + wl - 1) opre[it] = s0;
+        }
+        const float sum_o = s0;
+        const float rand2 = sum_o * uy;
+#pragma unroll
+        for (int it = 0; it < C; it++) {
+            const int vw = it * WPC + wl;
+            const float cumu_o = (vw > 0) ? oincl[it] + opre[it] : oincl[it];
+            const bool uo = (rand2 <= cumu_o);
+            bool uo_prev = __shfl_up_sync(0xffffffffu, uo, 1);
+            if (lane == 0) uo_prev = (vw > 0) ? (rand2 <= opre[it]) : false;
+            if (uo != uo_prev) *s_token = (idn_of[it] < V) ? idn_of[it] : 0;
+        }
+        __syncthreads();
+        token = *s_token;
+        if (t == 0) {
+            p.out[b] = token;
+            if (p.dbg_trace) {
+                rs_trace tr;
+                tr.maxu = mx; tr.denom = denom; tr.pmin = pmin; tr.pmax = pmax; tr.threshold = thr; tr.comp = comp;
+                tr.sgtp = sgtp; tr.sum_p = sum_p; tr.randp = randp; tr.sum_o = sum_o; tr.rand2 = rand2;
+                tr.left = left; tr.seqk = seqk; tr.sgtk = sgtk; tr.rounds = rounds; tr.idxt = (uint32_t)idxt;
+                tr.early_exit = early_exit ? 1u : 0u;
+                tr.rnd[0] = rnd4[0]; tr.rnd[1] = rnd4[1]; tr.rnd[2] = rnd4[2]; tr.rnd[3] = rnd4[3];
+                tr.token = token;
+                p.dbg_trace[b] = tr;
+            }
+        }
+    }
+
+    // ---- penalties: decay everything, add the hit on the sampled id (sampling.cu:427-437).
+    // The sampled id lies in the owner CTA's own stripes, so no cross-CTA hand-off is needed. ---
+    if (rep) {
+#pragma unroll 2
+        for (int s = 0; s < Kt; s++) {
+            const int i4 = s * kLanes + tg;
+            float4 q4 = reinterpret_cast<float4*>(prow)[i4];
+            float e[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float old = e[j];
+                e[j] = fmaf(old, p.decay, (i4 * 4 + j != token) ? 0.f : (old == 0.f ? p.presence : p.repetition));
+            }
+            reinterpret_cast<float4*>(prow)[i4] = make_float4(e[0], e[1], e[2], e[3]);
+        }
+    }
+}
+
+__global__ void setup_rand_kernel(unsigned char* states, unsigned long long seed, long long B, long long first_row) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= B) return;
+    const unsigned long long sub = (unsigned long long)(first_row + i);
+    const uint4 ctr = make_uint4(0u, 0u, (uint32_t)sub, (uint32_t)(sub >> 32));
+    const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    uint4* st = reinterpret_cast<uint4*>(states + i * RS_STATE_BYTES);
+    st[0] = ctr;
+    st[1] = philox4x32_10(ctr, k0, k1);
+    st[2] = make_uint4(k0, k1, 0u, 0u);
+    st[3] = make_uint4(0u, 0u, 0u, 0u);
+}
+
+// ------------------------------------------------------------------ host side -------------
+struct DeviceInfo {
+    bool ready = false;
+    int sms = 0, smem_optin = 0, smem_sm = 0;
+    bool attr_set[6][2] = {};
+};
+static DeviceInfo g_dev[64];
+static std::mutex g_mu;
+static std::atomic<uint64_t> g_launches{0};
+static std::atomic<int> g_cluster_override{0};
+static thread_local char g_err[256] = "";
+
+static int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_err, sizeof g_err, "%s: %s", what, cudaGetErrorString(e));
+    return RS_ERR_CUDA;
+}
+
+static int cidx(int C) { return C == 1 ? 0 : C == 2 ? 1 : C == 4 ? 2 : C == 8 ? 3 : 4; }
+
+template <int C, bool SMEM>
+static int launch_one(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
+    auto kern = sampler_kernel<C, SMEM>;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!di.attr_set[cidx(C)][SMEM ? 1 : 0]) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.smem_optin);
+            if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
+            if (C > 8) {
+                e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(cluster)");
+            }
+            di.attr_set[cidx(C)][SMEM ? 1 : 0] = true;
+        }
+    }
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((unsigned)(p.B * C), 1, 1);
+    cfg.blockDim = dim3(kLanes / C, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = C;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = (C > 1) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(sampler)");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RS_OK;
+}
+
+static int get_device(DeviceInfo** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (dev < 0 || dev >= 64) return RS_ERR_LIMIT;
+    DeviceInfo& di = g_dev[dev];
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!di.ready) {
+        if ((e = cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return cuda_fail(e, "attr");
+        if ((e = cudaDeviceGetAttribute(&di.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) return cuda_fail(e, "attr");
+        if ((e = cudaDeviceGetAttribute(&di.smem_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev)) != cudaSuccess) return cuda_fail(e, "attr");
+        di.ready = true;
+    }
+    *out = &di;
+    return RS_OK;
+}
+
+// Cluster width per row.  Small batches want the widest portable cluster (each of the 32
+// virtual warps gets a scheduler of its own at 8 CTAs); large batches want as many rows
+// resident as shared memory allows so that one row's load overlaps another row's search.
+static int choose_cluster(const DeviceInfo& di, long long B, int V, bool* use_smem) {
+    const int forced = g_cluster_override.load();
+    auto fits = [&](int C) { return kSlabOff + slab_bytes(V, C) <= di.smem_optin; };
+    *use_smem = true;
+    if (forced) {
+        if (fits(forced)) return forced;
+        *use_smem = false;
+        return 8;
+    }
+    auto resident_rows = [&](int C) {
+        const int need = kSlabOff + slab_bytes(V, C) + 1024;
+        int per_sm = di.smem_sm / need;
+        per_sm = per_sm < 2048 / (kLanes / C) ? per_sm : 2048 / (kLanes / C);
+        if (per_sm > 32) per_sm = 32;
+        return (long long)di.sms * per_sm / C;
+    };
+    if (fits(8) && B <= resident_rows(8)) return 8;
+    int best = 0;
+    long long best_rows = -1;
+    for (int C : {8, 4, 2, 1}) {
+        if (!fits(C)) continue;
+        const long long r = resident_rows(C);
+        if (r > best_rows) { best_rows = r; best = C; }
+    }
+    if (best) return best;
+    if (fits(16)) return 16;
+    *use_smem = false;
+    return 8;
+}
+
+static size_t ws_bytes(long long B, long long V) { return 256 + (size_t)B * (size_t)V * sizeof(float); }
+
+static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, float* penalties, void* states, int32_t* out,
+                       double temperature, int64_t top_k, double top_p, double presence, double repetition, double decay,
+                       void* workspace, size_t workspace_bytes, void* stream, float* dbg_probs, rs_trace* dbg_trace) {
+    // checks and remaps of the reference's host functions (sampling.cu:458-486, :982-1011)
+    if (!(V > 0 && V <= 1048576 && V % 4 == 0)) return RS_ERR_VOCAB;
+    if (!(B > 0 && T > 0)) return RS_ERR_BATCH;
+    if (!(temperature >= 0.001 && temperature <= 1000)) return RS_ERR_TEMPERATURE;
+    if (B > (1ll << 24)) return RS_ERR_LIMIT;
+    if (!logits || !states || !out || !workspace) return RS_ERR_POINTER;
+    if (((uintptr_t)logits & 15) || ((uintptr_t)states & 15) || ((uintptr_t)penalties & 15) || ((uintptr_t)workspace & 255))
+        return RS_ERR_POINTER;
+    if (top_k <= 0 || top_k > V) top_k = V;
+    if (top_p < 0 || top_p > 1) top_p = 1;
+    if (top_p == 0) { top_k = 1; top_p = 1; }
+    const double log2e_inv_temp = 1.4426950408889634074 / temperature;
+
+    DeviceInfo* di = nullptr;
+    int rc = get_device(&di);
+    if (rc) return rc;
+    bool use_smem = true;
+    const int C = choose_cluster(*di, B, (int)V, &use_smem);
+    if (workspace_bytes < (use_smem ? (size_t)256 : ws_bytes(B, V))) return RS_ERR_WORKSPACE;
+
+    Params p;
+    p.logits = logits + (T - 1) * V;
+    p.row_stride = (long long)T * V;
+    p.penalties = penalties;
+    p.states = (unsigned char*)states;
+    p.out = out;
+    p.status = (int*)workspace;
+    p.scratch = (float*)((char*)workspace + 256);
+    p.dbg_probs = dbg_probs;
+    p.dbg_trace = dbg_trace;
+    p.B = (int)B;
+    p.V = (int)V;
+    p.kind = penalties ? kRepetition : ((temperature == 1 && top_k == V) ? kTopP : kGeneral);
+    p.top_k = (int)top_k;
+    p.scale = (p.kind == kTopP) ? (float)1.4426950408889634074 : (float)log2e_inv_temp;
+    p.top_p = (float)top_p;
+    p.presence = (float)presence;
+    p.repetition = (float)repetition;
+    p.decay = (float)decay;
+
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!use_smem) return launch_one<8, false>(p, kSlabOff, st, *di);
+    const int smem = kSlabOff + slab_bytes((int)V, C);
+    switch (C) {
+        case 1: return launch_one<1, true>(p, smem, st, *di);
+        case 2: return launch_one<2, true>(p, smem, st, *di);
+        case 4: return launch_one<4, true>(p, smem, st, *di);
+        case 8: return launch_one<8, true>(p, smem, st, *di);
+        case 16: return launch_one<16, true>(p, smem, st, *di);
+    }
+    return RS_ERR_LIMIT;
+}
+
+}  // namespace rs
+
+// ------------------------------------------------------------------- C ABI -----------------
+extern "C" {
+
+int rs_setup_rand(void* states_device, uint64_t seed, int64_t B, int64_t first_row, void* stream) {
+    if (B <= 0) return RS_ERR_BATCH;
+    if (!states_device || ((uintptr_t)states_device & 15)) return RS_ERR_POINTER;
+    const int threads = 128;
+    const unsigned blocks = (unsigned)((B + threads - 1) / threads);
+    rs::setup_rand_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((unsigned char*)states_device, seed, B, first_row);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return rs::cuda_fail(e, "setup_rand launch");
+    rs::g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RS_OK;
+}
+
+size_t rs_workspace_bytes(int64_t B, int64_t V) {
+    if (B <= 0 || V <= 0) return 256;
+    // Only rows that exceed the widest cluster's shared memory need the global scratch row.
+    const bool may_fit = rs::kSlabOff + rs::slab_bytes((int)V, 16) <= 227 * 1024;
+    return may_fit ? 256 : rs::ws_bytes(B, V);
+}
+
+int rs_sample(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device, void* states_device,
+              int32_t* out_device, double temperature, int64_t top_k, double top_p, double presence_penalty,
+              double repetition_penalty, double penalty_decay, void* workspace_device, size_t workspace_bytes,
+              void* stream) {
+    return rs::sample_impl(logits_device, B, T, V, penalties_device, states_device, out_device, temperature, top_k, top_p,
+                           presence_penalty, repetition_penalty, penalty_decay, workspace_device, workspace_bytes, stream,
+                           nullptr, nullptr);
+}
+
+int rs_sample_debug(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                    void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
+                    double presence_penalty, double repetition_penalty, double penalty_decay, void* workspace_device,
+                    size_t workspace_bytes, void* stream, float* probs_device, rs_trace* trace_device) {
+    return rs::sample_impl(logits_device, B, T, V, penalties_device, states_device, out_device, temperature, top_k, top_p,
+                           presence_penalty, repetition_penalty, penalty_decay, workspace_device, workspace_bytes, stream,
+                           probs_device, trace_device);
+}
+
+int rs_sample_host(const float* logits_host, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                   void* states_device, int32_t* out_host, double temperature, int64_t top_k, double top_p,
+                   double presence_penalty, double repetition_penalty, double penalty_decay, float* staging_device,
+                   int32_t* out_device, void* workspace_device, size_t workspace_bytes, void* stream) {
+    if (!logits_host || !out_host || !staging_device || !out_device) return RS_ERR_POINTER;
+    if (!(V > 0 && V <= 1048576 && V % 4 == 0)) return RS_ERR_VOCAB;
+    if (!(B > 0 && T > 0)) return RS_ERR_BATCH;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (T == 1) {
+        e = cudaMemcpyAsync(staging_device, logits_host, (size_t)B * V * sizeof(float), cudaMemcpyHostToDevice, st);
+    } else {  // only the last position of every row crosses the bus
+        e = cudaMemcpy2DAsync(staging_device, (size_t)V * sizeof(float), logits_host + (T - 1) * V,
+                              (size_t)T * V * sizeof(float), (size_t)V * sizeof(float), (size_t)B, cudaMemcpyHostToDevice, st);
+    }
+    if (e != cudaSuccess) return rs::cuda_fail(e, "logits H2D");
+    int rc = rs::sample_impl(staging_device, B, 1, V, penalties_device, states_device, out_device, temperature, top_k,
+                             top_p, presence_penalty, repetition_penalty, penalty_decay, workspace_device,
+                             workspace_bytes, stream, nullptr, nullptr);
+    if (rc) return rc;
+    e = cudaMemcpyAsync(out_host, out_device, (size_t)B * sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return rs::cuda_fail(e, "ids D2H");
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return rs::cuda_fail(e, "cudaStreamSynchronize");
+    return RS_OK;
+}
+
+int rs_device_status(void* workspace_device, void* stream) {
+    int v = 0;
+    cudaError_t e = cudaMemcpyAsync(&v, workspace_device, sizeof v, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return rs::cuda_fail(e, "status read");
+    return v;
+}
+
+int rs_set_cluster_override(int cluster_ctas) {
+    const bool valid = cluster_ctas == 0 || cluster_ctas == 1 || cluster_ctas == 2 || cluster_ctas == 4 ||
+                       cluster_ctas == 8 || cluster_ctas == 16;
+    return valid ? rs::g_cluster_override.exchange(cluster_ctas) : rs::g_cluster_override.load();
+}
+
+uint64_t rs_kernel_launch_count(void) { return rs::g_launches.load(); }
+
+const char* rs_status_string(int status) {
+    switch (status) {
+        case RS_OK: return "ok";
+        case RS_ERR_DTYPE: return "Logits tensor must be of type float32 (FP32)";
+        case RS_ERR_VOCAB: return "Vocabulary size must be multiple of 4, and no larger than 1048576";
+        case RS_ERR_BATCH: return "B and T must be positive";
+        case RS_ERR_TEMPERATURE: return "Temperature outside range, expect [0.001, 1000]";
+        case RS_ERR_POINTER: return "null or misaligned pointer";
+        case RS_ERR_WORKSPACE: return "workspace too small";
+        case RS_ERR_CUDA: return "CUDA runtime error";
+        case RS_ERR_TIMEOUT: return "a bounded on-chip wait gave up";
+        case RS_ERR_LIMIT: return "size beyond what this entry point supports";
+    }
+    return "unknown status";
+}
+
+const char* rs_last_cuda_error(void) { return rs::g_err; }
+const char* rs_version(void) { return "rapid_sampling_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

@@ -1,0 +1,108 @@
+// PyTorch binding: the three functions of the reference's module (sampling.cpp:5-9) with the same
+// names, argument order and tensor semantics, forwarding to the C ABI of this library.
+// Argument names follow the reference's README so keyword calls work as well as positional ones.
+#include <torch/extension.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+
+#include "../../include/rapid_sampling_b200.h"
+
+namespace {
+
+[[noreturn]] void fail(int rc, const std::string& detail) {
+    std::string msg = std::string(rs_status_string(rc)) + detail + " !\n";
+    if (rc == RS_ERR_CUDA) throw std::runtime_error(msg + rs_last_cuda_error());
+    throw std::invalid_argument(msg);  // pybind11 maps this to ValueError, as in the reference
+}
+
+// One zero-initialised workspace per (device, stream); grows, never shrinks.
+at::Tensor& workspace_for(int device, cudaStream_t stream, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, at::Tensor> cache;
+    std::lock_guard<std::mutex> lk(mu);
+    at::Tensor& w = cache[{device, stream}];
+    if (!w.defined() || (size_t)w.numel() < bytes)
+        w = at::zeros({(int64_t)bytes}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
+    return w;
+}
+
+at::Tensor sample_common(at::Tensor& logits, at::Tensor* penalties, at::Tensor& states, double presence,
+                         double repetition, double decay, double temperature, int64_t top_k, double top_p) {
+    if (logits.dtype() != at::kFloat)
+        throw std::invalid_argument("Logits tensor must be of type float32 (FP32), got " +
+                                    std::string(logits.dtype().name()) + " !\n");
+    if (!logits.is_cuda() || !states.is_cuda()) throw std::invalid_argument("logits and states must be CUDA tensors !\n");
+    if (logits.dim() < 1 || logits.dim() > 3) throw std::invalid_argument("logits must have shape (V,), (B,V) or (B,T,V) !\n");
+    if (!logits.is_contiguous() || !states.is_contiguous()) throw std::invalid_argument("logits and states must be contiguous !\n");
+    const int64_t V = logits.size(-1);
+    int64_t B = (logits.dim() >= 2) ? logits.size(0) : 1;            // sampling.cu:983
+    const int64_t T = (logits.dim() == 3) ? logits.size(1) : 1;      // sampling.cu:984
+    float* pen = nullptr;
+    if (penalties) {
+        B = (penalties->dim() == 2) ? penalties->size(0) : 1;        // sampling.cu:459
+        if (penalties->dtype() != at::kFloat || !penalties->is_cuda() || !penalties->is_contiguous() ||
+            penalties->get_device() != logits.get_device())
+            throw std::invalid_argument("penalties must be a contiguous float32 CUDA tensor on the logits' device !\n");
+        if (penalties->numel() != B * V) throw std::invalid_argument("penalties must have shape (B, V) !\n");
+        if (logits.numel() < B * T * V) throw std::invalid_argument("logits hold fewer rows than penalties !\n");
+        pen = penalties->data_ptr<float>();
+    }
+    if (V > 0 && B > 0 && states.numel() * (int64_t)states.element_size() < B * RS_STATE_BYTES)
+        throw std::invalid_argument("states tensor is smaller than B rows of setup_rand output !\n");
+    if (states.get_device() != logits.get_device()) throw std::invalid_argument("states must live on the logits' device !\n");
+
+    c10::cuda::CUDAGuard guard(logits.device());
+    const int dev = logits.get_device();
+    cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
+    const size_t wsb = rs_workspace_bytes(B, V);
+    at::Tensor& ws = workspace_for(dev, stream, wsb);
+    at::Tensor out = at::empty({B > 0 ? B : 0}, at::TensorOptions().dtype(at::kInt).device(logits.device()));
+    const int rc = rs_sample(logits.data_ptr<float>(), B, T, V, pen, states.data_ptr(), out.data_ptr<int32_t>(), temperature,
+                             top_k, top_p, presence, repetition, decay, ws.data_ptr(), (size_t)ws.numel(), stream);
+    if (rc == RS_ERR_VOCAB) fail(rc, ", got " + std::to_string(V));
+    if (rc == RS_ERR_BATCH) fail(rc, ", got B=" + std::to_string(B) + ", T=" + std::to_string(T));
+    if (rc == RS_ERR_TEMPERATURE) fail(rc, ", got " + std::to_string(temperature));
+    if (rc != RS_OK) fail(rc, "");
+    return out;
+}
+
+}  // namespace
+
+at::Tensor setup_rand(int64_t seed, int64_t B) {
+    if (B <= 0) throw std::invalid_argument("B must be positive, got B=" + std::to_string(B) + " !\n");
+    at::Tensor state = at::empty({B * RS_STATE_BYTES}, at::TensorOptions().dtype(at::kChar).device(at::kCUDA));
+    const int rc = rs_setup_rand(state.data_ptr(), (uint64_t)seed, B, 0, at::cuda::getCurrentCUDAStream().stream());
+    if (rc != RS_OK) fail(rc, "");
+    return state;
+}
+
+at::Tensor batch_sampling_temperature_topk_topp(at::Tensor& logits, at::Tensor& states, double temperature, int64_t top_k,
+                                                double top_p) {
+    return sample_common(logits, nullptr, states, 0.0, 0.0, 0.0, temperature, top_k, top_p);
+}
+
+at::Tensor batch_sampling_repetition_temperature_topk_topp(at::Tensor& logits, at::Tensor& penalties, at::Tensor& states,
+                                                           double presence_penalty, double repetition_penalty,
+                                                           double penalty_decay, double temperature, int64_t top_k,
+                                                           double top_p) {
+    return sample_common(logits, &penalties, states, presence_penalty, repetition_penalty, penalty_decay, temperature,
+                         top_k, top_p);
+}
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    namespace py = pybind11;
+    m.def("setup_rand", &setup_rand, py::arg("seed"), py::arg("B"));
+    m.def("batch_sampling_repetition_temperature_topk_topp", &batch_sampling_repetition_temperature_topk_topp,
+          py::arg("logits"), py::arg("penalties"), py::arg("states"), py::arg("presence_penalty"),
+          py::arg("repetition_penalty"), py::arg("penalty_decay"), py::arg("temperature"), py::arg("top_k"),
+          py::arg("top_p"));
+    m.def("batch_sampling_temperature_topk_topp", &batch_sampling_temperature_topk_topp, py::arg("logits"),
+          py::arg("states"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"));
+    m.def("kernel_launch_count", []() { return rs_kernel_launch_count(); });
+    m.def("version", []() { return std::string(rs_version()); });
+}
