@@ -1,0 +1,342 @@
+#!/usr/bin/env python
+"""Benchmark of the sampling hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C1..C5] [--impl ours|reference|reference-cuda]
+
+A step is ONE sampling call over one batch of synthetic logits.  Default workload (N=1): the
+headline shape B=1, V=262144, N(0,3^2) logits, temperature 1, top_k -1, top_p 0.3.  Prints one JSON
+line: `value` = rows/s over all GPUs with inputs resident in HBM (each step reads a different row set
+from a pool larger than L2), `median_us` = median per-call latency, `e2e` = the same metric through
+the torch-facing API with pinned HOST logits (H2D + call + D2H of ids inside the timed region),
+`roofline` for the sampler kernel against the measured HBM copy bandwidth, `cpu_baseline` = the
+CPU port of the reference timed on the host.
+
+Under torchrun each rank takes the same per-GPU batch (weak scaling); rows are independent, so there
+is no collective on the data path -- only the barrier and the max-over-ranks of the timings.
+`--impl reference` times the CPU restatement of the reference (the reference has no CPU code of its
+own) on rank 0; `--impl reference-cuda` times the reference's own CUDA extension (oracle/_ref) on the
+same workload, for the latency comparison against the original kernel.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1000 * 1000
+# per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of sampler_kernel from the ncu
+# captures summarised under profiles/, keyed by workload; None where no capture exists.
+NCU_TRAFFIC = {}
+
+
+def workload(name):
+    """BASELINE configs. Returns dict(B, T, V, temperature, top_k, top_p, rep, dist, seed)."""
+    W = {
+        "C1": dict(B=4, T=1, V=131072, temperature=1.0, top_k=-1, top_p=0.5, rep=False, dist="uniform", seed=0,
+                   desc="example.py: B=4 V=131072 U[0,1) T=1 top_k=-1 top_p=0.5"),
+        "C2": dict(B=1, T=1, V=262144, temperature=1.0, top_k=-1, top_p=0.3, rep=False, dist="normal3", seed=1,
+                   desc="headline: B=1 V=262144 N(0,3^2) T=1 top_k=-1 top_p=0.3"),
+        "C3": dict(B=64, T=1, V=151936, temperature=0.8, top_k=50, top_p=0.9, rep=False, dist="peaked", seed=2,
+                   desc="batched decode: B=64 V=151936 N(0,2^2)+10 on 32 ids T=0.8 top_k=50 top_p=0.9"),
+        "C4": dict(B=256, T=1, V=65536, temperature=0.8, top_k=50, top_p=0.9, rep=True, dist="normal2.5", seed=3,
+                   desc="repetition: B=256 V=65536 N(0,2.5^2) penalties presence=.1 repetition=.1 decay=.95 T=0.8 top_k=50 top_p=0.9"),
+        "C5": dict(B=32, T=4, V=1048576, temperature=1.0, top_k=-1, top_p=0.95, rep=False, dist="boosted", seed=4,
+                   desc="large vocab: (B,T,V)=(32,4,1048576) N(0,1)+8 on 1% ids T=1 top_k=-1 top_p=0.95"),
+    }
+    return W[name]
+
+
+def gen_logits(w, seed, device, torch):
+    """One synthetic logits tensor of the workload's shape and distribution, generated on `device`."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    B, T, V = w["B"], w["T"], w["V"]
+    shape = (B, V) if T == 1 else (B, T, V)
+    d = w["dist"]
+    if d == "uniform":
+        return torch.rand(shape, generator=g, device=device)
+    x = torch.randn(shape, generator=g, device=device)
+    if d == "normal3":
+        return x * 3
+    if d == "normal2.5":
+        return x * 2.5
+    if d == "peaked":
+        x = x * 2
+        idx = torch.rand(B, V, generator=g, device=device).argsort(dim=-1)[:, :32]
+        return x.scatter_add_(1, idx, torch.full((B, 32), 10.0, device=device))
+    if d == "boosted":
+        n = V // 100
+        idx = torch.randint(0, V, (B, n), generator=g, device=device)
+        boost = torch.zeros(B, V, device=device).scatter_(1, idx, 8.0)
+        return x + (boost if T == 1 else boost.unsqueeze(1))
+    raise ValueError(d)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run (read-only)."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40,
+                 "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h) if hasattr(nv, "nvmlDeviceGetCurrentClocksEventReasons") \
+                    else nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.01)
+
+    def start(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_port_baseline(w, budget_s=12.0, max_calls=64):
+    """Times the CPU restatement of the reference (oracle/sampler_oracle.c) on this host: whole calls of the
+    workload's shape, rows spread over the host cores, until the budget is used."""
+    import numpy as np
+    import torch
+    from oracle import c_oracle as co
+    B, V = w["B"], w["V"]
+    lg = gen_logits(dict(w, T=1), w["seed"], "cpu", torch).numpy()
+    pen = np.zeros((B, V), dtype=np.float32) if w["rep"] else None
+    st = co.setup_rand(w["seed"], B)
+    cores = min(os.cpu_count() or 1, B)
+    co.sample(lg, st, w["temperature"], w["top_k"], w["top_p"], penalties=pen, presence=0.1, repetition=0.1, decay=0.95,
+              nthreads=cores)
+    t0 = time.perf_counter()
+    calls = 0
+    while calls < max_calls and time.perf_counter() - t0 < budget_s:
+        co.sample(lg, st, w["temperature"], w["top_k"], w["top_p"], penalties=pen, presence=0.1, repetition=0.1,
+                  decay=0.95, nthreads=cores)
+        calls += 1
+    dt = time.perf_counter() - t0
+    return {"value": B * calls / dt, "unit": "rows/s", "cores": cores, "kind": "port",
+            "sample": "%d whole calls of the workload (%d rows x V=%d each), %.1f s" % (calls, B, V, dt),
+            "ms_per_call": dt / calls * 1e3}
+
+
+def cpu_torch_f64(w, budget_s=6.0, max_calls=16):
+    """The same semantics as a float64 torch CPU path (sort + cumsum), for the record."""
+    import torch
+    from oracle import cpu_ref
+    lg = gen_logits(dict(w, T=1), w["seed"], "cpu", torch)
+    pen = torch.zeros(w["B"], w["V"]) if w["rep"] else None
+    cpu_ref.sample(lg, w["temperature"], w["top_k"], w["top_p"], pen, 0.1, 0.1, 0.95)
+    t0 = time.perf_counter()
+    calls = 0
+    while calls < max_calls and time.perf_counter() - t0 < budget_s:
+        cpu_ref.sample(lg, w["temperature"], w["top_k"], w["top_p"], pen, 0.1, 0.1, 0.95)
+        calls += 1
+    dt = time.perf_counter() - t0
+    return {"rows_per_s": w["B"] * calls / dt, "ms_per_call": dt / calls * 1e3, "threads": torch.get_num_threads(),
+            "cpu_count": os.cpu_count()}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    w = workload(a.config)
+    K, Wm = max(a.steps, 1), max(a.warmup, 3)
+    B, T, V = w["B"], w["T"], w["V"]
+    base = {"metric": "rows_per_s", "unit": "rows/s", "n_gpus": world, "steps": K, "warmup": Wm,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": a.config + " " + w["desc"], "rows_per_gpu": B, "parallelism": "batch-sharded x%d" % world}}
+
+    if a.impl == "reference":
+        # CPU arm: the reference ships no CPU implementation, so this is the CPU restatement (oracle port).
+        if rank != 0:
+            return
+        cb = cpu_port_baseline(w, budget_s=max(5.0, min(60.0, 0.05 * K)), max_calls=K)
+        line = dict(base, impl="reference", value=cb["value"], ms_per_step=cb["ms_per_call"], n_gpus=world,
+                    cpu_baseline=cb, gpu_launches=0,
+                    e2e={"value": cb["value"], "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        line["config"]["parallelism"] = "host cores (%d threads)" % cb["cores"]
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    if a.impl == "ours":
+        import rapid_sampling_b200 as rs
+        from rapid_sampling_b200.sharding import setup_rand_rows
+        ext = rs._load_ext()
+        states = setup_rand_rows(w["seed"], rank * B, B)
+        launches = ext.kernel_launch_count
+    else:
+        from oracle import build_ref
+        ext = build_ref.load_ref()
+        if ext is None:
+            if rank == 0:
+                print(json.dumps({"impl": "reference-cuda", "unavailable": "oracle/_ref was not built"}))
+            return
+        if T != 1:
+            w = dict(w, T=1)   # the reference kernel writes out of bounds for 3-D input: feed it the last slice
+            T = 1
+        states = ext.setup_rand(w["seed"], B)
+        launches = lambda: 0  # noqa: E731
+
+    # input pool larger than L2 so that every step reads its logits from HBM
+    row_bytes = B * T * V * 4
+    pool_n = max(2, min(256, -(-int(1.6 * L2_BYTES) // row_bytes)))
+    if a.config == "C5":
+        pool_n = 2
+    pool = [gen_logits(w, w["seed"] + 1000 * i + 7 * rank, dev, torch) for i in range(pool_n)]
+    pen = torch.zeros(B, V, device=dev) if w["rep"] else None
+
+    def call(lg):
+        if w["rep"]:
+            return ext.batch_sampling_repetition_temperature_topk_topp(lg, pen, states, 0.1, 0.1, 0.95, w["temperature"],
+                                                                       w["top_k"], w["top_p"])
+        return ext.batch_sampling_temperature_topk_topp(lg, states, w["temperature"], w["top_k"], w["top_p"])
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for i in range(Wm):
+        call(pool[i % pool_n])
+    sync_all()
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+
+    # ---- timed region: exactly K steps, device-timed, max over ranks -------------------------------
+    n0 = launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for i in range(K):
+        call(pool[i % pool_n])
+    e1.record()
+    torch.cuda.synchronize()
+    gpu_launches = launches() - n0
+    total_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t[0])
+
+    # ---- per-call latency (median), events around every call --------------------------------------
+    nlat = min(K, 1000)
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nlat)]
+    for i in range(nlat):
+        evs[i][0].record()
+        call(pool[i % pool_n])
+        evs[i][1].record()
+    torch.cuda.synchronize()
+    lat = sorted(x.elapsed_time(y) * 1e3 for x, y in evs)
+    median_us = lat[len(lat) // 2]
+    # wall-clock per call with a sync, the reference bench's own method (bench.py:73-92)
+    nw = min(K, 200)
+    walls = []
+    for i in range(nw):
+        t0 = time.perf_counter()
+        call(pool[i % pool_n])
+        torch.cuda.synchronize()
+        walls.append((time.perf_counter() - t0) * 1e6)
+    wall_median_us = statistics.median(walls)
+
+    # ---- end to end: pinned host logits -> device -> call -> ids back on the host ------------------
+    host_n = max(2, min(8, pool_n))
+    last = (lambda x: x) if T == 1 else (lambda x: x[:, -1, :].contiguous())   # only position T-1 is ever read
+    host_pool = [last(pool[i]).cpu().pin_memory() for i in range(host_n)]
+    e2e = None
+    if host_pool is not None:
+        stage = torch.empty(B, V, device=dev)
+        ke = max(3, min(K, 200))
+
+        def e2e_step(i):
+            stage.copy_(host_pool[i % host_n], non_blocking=True)
+            return call(stage).cpu()
+        for i in range(3):
+            e2e_step(i)
+        sync_all()
+        t0 = time.perf_counter()
+        for i in range(ke):
+            e2e_step(i)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t[0])
+        e2e = {"value": world * B * ke / dt, "unit": "rows/s", "h2d_bytes_per_step": B * V * 4, "d2h_bytes_per_step": 4 * B,
+               "steps": ke, "ms_per_step": dt / ke * 1e3}
+    clk = clocks.stop()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_per_step = total_ms / K
+    alg_bytes = (12 if w["rep"] else 4) * V * B            # logits read once (+ penalties read + write)
+    peak, peak_src = 6650.0, "fallback"
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        peak_src = "measured"
+    except Exception:
+        pass
+    achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    line = dict(base, impl=a.impl, value=world * B * K / (total_ms * 1e-3), ms_per_step=ms_per_step,
+                median_us=median_us, p10_us=lat[len(lat) // 10], p90_us=lat[(len(lat) * 9) // 10],
+                wall_sync_median_us=wall_median_us, clocks=clk, e2e=e2e, gpu_launches=int(gpu_launches),
+                roofline={"bound": "hbm", "kernel": "sampler_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                          "frac": achieved / peak, "peak_source": peak_src + " HBM copy bandwidth",
+                          "algorithmic_bytes_per_launch": alg_bytes, "traffic": NCU_TRAFFIC.get(a.config)})
+    line["config"]["l2"] = "inputs rotate through a pool of %d logits sets (%.0f MB > L2)" % (pool_n, pool_n * row_bytes / 1e6)
+    if a.impl == "ours" and not a.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_port_baseline(w)
+        line["cpu_torch_f64"] = cpu_torch_f64(w)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

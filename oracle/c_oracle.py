@@ -50,6 +50,15 @@ def lib():
                                           C.POINTER(C.c_int), fp, C.POINTER(C.c_int), fp]
         L.rs_oracle_sample.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                        C.c_double, C.c_int64, C.c_double, C.c_double, C.c_double, C.c_double, C.c_int]
+        L.rs_oracle_block_scan.argtypes = [C.c_void_p, C.c_void_p]
+        L.rs_oracle_block_scan.restype = C.c_float
+        L.rs_oracle_warp_scan_ascending.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.rs_oracle_warp_scan_descending.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        for f in ("rs_oracle_block_sum_tree", "rs_oracle_block_sum_seq"):
+            getattr(L, f).argtypes = [C.c_void_p]
+            getattr(L, f).restype = C.c_float
+        L.rs_oracle_sf.argtypes = [C.c_float]
+        L.rs_oracle_sf.restype = C.c_float
         _lib = L
     return _lib
 
@@ -133,4 +142,20 @@ def sample(logits, states, temperature, top_k, top_p, penalties=None, presence=0
                                 presence, repetition, decay, nthreads or os.cpu_count() or 1)
     if rc:
         raise ArgError(_ERR[rc])
+    return out
+
+
+def block_scan(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.size == 1024
+    out = np.empty(1024, dtype=np.float32)
+    total = lib().rs_oracle_block_scan(x.ctypes.data, out.ctypes.data)
+    return out, np.float32(total)
+
+
+def scan_n(x, ascending):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    f = lib().rs_oracle_warp_scan_ascending if ascending else lib().rs_oracle_warp_scan_descending
+    f(x.ctypes.data, out.ctypes.data, x.size)
     return out

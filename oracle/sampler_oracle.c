@@ -415,3 +415,41 @@ int rs_oracle_sample(const float* logits, float* penalties, uint8_t* states, int
     }
     return 0;
 }
+
+/* ------------------------------------------------------ exported primitives (tests) ---- */
+
+/* The 1024-wide inclusive scan used for the lane / element picks. Returns the total. */
+float rs_oracle_block_scan(const float* in, float* out) { return block_scan(in, out); }
+
+/* The variant the reference rejects (sampling.cu:79-83 and monotonicity.py): ascending offsets.
+ * Kept only so that a test can show it is NOT monotone while the descending one is. */
+void rs_oracle_warp_scan_ascending(const float* in, float* out, int n) {
+    float* a = (float*)malloc(sizeof(float) * (size_t)n);
+    float* b = (float*)malloc(sizeof(float) * (size_t)n);
+    memcpy(a, in, sizeof(float) * (size_t)n);
+    for (int off = 1; off < n; off <<= 1) {
+        for (int i = 0; i < n; i++) b[i] = (i >= off) ? a[i] + a[i - off] : a[i];
+        memcpy(a, b, sizeof(float) * (size_t)n);
+    }
+    memcpy(out, a, sizeof(float) * (size_t)n);
+    free(a);
+    free(b);
+}
+
+/* Descending offsets over n (a power of two) values: the order of sampling.cu:48-58 generalised. */
+void rs_oracle_warp_scan_descending(const float* in, float* out, int n) {
+    float* a = (float*)malloc(sizeof(float) * (size_t)n);
+    float* b = (float*)malloc(sizeof(float) * (size_t)n);
+    memcpy(a, in, sizeof(float) * (size_t)n);
+    for (int off = n / 2; off > 0; off >>= 1) {
+        for (int i = 0; i < n; i++) b[i] = (i >= off) ? a[i] + a[i - off] : a[i];
+        memcpy(a, b, sizeof(float) * (size_t)n);
+    }
+    memcpy(out, a, sizeof(float) * (size_t)n);
+    free(a);
+    free(b);
+}
+
+float rs_oracle_block_sum_tree(const float* lane) { return block_sum_tree(lane); }
+float rs_oracle_block_sum_seq(const float* lane) { return block_sum_seq(lane); }
+float rs_oracle_sf(float x) { return sf(x); }

@@ -114,3 +114,25 @@ class Abi:
 
     def set_cluster(self, c):
         return self.L.rs_set_cluster_override(c)
+
+
+def kept_set_flips_ok(kept32, d, b, mass_tol=1e-6, tie_tol=4e-6):
+    """True when every token whose membership differs between the fp32 kept set and the float64
+    closed form `d` (oracle.cpu_ref.distribution) lies on the boundary: its float64 cumulative
+    mass is within `mass_tol` relative of top_p, or its probability ties with the boundary
+    probability within `tie_tol` relative (fp32 rounding of p). Returns (ok, n_flips)."""
+    kept64 = d["kept"][b].numpy()
+    flips = np.nonzero(kept32 ^ kept64)[0]
+    if len(flips) == 0:
+        return True, 0
+    V = kept64.shape[0]
+    order = d["order"][b].numpy()
+    cum = d["cum_sorted"][b].numpy()
+    rank = np.empty(V, dtype=np.int64)
+    rank[order] = np.arange(V)
+    p64, v64, top_p = d["probs"][b].numpy(), float(d["v"][b]), d["top_p"]
+    r = rank[flips]
+    near_mass = np.abs(cum[r] - top_p) <= mass_tol * top_p
+    near_mass |= np.abs(cum[np.maximum(r - 1, 0)] - top_p) <= mass_tol * top_p
+    near_tie = np.abs(p64[flips] - v64) <= tie_tol * v64
+    return bool(np.all(near_mass | near_tie)), len(flips)
