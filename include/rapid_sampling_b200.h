@@ -96,6 +96,31 @@ int rs_sample_host(const float* logits_host, int64_t B, int64_t T, int64_t V, fl
                    float* staging_device, int32_t* out_device, void* workspace_device, size_t workspace_bytes,
                    void* stream);
 
+/*
+ * Sampling for callers that cannot allocate device memory.  No counterpart in the reference (its host
+ * functions allocate a scratch tensor on every call, sampling.cu:488, :1014).
+ *
+ * Who needs it: a serving process that gave all of HBM to its own arena at start-up, so that cudaMalloc has
+ * nothing left to hand out; and a latency-critical decode loop that must not enter an allocator which may
+ * synchronise the device.  Same arguments and results as rs_sample, but without a workspace: the kernel's
+ * scratch rows live in a fixed array inside the library image (16 MiB + 256 B, held by every GPU that loads
+ * the library until the process exits), and the call performs no cudaMalloc, cudaFree or other allocation.
+ *
+ * Limits and rules:
+ *  - B * V must not exceed RS_STATIC_SCRATCH_FLOATS, otherwise RS_ERR_LIMIT is returned and nothing runs.
+ *  - The first call on each device looks up the array's device address (and clears its status word); make
+ *    that first call before any stream capture begins.
+ *  - All calls on a device share the one array, which keeps whatever the previous call left in it (the kernel
+ *    overwrites what it reads, only the status word relies on the initial clearing).  Two calls that overlap
+ *    on the GPU (different streams) race on it: keep calls to this entry point on one stream, or order them.
+ *  - It always runs the global-scratch-row variant of the kernel, so it is slower than rs_sample for rows that
+ *    would fit on chip; ids, states and penalties are identical to rs_sample's.
+ */
+#define RS_STATIC_SCRATCH_FLOATS 4194304
+int rs_sample_static_scratch(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                             void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
+                             double presence_penalty, double repetition_penalty, double penalty_decay, void* stream);
+
 /* Reads the device status word of `workspace_device` (synchronises `stream`): RS_OK or RS_ERR_TIMEOUT. */
 int rs_device_status(void* workspace_device, void* stream);
 

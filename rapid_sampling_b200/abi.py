@@ -13,8 +13,9 @@ RS_OK = 0
 RS_ERR_DTYPE, RS_ERR_VOCAB, RS_ERR_BATCH, RS_ERR_TEMPERATURE = -1, -2, -3, -4
 RS_ERR_POINTER, RS_ERR_WORKSPACE, RS_ERR_CUDA, RS_ERR_TIMEOUT, RS_ERR_LIMIT = -5, -6, -7, -8, -9
 RS_STATE_BYTES = 64
+RS_STATIC_SCRATCH_FLOATS = 4194304
 
-SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host",
+SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_static_scratch",
            "rs_device_status", "rs_set_cluster_override", "rs_kernel_launch_count", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
@@ -45,6 +46,7 @@ def load():
     L.rs_sample.argtypes = common + [vp, C.c_size_t, vp]
     L.rs_sample_debug.argtypes = common + [vp, C.c_size_t, vp, vp, vp]
     L.rs_sample_host.argtypes = common + [vp, vp, vp, C.c_size_t, vp]
+    L.rs_sample_static_scratch.argtypes = common + [vp]
     L.rs_device_status.argtypes = [vp, vp]
     L.rs_set_cluster_override.argtypes = [C.c_int]
     L.rs_kernel_launch_count.restype = C.c_uint64

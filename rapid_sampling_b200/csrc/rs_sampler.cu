@@ -675,6 +675,79 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     return RS_ERR_LIMIT;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Scratch that lives inside the library image, for rs_sample_static_scratch().
+//
+// Some hosts may not allocate device memory when they want to sample: a serving process that has
+// handed all of HBM to its own arena at start-up has nothing left for cudaMalloc to give, and a
+// latency-critical decode loop must not call an allocator that can synchronise the whole device.
+// For them the global-scratch-row variant of the sampler runs on this fixed array instead of a
+// caller-provided workspace.  Layout: 256 bytes of status word, then the scratch rows.
+// Every GPU that loads the library carries the array (16 MiB + 256 B) until the process exits.
+static __device__ __align__(256) float g_static_scratch[64 + RS_STATIC_SCRATCH_FLOATS];
+static float* g_static_ptr[64] = {};   // device address of the array, per device, filled at set-up
+
+// Set-up, once per device, with that device current.  In host code the array's NAME is only a
+// host-side handle; the device address has to be asked for.
+static int static_scratch_address(int dev, float** out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_static_ptr[dev]) {
+        float* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+        if (!ptr) return RS_ERR_POINTER;
+        e = cudaMemset(ptr, 0, 256);   // the status word starts clear; the rows need no clearing (written before read)
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(static status word)");
+        g_static_ptr[dev] = ptr;
+    }
+    *out = g_static_ptr[dev];
+    return RS_OK;
+}
+
+static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t V, float* penalties, void* states,
+                              int32_t* out, double temperature, int64_t top_k, double top_p, double presence,
+                              double repetition, double decay, void* stream) {
+    if (!(V > 0 && V <= 1048576 && V % 4 == 0)) return RS_ERR_VOCAB;
+    if (!(B > 0 && T > 0)) return RS_ERR_BATCH;
+    if (!(temperature >= 0.001 && temperature <= 1000)) return RS_ERR_TEMPERATURE;
+    if (B * V > (int64_t)RS_STATIC_SCRATCH_FLOATS) return RS_ERR_LIMIT;
+    if (!logits || !states || !out) return RS_ERR_POINTER;
+    if (((uintptr_t)logits & 15) || ((uintptr_t)states & 15) || ((uintptr_t)penalties & 15)) return RS_ERR_POINTER;
+    if (top_k <= 0 || top_k > V) top_k = V;
+    if (top_p < 0 || top_p > 1) top_p = 1;
+    if (top_p == 0) { top_k = 1; top_p = 1; }
+    DeviceInfo* di = nullptr;
+    int rc = get_device(&di);
+    if (rc) return rc;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    float* base = nullptr;
+    rc = static_scratch_address(dev, &base);
+    if (rc) return rc;
+    Params p;
+    p.logits = logits + (T - 1) * V;
+    p.row_stride = (long long)T * V;
+    p.penalties = penalties;
+    p.states = (unsigned char*)states;
+    p.out = out;
+    p.status = (int*)base;
+    p.scratch = base + 64;
+    p.dbg_probs = nullptr;
+    p.dbg_trace = nullptr;
+    p.B = (int)B;
+    p.V = (int)V;
+    p.kind = penalties ? kRepetition : ((temperature == 1 && top_k == V) ? kTopP : kGeneral);
+    p.top_k = (int)top_k;
+    p.scale = (p.kind == kTopP) ? (float)1.4426950408889634074 : (float)(1.4426950408889634074 / temperature);
+    p.top_p = (float)top_p;
+    p.presence = (float)presence;
+    p.repetition = (float)repetition;
+    p.decay = (float)decay;
+    return launch_one<8, false>(p, kSlabOff, (cudaStream_t)stream, *di);
+}
+
 }  // namespace rs
 
 // ------------------------------------------------------------------- C ABI -----------------
@@ -774,6 +847,13 @@ const char* rs_status_string(int status) {
         case RS_ERR_LIMIT: return "size beyond what this entry point supports";
     }
     return "unknown status";
+}
+
+int rs_sample_static_scratch(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                             void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
+                             double presence_penalty, double repetition_penalty, double penalty_decay, void* stream) {
+    return rs::sample_static_impl(logits_device, B, T, V, penalties_device, states_device, out_device, temperature, top_k,
+                                  top_p, presence_penalty, repetition_penalty, penalty_decay, stream);
 }
 
 const char* rs_last_cuda_error(void) { return rs::g_err; }
