@@ -30,7 +30,8 @@ enum {
     RS_ERR_WORKSPACE = -6,   /* workspace smaller than rs_workspace_bytes()                      */
     RS_ERR_CUDA = -7,        /* a CUDA runtime call failed; see rs_last_cuda_error()             */
     RS_ERR_TIMEOUT = -8,     /* device status: a bounded on-chip wait gave up                    */
-    RS_ERR_LIMIT = -9        /* size beyond what this entry point supports                       */
+    RS_ERR_LIMIT = -9,       /* size beyond what this entry point supports                       */
+    RS_ERR_INTERNAL = -10    /* device status: an invariant of the cutoff search was violated    */
 };
 
 /* Bytes per row of the RNG state tensor: layout-compatible with curandStatePhilox4_32_10_t
@@ -42,6 +43,10 @@ typedef struct rs_trace {
     float maxu, denom, pmin, pmax, threshold, comp, sgtp, sum_p, randp, sum_o, rand2;
     uint32_t left, seqk, sgtk, rounds, idxt, early_exit, rnd[4];
     int32_t token;
+    uint32_t path;   /* 0 = cutoff found on the candidate list, 1 = whole-row search */
+    uint32_t ncand;  /* elements on the candidate list */
+    uint32_t t_ns[10]; /* ns since kernel entry of the owner CTA's thread 0 at: 1 row resident, 2 pass 1, 3 exchange,
+                          4 pass 2, 5 exchange, 6 search+recount, 7 lane pick, 8 element pick */
 } rs_trace;
 
 /*
@@ -127,6 +132,10 @@ int rs_device_status(void* workspace_device, void* stream);
 /* Forces the thread-block-cluster width (1, 2, 4, 8 or 16) used per row; 0 restores the automatic
  * choice.  Benchmarking aid; returns the previous value. */
 int rs_set_cluster_override(int cluster_ctas);
+
+/* Search strategy: 0 = automatic (candidate shortcut with whole-row fallback), 1 = always search the whole
+ * row.  Results are identical; testing / benchmarking aid.  Returns the previous value. */
+int rs_set_path_override(int mode);
 
 /* Number of sampler kernels launched through this library since it was loaded. */
 uint64_t rs_kernel_launch_count(void);

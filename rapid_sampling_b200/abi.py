@@ -12,11 +12,12 @@ LIB_PATH = os.path.join(HERE, "librapid_sampling_b200.so")
 RS_OK = 0
 RS_ERR_DTYPE, RS_ERR_VOCAB, RS_ERR_BATCH, RS_ERR_TEMPERATURE = -1, -2, -3, -4
 RS_ERR_POINTER, RS_ERR_WORKSPACE, RS_ERR_CUDA, RS_ERR_TIMEOUT, RS_ERR_LIMIT = -5, -6, -7, -8, -9
+RS_ERR_INTERNAL = -10
 RS_STATE_BYTES = 64
 RS_STATIC_SCRATCH_FLOATS = 4194304
 
 SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_static_scratch",
-           "rs_device_status", "rs_set_cluster_override", "rs_kernel_launch_count", "rs_status_string",
+           "rs_device_status", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
 
@@ -24,7 +25,7 @@ class Trace(C.Structure):
     _fields_ = [(n, C.c_float) for n in
                 ("maxu", "denom", "pmin", "pmax", "threshold", "comp", "sgtp", "sum_p", "randp", "sum_o", "rand2")] + \
                [(n, C.c_uint32) for n in ("left", "seqk", "sgtk", "rounds", "idxt", "early_exit")] + \
-               [("rnd", C.c_uint32 * 4), ("token", C.c_int32)]
+               [("rnd", C.c_uint32 * 4), ("token", C.c_int32), ("path", C.c_uint32), ("ncand", C.c_uint32), ("t_ns", C.c_uint32 * 10)]
 
 
 _lib = None
@@ -49,6 +50,7 @@ def load():
     L.rs_sample_static_scratch.argtypes = common + [vp]
     L.rs_device_status.argtypes = [vp, vp]
     L.rs_set_cluster_override.argtypes = [C.c_int]
+    L.rs_set_path_override.argtypes = [C.c_int]
     L.rs_kernel_launch_count.restype = C.c_uint64
     for f in ("rs_status_string", "rs_last_cuda_error", "rs_version"):
         getattr(L, f).restype = C.c_char_p

@@ -41,6 +41,8 @@ struct Params {
     rs_trace* dbg_trace;     // optional B
     int* status;             // device status word
     int B, V, kind, top_k;
+    int sel_rank;            // 0 = no candidate shortcut; else rank of the per-warp thread maximum used as bound
+    int cand_slots;          // float4 slots per lane of the candidate buffer (shared-memory variant)
     float scale, top_p, presence, repetition, decay;
 };
 
@@ -69,7 +71,7 @@ __device__ __forceinline__ float scaled_logit(float l, float pen, bool rep, floa
     return rep ? sanitize((sanitize(l) - pen) * scale) : sanitize(l * scale);
 }
 
-// One search pass over this lane's candidate list: counts and ordered masses at three pivots;
+// One search pass over this lane's list in the slab: counts and ordered masses at three pivots;
 // optionally keeps only elements >= keepf (in place, order preserved, tail padded with -1).
 template <int C, bool SMEM, bool COMPACT>
 __device__ __forceinline__ void search_pass(const Row<C, SMEM>& row, int& n, float py, float pz, float pw, float keepf,
@@ -113,10 +115,17 @@ __device__ __forceinline__ void search_pass(const Row<C, SMEM>& row, int& n, flo
     mass[0] = my; mass[1] = mz; mass[2] = mw;
 }
 
+// Sanitised scaled logit with the common case (finite product) kept to a multiply and a compare.
+__device__ __forceinline__ float scaled_fast(float l, float scale) {
+    const float x = l * scale;
+    return (fabsf(x) <= FLT_MAX) ? x : sanitize(x);
+}
+
 template <int C, bool SMEM>
 __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     constexpr int L = kLanes / C;
     constexpr int WPC = L / 32;  // warps per CTA
+    constexpr unsigned FULL = 0xffffffffu;
     extern __shared__ __align__(128) unsigned char smem[];
     const int t = threadIdx.x, lane = t & 31, wl = t >> 5;
     const uint32_t crank = (C == 1) ? 0u : cluster_ctarank();
@@ -134,11 +143,17 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + kMiscOff);
     int* s_idxt = reinterpret_cast<int*>(smem + kMiscOff + 8);
     int* s_token = reinterpret_cast<int*>(smem + kMiscOff + 12);
+    uint32_t* s_res = reinterpret_cast<uint32_t*>(smem + kMiscOff + 32);   // 8 words: combined round result
     float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
     Row<C, SMEM> row;
-    row.slab = SMEM ? reinterpret_cast<float4*>(smem + kSlabOff) : reinterpret_cast<float4*>(p.scratch + (long long)b * V);
+    row.slab = SMEM ? reinterpret_cast<float4*>(smem + kSlabOff + p.cand_slots * L * 16)
+                    : reinterpret_cast<float4*>(p.scratch + (long long)b * V);
     row.t = t;
     row.tg = tg;
+    // candidate buffer: cand_slots float4 slots per lane, [slot][lane] like the slab
+    float* cand = reinterpret_cast<float*>(smem + kSlabOff);
+    const int cap = p.cand_slots * 4;
+    auto cand_at = [&](int i) -> float& { return cand[((i >> 2) * L + t) * 4 + (i & 3)]; };
 
     const uint32_t mbox_a = smem_addr(mbox);
     int phase = 0;
@@ -160,6 +175,58 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         else { cluster_arrive(); cluster_wait(); }
     };
     const float4* mb;  // mailbox buffer to read after a sync
+    // phase timestamps (ns) for the trace: test instrumentation only
+    uint32_t ts[10];
+    const bool want_ts = (p.dbg_trace != nullptr);
+    unsigned long long t_begin = 0;
+    auto stamp = [&](int i) {
+        if (want_ts) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (i == 0) t_begin = now;
+            ts[i] = (uint32_t)(now - t_begin);
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < 10; i++) ts[i] = 0;
+    stamp(0);
+
+    // One search round's reduction: warp partials -> mailboxes -> one warp per CTA combines the 32
+    // entries (counts exactly; masses in warp order 0..31, as thread 0 of the reference does,
+    // sampling.cu:34-42) and hands the six totals to the other warps through shared memory.
+    auto combine_round = [&](uint32_t cnt[3], float mass[3]) {
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            cnt[i] = __reduce_add_sync(FULL, cnt[i]);
+            mass[i] = warp_tree_sum(mass[i]);
+        }
+        post(make_uint4(cnt[0], cnt[1], cnt[2], 0),
+             make_uint4(__float_as_uint(mass[0]), __float_as_uint(mass[1]), __float_as_uint(mass[2]), 0));
+        exchange_sync();
+        const float4* m = mbox + phase * 64;
+        phase ^= 1;
+        if (wl == 0) {
+            const uint4 c4 = reinterpret_cast<const uint4*>(m)[lane * 2];
+            const uint32_t c0 = __reduce_add_sync(FULL, c4.x), c1 = __reduce_add_sync(FULL, c4.y),
+                           c2 = __reduce_add_sync(FULL, c4.z);
+            float4 m4 = m[1];
+            float s0 = m4.x, s1 = m4.y, s2 = m4.z;
+#pragma unroll
+            for (int w = 1; w < kWarps; w++) {
+                m4 = m[w * 2 + 1];
+                s0 += m4.x; s1 += m4.y; s2 += m4.z;
+            }
+            if (lane == 0) {
+                reinterpret_cast<uint4*>(s_res)[0] = make_uint4(c0, c1, c2, 0);
+                reinterpret_cast<float4*>(s_res)[1] = make_float4(s0, s1, s2, 0.f);
+            }
+        }
+        __syncthreads();
+        const uint4 rc = reinterpret_cast<const uint4*>(s_res)[0];
+        const float4 rm = reinterpret_cast<const float4*>(s_res)[1];
+        cnt[0] = rc.x; cnt[1] = rc.y; cnt[2] = rc.z;
+        mass[0] = rm.x; mass[1] = rm.y; mass[2] = rm.z;
+    };
 
     // ---- load: bulk async copies of this CTA's stripes; RNG state read meanwhile -------------
     if (SMEM) {
@@ -200,30 +267,70 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         if (!mbar_wait_bounded(smem_addr(mbar), 0, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
     }
 
-    // ---- pass 1: x = sanitised scaled logit, row max (sampling.cu:208-227, :547-559) ---------
-    float mx = -INFINITY;
+    stamp(1);   // row resident
+    // ---- pass 1: x = sanitised scaled logit (sampling.cu:208-227, :547-559); row max; and this
+    // thread's own maximum, from which a lower bound for the cutoff is derived below -------------
+    float tmax = -INFINITY;
+    if (rep) {
 #pragma unroll 2
-    for (int s = 0; s < Kt; s++) {
-        float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
-        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (rep) q4 = reinterpret_cast<const float4*>(prow)[s * kLanes + tg];
-        v.x = scaled_logit(v.x, q4.x, rep, p.scale);
-        v.y = scaled_logit(v.y, q4.y, rep, p.scale);
-        v.z = scaled_logit(v.z, q4.z, rep, p.scale);
-        v.w = scaled_logit(v.w, q4.w, rep, p.scale);
-        mx = fmaxf(fmaxf(fmaxf(mx, v.x), fmaxf(v.y, v.z)), v.w);
-        row.st(s, v);
+        for (int s = 0; s < Kt; s++) {
+            float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
+            const float4 q4 = reinterpret_cast<const float4*>(prow)[s * kLanes + tg];
+            v.x = scaled_logit(v.x, q4.x, true, p.scale);
+            v.y = scaled_logit(v.y, q4.y, true, p.scale);
+            v.z = scaled_logit(v.z, q4.z, true, p.scale);
+            v.w = scaled_logit(v.w, q4.w, true, p.scale);
+            tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
+            row.st(s, v);
+        }
+    } else {
+#pragma unroll 4
+        for (int s = 0; s < Kt; s++) {
+            float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
+            v.x = scaled_fast(v.x, p.scale);
+            v.y = scaled_fast(v.y, p.scale);
+            v.z = scaled_fast(v.z, p.scale);
+            v.w = scaled_fast(v.w, p.scale);
+            tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
+            row.st(s, v);
+        }
     }
-    mx = warp_max(mx);
+    stamp(2);   // pass 1 done
+    float mx = warp_max(tmax);
+    // The warp's sel_rank-th largest thread maximum: at least sel_rank elements of this warp are >= it.
+    float wsel = INFINITY;
+    const int sel_rank = p.sel_rank;
+    if (sel_rank > 0) {
+        int rank = 0;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            const float o = __shfl_sync(FULL, tmax, i);
+            rank += (o > tmax || (o == tmax && i < lane)) ? 1 : 0;
+        }
+        const unsigned m = __ballot_sync(FULL, rank == sel_rank - 1);
+        wsel = __shfl_sync(FULL, tmax, __ffs(m) - 1);
+    }
     if (C > 1) cluster_wait();
-    post(make_uint4(__float_as_uint(mx), 0, 0, 0), make_uint4(0, 0, 0, 0));
+    post(make_uint4(__float_as_uint(mx), __float_as_uint(wsel), 0, 0), make_uint4(0, 0, 0, 0));
     exchange_sync();
     mb = mbox + phase * 64;
     phase ^= 1;
-    mx = warp_max(mb[lane * 2].x);
+    float beta_x;
+    {
+        const float4 e = mb[lane * 2];
+        mx = warp_max(e.x);
+        beta_x = warp_min(e.y);   // every warp holds >= sel_rank elements >= beta_x
+    }
+    stamp(3);   // first exchange done
+    const bool try_cand = (sel_rank > 0) && SMEM;
+    // Candidates are defined in the domain of e = exp2f(x - max): division by the denominator is
+    // monotone, so {e >= beta_e} contains every element whose probability exceeds beta_e / denom.
+    const float beta_e = try_cand ? exp2f(beta_x - mx) : INFINITY;
 
-    // ---- pass 2: e = exp2f(x - max), ordered denominator (sampling.cu:560-572) ---------------
+    // ---- pass 2: e = exp2f(x - max), ordered denominator (sampling.cu:560-572); min/max of e;
+    // elements with e >= beta_e are appended, in order, to this lane's candidate list -----------
     float acc = 0.f, emin = INFINITY, emax = -INFINITY;
+    int nc = 0, ns = 0;   // candidates, and those strictly above the bound
 #pragma unroll 2
     for (int s = 0; s < Kt; s++) {
         float4 v = row.ld(s);
@@ -234,107 +341,489 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         float em = 0.f;
         em += v.x; em += v.y; em += v.z; em += v.w;
         acc += em;
+        const float hi = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
         emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
-        emax = fmaxf(fmaxf(emax, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
-        row.st(s, v);
+        emax = fmaxf(emax, hi);
+        if (hi >= beta_e) {
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (e[j] >= beta_e) {
+                    if (nc < cap) cand_at(nc) = e[j];
+                    nc++;
+                    ns += (e[j] > beta_e) ? 1 : 0;
+                }
+            }
+        }
     }
+    stamp(4);   // pass 2 done
     acc = warp_tree_sum(acc);
     emin = warp_min(emin);
     emax = warp_max(emax);
-    post(make_uint4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), 0), make_uint4(0, 0, 0, 0));
+    const unsigned overflow = __any_sync(FULL, nc > cap) ? 1u : 0u;
+    const uint32_t wnc = __reduce_add_sync(FULL, (uint32_t)nc), wns = __reduce_add_sync(FULL, (uint32_t)ns);
+    post(make_uint4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow), make_uint4(wnc, wns, 0, 0));
     exchange_sync();
     mb = mbox + phase * 64;
     phase ^= 1;
     float denom;
+    bool cand_ok;
+    uint32_t ncand, nstrict;
     {
         const float4 e = mb[lane * 2];
         denom = warp_tree_sum(e.x);  // tree over the 32 warp partials (sampling.cu:29-33)
         emin = warp_min(e.y);
         emax = warp_max(e.z);
+        cand_ok = try_cand && (__reduce_add_sync(FULL, __float_as_uint(e.w)) == 0u);
+        ncand = __reduce_add_sync(FULL, reinterpret_cast<const uint4*>(mb)[lane * 2 + 1].x);
+        nstrict = __reduce_add_sync(FULL, reinterpret_cast<const uint4*>(mb)[lane * 2 + 1].y);
     }
-
-    // ---- pass 3: p = e / denom (sampling.cu:573-590); division is monotone, so the row's
-    // min/max probability are the quotients of the min/max numerators ---------------------------
+    // division is monotone, so the row's min/max probability are the quotients of min/max e
     const float pmin = emin / denom, pmax = emax / denom;
-    float* dprow = p.dbg_probs ? p.dbg_probs + (long long)b * V : nullptr;
-#pragma unroll 2
-    for (int s = 0; s < Kt; s++) {
-        float4 v = row.ld(s);
-        v.x = v.x / denom;
-        v.y = v.y / denom;
-        v.z = v.z / denom;
-        v.w = v.w / denom;
-        row.st(s, v);
-        if (dprow) reinterpret_cast<float4*>(dprow)[s * kLanes + tg] = v;
+    if (p.dbg_probs) {   // test instrumentation: the probabilities of the whole row
+        float* dprow = p.dbg_probs + (long long)b * V;
+        for (int s = 0; s < Kt; s++) {
+            float4 v = row.ld(s);
+            v.x = exp2f(v.x - mx) / denom;
+            v.y = exp2f(v.y - mx) / denom;
+            v.z = exp2f(v.z - mx) / denom;
+            v.w = exp2f(v.w - mx) / denom;
+            reinterpret_cast<float4*>(dprow)[s * kLanes + tg] = v;
+        }
     }
 
+    stamp(5);   // second exchange done
     // ---- cutoff search (sampling.cu:593-654, :829-878) ---------------------------------------
-    uint32_t left = __float_as_uint(pmin), right = __float_as_uint(pmax) + 1u;
-    uint32_t cnt_x = (uint32_t)V;
-    float mass_x = 1.0f;
-    int n = Kt * 4;                      // live elements of this lane's list
-    uint32_t list_total = (uint32_t)V;   // live elements over the whole row
-    uint32_t list_left = left;           // the list holds exactly the elements >= list_left
-    uint32_t rounds = 0;
     const uint32_t top_k = (uint32_t)p.top_k;
     const float top_p = p.top_p;
-    while (rounds < 64u) {
-        const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
-        if (!(go && left < right - 1u)) break;
-        rounds++;
-        const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
-        uint32_t cnt[3];
-        float mass[3];
-        const bool compact = (left != list_left) && (cnt_x * 2u <= list_total);
-        if (compact) {
-            search_pass<C, SMEM, true>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw),
-                                       __uint_as_float(left), cnt, mass);
-            list_total = cnt_x;
-            list_left = left;
+    uint32_t left = 0, right = 0, rounds = 0;
+    float gtp = 0.f;
+    uint32_t eqk = 0, gtk = 0;
+    uint32_t path = 1;
+
+    if (cand_ok) {
+        // ===== candidate path: the row's few candidates move to CTA 0, which finishes the call alone =====
+        // Every probability above beta_p = beta_e / denom is a candidate, so a pivot above beta_p sees
+        // exactly the elements the reference sees.  A pivot u <= beta_p is not evaluated; instead the
+        // set {p > beta_p} is (pivot u*, the next float after beta_p): if it already holds more than
+        // top_k elements or more than top_p mass, so does the larger set {p >= u}, hence the reference's
+        // test at u fails and its carried state keeps the loop going -- all it uses these values for.
+        const uint32_t beta_p = __float_as_uint(beta_e / denom);
+        // With more than top_k candidates strictly above the bound the replay cannot fail (the cutoff
+        // lies above the bound), so the other CTAs need not wait for its verdict.
+        const bool sure = use_cnt && (nstrict > top_k);
+        if (p.dbg_probs) exchange_sync();   // the dump above still read the stripes that now receive the table
+        // table in CTA 0's (now dead) stripes: count per lane, then values [entry][lane]
+        {
+            const uint32_t tab = map_to_cta(smem_addr(row.slab), 0u);
+            const int m = min(nc, cap);
+            if (C == 1) {
+                reinterpret_cast<uint32_t*>(row.slab)[tg] = (uint32_t)m;
+                for (int i = 0; i < m; i++) reinterpret_cast<float*>(row.slab)[kLanes * (1 + i) + tg] = cand_at(i) / denom;
+            } else {
+                st_cluster_u32(tab + 4u * tg, (uint32_t)m);
+                for (int i = 0; i < m; i++) st_cluster_u32(tab + 4u * (kLanes * (1 + i) + tg), __float_as_uint(cand_at(i) / denom));
+            }
+        }
+        if (C > 1) {
+            cluster_arrive();
+            if (crank != 0 && sure && !rep) return;   // nothing left to do for this CTA
+            cluster_wait();
         } else {
-            search_pass<C, SMEM, false>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw), 0.f, cnt,
-                                        mass);
+            __syncthreads();
         }
+        stamp(6);
+        bool valid = true;
+        int token = -1;
+        if (crank == 0) {
+            const uint32_t* tcnt = reinterpret_cast<const uint32_t*>(row.slab);
+            const float* tval = reinterpret_cast<const float*>(row.slab) + kLanes;
+            // CTA-local partials in the (now idle) mailbox area, two alternating buffers:
+            //   pm[buf][pivot 0..3][virtual warp 0..31] fp32 masses, pc[buf][physical warp] counts and bounds
+            float* pm = reinterpret_cast<float*>(mbox);                       // 2 * 128 floats
+            uint4* pc = reinterpret_cast<uint4*>(smem + kMboxOff + 1024);     // 2 * 32 entries
+            int tb = 0;
+            int nci[C];
+            int maxn = 0;
 #pragma unroll
-        for (int i = 0; i < 3; i++) {
-            cnt[i] = warp_sum_u32(cnt[i]);
-            mass[i] = warp_tree_sum(mass[i]);
+            for (int i = 0; i < C; i++) {
+                nci[i] = (int)tcnt[t + L * i];
+                maxn = max(maxn, nci[i]);
+            }
+            maxn = __reduce_max_sync(FULL, maxn);
+            // Totals over the row's 1024 virtual lanes for four pivots f[0..3], in the reference's order:
+            // per-lane chain in element order, xor tree over the 32 lanes of a virtual warp, warp totals
+            // added in warp order (sampling.cu:34-42).  The 4*C per-lane sums of a physical warp are
+            // tree-reduced together: at each butterfly level a lane keeps half of the sums and hands the
+            // other half to its partner, which performs exactly the additions of the plain butterfly
+            // (offsets 16, 8, 4, 2, 1) with 31 shuffles instead of 5 per sum.  Also returns the smallest and
+            // largest candidate bit pattern strictly inside (lo, hi).
+            auto eval = [&](const float (&f)[4], uint32_t lo, uint32_t hi, uint32_t oc[4], float om[4], uint32_t& vmin,
+                            uint32_t& vmax) {
+                uint32_t c01 = 0, c23 = 0;   // packed per-thread counts: (f0 | f1 << 16), (f2 | f3 << 16)
+                uint32_t mn = 0xffffffffu, mxv = 0u;
+                constexpr int NB = (C > 8) ? C / 8 : 1;   // batches of 8 virtual warps (32 sums) per tree pass
+                constexpr int NI = (C > 8) ? 8 : C;
+#pragma unroll
+                for (int bt = 0; bt < NB; bt++) {
+                    float v[32];
+#pragma unroll
+                    for (int k = 0; k < 32; k++) v[k] = 0.f;
+                    for (int j = 0; j < maxn; j++) {
+#pragma unroll
+                        for (int ii = 0; ii < NI; ii++) {
+                            const int i = bt * 8 + ii;
+                            if (j < nci[i]) {
+                                const float q = tval[j * kLanes + t + L * i];
+                                const uint32_t qb = __float_as_uint(q);
+                                if (q >= f[0]) { c01 += 1u; v[4 * ii] += q; }
+                                if (q >= f[1]) { c01 += 0x10000u; v[4 * ii + 1] += q; }
+                                if (q >= f[2]) { c23 += 1u; v[4 * ii + 2] += q; }
+                                if (q >= f[3]) { c23 += 0x10000u; v[4 * ii + 3] += q; }
+                                if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        const bool up = (lane & o) != 0;
+#pragma unroll
+                        for (int k = 0; k < o; k++) {
+                            const float keep = up ? v[k + o] : v[k];
+                            const float give = up ? v[k] : v[k + o];
+                            v[k] = keep + __shfl_xor_sync(FULL, give, o);
+                        }
+                    }
+                    // lane l now holds the tree total of sum index l = 4 * ii + pivot
+                    if (lane < 4 * NI) pm[tb * 128 + (lane & 3) * 32 + wl + WPC * (bt * 8 + (lane >> 2))] = v[0];
+                }
+                c01 = __reduce_add_sync(FULL, c01);
+                c23 = __reduce_add_sync(FULL, c23);
+                mn = __reduce_min_sync(FULL, mn);
+                mxv = __reduce_max_sync(FULL, mxv);
+                if (lane == 0) pc[tb * 32 + wl] = make_uint4(c01, c23, mn, mxv);
+                __syncthreads();
+                {
+                    const uint4 c4 = (lane < WPC) ? pc[tb * 32 + lane] : make_uint4(0u, 0u, 0xffffffffu, 0u);
+                    const uint32_t a = __reduce_add_sync(FULL, c4.x), bq = __reduce_add_sync(FULL, c4.y);
+                    vmin = __reduce_min_sync(FULL, c4.z);
+                    vmax = __reduce_max_sync(FULL, c4.w);
+                    oc[0] = a & 0xffffu; oc[1] = a >> 16; oc[2] = bq & 0xffffu; oc[3] = bq >> 16;
+                    float sacc = 0.f;
+                    if (lane < 4) {
+                        const float4* q4 = reinterpret_cast<const float4*>(pm + tb * 128 + lane * 32);
+                        float4 x4 = q4[0];
+                        sacc = x4.x; sacc += x4.y; sacc += x4.z; sacc += x4.w;
+#pragma unroll
+                        for (int w4 = 1; w4 < 8; w4++) {
+                            x4 = q4[w4];
+                            sacc += x4.x; sacc += x4.y; sacc += x4.z; sacc += x4.w;
+                        }
+                    }
+                    om[0] = __shfl_sync(FULL, sacc, 0);
+                    om[1] = __shfl_sync(FULL, sacc, 1);
+                    om[2] = __shfl_sync(FULL, sacc, 2);
+                    om[3] = __shfl_sync(FULL, sacc, 3);
+                }
+                tb ^= 1;
+            };
+            const uint32_t ustar = beta_p + 1u;
+            uint32_t n_eval = 0;
+            left = __float_as_uint(pmin);
+            right = __float_as_uint(pmax) + 1u;
+            uint32_t cnt_x = (uint32_t)V, cnt_r = 0u;   // counts at left / at right
+            float mass_x = 1.0f, mass_r = 0.f;
+            // Once every element strictly inside (left, right) has one and the same value v, the remaining
+            // rounds need no data: a pivot equal to `left` selects the set of `left`, a pivot in (left, v]
+            // the set {p >= v}, a pivot above v the set of `right`.  They are then replayed arithmetically.
+            bool frozen = false;
+            uint32_t v_bits = 0, cnt_v = 0;
+            float mass_v = 0.f;
+            while (rounds < 64u) {
+                const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
+                if (!(go && left < right - 1u)) break;
+                rounds++;
+                const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
+                const uint32_t pv[3] = {py, pz, pw};
+                uint32_t cnt[4];
+                float mass[4];
+                if (!frozen) {
+                    n_eval++;
+                    const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
+                                        __uint_as_float(max(pw, ustar)), __uint_as_float(max(left + 1u, ustar))};
+                    uint32_t vmin, vmax;
+                    eval(f, left, right, cnt, mass, vmin, vmax);
+                    if (left >= beta_p && (vmin >= vmax)) {   // one distinct value inside (or none: vmin > vmax)
+                        frozen = true;
+                        v_bits = (vmin == vmax) ? vmin : left;
+                        cnt_v = cnt[3];      // the set {p >= left + 1} is {p >= v}
+                        mass_v = mass[3];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 3; i++) {
+                        const bool at_left = (pv[i] == left), le_v = (pv[i] <= v_bits);
+                        cnt[i] = at_left ? cnt_x : le_v ? cnt_v : cnt_r;
+                        mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
+                    }
+                }
+                bool ok[3];
+#pragma unroll
+                for (int i = 0; i < 3; i++) {
+                    if (pv[i] <= beta_p) {
+                        ok[i] = false;
+                        if (!((use_cnt && cnt[i] > top_k) || mass[i] > top_p)) valid = false;
+                    } else {
+                        ok[i] = (use_cnt ? cnt[i] < top_k : true) && mass[i] < top_p;
+                    }
+                }
+                if (!valid) break;
+                if (ok[0]) { right = py; cnt_r = cnt[0]; mass_r = mass[0]; }
+                else if (ok[1]) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; cnt_r = cnt[1]; mass_r = mass[1]; }
+                else if (ok[2]) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; cnt_r = cnt[2]; mass_r = mass[2]; }
+                else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
+            }
+            stamp(9);   // replay rounds done
+            valid = valid && (left > beta_p);
+            if (valid) {
+                path = 0;
+                const bool early_exit = left < right - 1u;
+                const float thr = __uint_as_float(left);
+                // recount at the threshold (sampling.cu:657-680): elements above the threshold are those
+                // >= the next float; the three totals have the association of the search masses
+                uint32_t tc[4], d0, d1;
+                float tm[4];
+                const float fr[4] = {__uint_as_float(left + 1u), thr, INFINITY, INFINITY};
+                eval(fr, 0u, 0u, tc, tm, d0, d1);
+                const uint32_t sgtk = tc[0], seqk = tc[1] - tc[0];
+                const float sgtp = tm[0];
+                float comp = 1.0f;   // sampling.cu:690-696, :903-908
+                if (seqk > 0) {
+                    comp = fminf(sanitize((top_p - sgtp) / (thr * seqk)), comp);
+                    if (use_cnt) comp = fminf(sanitize(float(top_k - sgtk) / seqk), comp);
+                    comp = fmaxf(comp, 0.0f);
+                }
+                // lane pick (sampling.cu:699-723)
+                float incl[C];
+#pragma unroll
+                for (int i = 0; i < C; i++) {
+                    float g = 0.f;
+                    uint32_t e = 0;
+                    for (int j = 0; j < nci[i]; j++) {
+                        const float q = tval[j * kLanes + t + L * i];
+                        if (q == thr) e++;
+                        if (q > thr) g += q;
+                    }
+                    const float actual_p = g + (thr * e) * comp;
+                    incl[i] = warp_scan_desc(actual_p, lane);
+                    if (lane == 31) s_wtot[wl + WPC * i] = incl[i];
+                }
+                __syncthreads();
+                float pre_prev[C];
+#pragma unroll
+                for (int i = 0; i < C; i++) pre_prev[i] = 0.f;
+                float s0 = 0.f;
+                {
+#pragma unroll
+                    for (int w = 0; w < kWarps; w++) {
+                        s0 = (w == 0) ? s_wtot[0] : s0 + s_wtot[w];
+#pragma unroll
+                        for (int i = 0; i < C; i++)
+                            if (w == wl + WPC * i - 1) pre_prev[i] = s0;
+                    }
+                }
+                const float sum_p = s0;
+                const float randp = sum_p * ux;
+#pragma unroll
+                for (int i = 0; i < C; i++) {
+                    const int vw = wl + WPC * i;
+                    const float cumu_p = (vw > 0) ? incl[i] + pre_prev[i] : incl[i];
+                    const bool u = (randp <= cumu_p);
+                    bool u_prev = __shfl_up_sync(FULL, u, 1);
+                    if (lane == 0) u_prev = (vw > 0) ? (randp <= pre_prev[i]) : false;
+                    if (u != u_prev) *s_idxt = t + L * i;
+                }
+                if (t == 0) {  // advance the stored RNG state by one 4-word block
+                    const uint4 nctr = ctr_next(rng.ctr);
+                    uint4* st = reinterpret_cast<uint4*>(p.states + (long long)b * RS_STATE_BYTES);
+                    st[0] = nctr;
+                    st[1] = philox4x32_10(nctr, rng.key_pos.x, rng.key_pos.y);
+                }
+                __syncthreads();
+                stamp(7);
+                // element pick inside the chosen lane (sampling.cu:725-751)
+                const int idxt = *s_idxt;
+                float oincl[C];
+                int idn_of[C];
+#pragma unroll
+                for (int it = 0; it < C; it++) {
+                    const int vt = it * L + t;
+                    const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
+                    float o0 = 0.f;
+                    if (idn < V) {
+                        const float x = scaled_logit(lrow[idn], rep ? prow[idn] : 0.f, rep, p.scale);
+                        o0 = exp2f(x - mx) / denom;
+                    }
+                    const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
+                    oincl[it] = warp_scan_desc(o, lane);
+                    idn_of[it] = idn;
+                    if (lane == 31) s_wtot[vt >> 5] = oincl[it];
+                }
+                __syncthreads();
+                float opre[C];
+                s0 = 0.f;
+#pragma unroll
+                for (int it = 0; it < C; it++) opre[it] = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) {
+                    s0 = (w == 0) ? s_wtot[0] : s0 + s_wtot[w];
+#pragma unroll
+                    for (int it = 0; it < C; it++)
+                        if (w == it * WPC + wl - 1) opre[it] = s0;
+                }
+                const float sum_o = s0;
+                const float rand2 = sum_o * uy;
+#pragma unroll
+                for (int it = 0; it < C; it++) {
+                    const int vw = it * WPC + wl;
+                    const float cumu_o = (vw > 0) ? oincl[it] + opre[it] : oincl[it];
+                    const bool uo = (rand2 <= cumu_o);
+                    bool uo_prev = __shfl_up_sync(FULL, uo, 1);
+                    if (lane == 0) uo_prev = (vw > 0) ? (rand2 <= opre[it]) : false;
+                    if (uo != uo_prev) *s_token = (idn_of[it] < V) ? idn_of[it] : 0;
+                }
+                __syncthreads();
+                token = *s_token;
+                stamp(8);
+                if (t == 0) {
+                    p.out[b] = token;
+                    if (p.dbg_trace) {
+                        rs_trace tr;
+                        tr.maxu = mx; tr.denom = denom; tr.pmin = pmin; tr.pmax = pmax; tr.threshold = thr; tr.comp = comp;
+                        tr.sgtp = sgtp; tr.sum_p = sum_p; tr.randp = randp; tr.sum_o = sum_o; tr.rand2 = rand2;
+                        tr.left = left; tr.seqk = seqk; tr.sgtk = sgtk; tr.rounds = rounds; tr.idxt = (uint32_t)idxt;
+                        tr.early_exit = early_exit ? 1u : 0u;
+                        tr.rnd[0] = rnd4[0]; tr.rnd[1] = rnd4[1]; tr.rnd[2] = rnd4[2]; tr.rnd[3] = rnd4[3];
+                        tr.token = token;
+                        tr.path = 0;
+                        tr.ncand = ncand;
+#pragma unroll
+                        for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
+                        tr.t_ns[0] = n_eval;
+                        p.dbg_trace[b] = tr;
+                    }
+                }
+            } else if (sure && !rep) {
+                // cannot happen (see `sure`); the other CTAs are gone, so only report it
+                if (t == 0) { atomicExch(p.status, RS_ERR_INTERNAL); p.out[b] = 0; }
+            }
+            __syncthreads();   // all reads of the CTA-local partials are done before the mailbox is reused
         }
-        post(make_uint4(cnt[0], cnt[1], cnt[2], 0),
-             make_uint4(__float_as_uint(mass[0]), __float_as_uint(mass[1]), __float_as_uint(mass[2]), 0));
+        if (sure && !rep) return;
+        // verdict (and the sampled id, which the penalty update needs) to every CTA
+        post(make_uint4(valid ? 1u : 0u, (uint32_t)token, 0, 0), make_uint4(0, 0, 0, 0));
         exchange_sync();
         mb = mbox + phase * 64;
         phase ^= 1;
         {
-            const uint4 c4 = reinterpret_cast<const uint4*>(mb)[lane * 2];
-            cnt[0] = warp_sum_u32(c4.x);
-            cnt[1] = warp_sum_u32(c4.y);
-            cnt[2] = warp_sum_u32(c4.z);
-            // thread 0 of the reference adds the 32 warp values in order (sampling.cu:34-42)
-            float4 m4 = mb[1];
-            float s0 = m4.x, s1 = m4.y, s2 = m4.z;
-#pragma unroll
-            for (int w = 1; w < kWarps; w++) {
-                m4 = mb[w * 2 + 1];
-                s0 += m4.x; s1 += m4.y; s2 += m4.z;
-            }
-            mass[0] = s0; mass[1] = s1; mass[2] = s2;
+            const uint4 r = reinterpret_cast<const uint4*>(mb)[0];   // CTA 0's first warp is virtual warp 0
+            valid = (r.x != 0u);
+            token = (int)r.y;
         }
-        const bool ok0 = (use_cnt ? cnt[0] < top_k : true) && mass[0] < top_p;
-        const bool ok1 = (use_cnt ? cnt[1] < top_k : true) && mass[1] < top_p;
-        const bool ok2 = (use_cnt ? cnt[2] < top_k : true) && mass[2] < top_p;
-        if (ok0) { right = py; }
-        else if (ok1) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; }
-        else if (ok2) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; }
-        else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
+        if (valid) {
+            if (rep) {   // sampling.cu:427-437
+#pragma unroll 2
+                for (int s = 0; s < Kt; s++) {
+                    const int i4 = s * kLanes + tg;
+                    float4 q4 = reinterpret_cast<float4*>(prow)[i4];
+                    float e[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float old = e[j];
+                        e[j] = fmaf(old, p.decay, (i4 * 4 + j != token) ? 0.f : (old == 0.f ? p.presence : p.repetition));
+                    }
+                    reinterpret_cast<float4*>(prow)[i4] = make_float4(e[0], e[1], e[2], e[3]);
+                }
+            }
+            return;
+        }
+        // The candidates did not settle the cutoff (too little mass above the bound): bring the row back
+        // (CTA 0's stripes held the table) and fall through to the whole-row search.
+        rounds = 0;
+        if (SMEM) {
+            if (wl == 0) {
+                const int kfull = V4 >> 10, rem = V4 & 1023;
+                const int vl = min(max(rem - (int)crank * L, 0), L);
+                const uint32_t bar = smem_addr(mbar);
+                if (lane == 0) mbar_expect_tx(bar, (uint32_t)(kfull * L + vl) * 16u);
+                __syncwarp();
+                const float4* src = reinterpret_cast<const float4*>(lrow) + crank * L;
+                const uint32_t dst = smem_addr(row.slab);
+                for (int k = lane; k < kfull; k += 32) bulk_g2s(dst + k * L * 16, src + k * kLanes, L * 16, bar);
+                if (lane == 0 && vl > 0) bulk_g2s(dst + kfull * L * 16, src + kfull * kLanes, vl * 16, bar);
+            }
+            if (!mbar_wait_bounded(smem_addr(mbar), 1, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
+            for (int s = 0; s < Kt; s++) {
+                float4 v = row.ld(s);
+                float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (rep) q4 = reinterpret_cast<const float4*>(prow)[s * kLanes + tg];
+                v.x = scaled_logit(v.x, q4.x, rep, p.scale);
+                v.y = scaled_logit(v.y, q4.y, rep, p.scale);
+                v.z = scaled_logit(v.z, q4.z, rep, p.scale);
+                v.w = scaled_logit(v.w, q4.w, rep, p.scale);
+                row.st(s, v);
+            }
+        }
     }
-    const bool early_exit = left < right - 1u;
-    const float thr = __uint_as_float(left);
 
-    // ---- recount at the threshold (sampling.cu:657-680) --------------------------------------
-    float gtp = 0.f;
-    uint32_t eqk = 0, gtk = 0;
+    // ===== whole-row path: every CTA searches its own stripes; partials meet in the mailboxes =====
     {
+        // pass 3: p = exp2f(x - max) / denom (sampling.cu:573-590), in place.
+#pragma unroll 2
+        for (int s = 0; s < Kt; s++) {
+            float4 v = row.ld(s);
+            v.x = exp2f(v.x - mx) / denom;
+            v.y = exp2f(v.y - mx) / denom;
+            v.z = exp2f(v.z - mx) / denom;
+            v.w = exp2f(v.w - mx) / denom;
+            row.st(s, v);
+        }
+        left = __float_as_uint(pmin);
+        right = __float_as_uint(pmax) + 1u;
+        rounds = 0;
+        uint32_t cnt_x = (uint32_t)V;
+        float mass_x = 1.0f;
+        int n = Kt * 4;                      // live elements of this lane's list
+        uint32_t list_total = (uint32_t)V;   // live elements over the whole row
+        uint32_t list_left = left;           // the list holds exactly the elements >= list_left
+        while (rounds < 64u) {
+            const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
+            if (!(go && left < right - 1u)) break;
+            rounds++;
+            const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
+            uint32_t cnt[3];
+            float mass[3];
+            const bool compact = (left != list_left) && (cnt_x * 2u <= list_total);
+            if (compact) {
+                search_pass<C, SMEM, true>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw),
+                                           __uint_as_float(left), cnt, mass);
+                list_total = cnt_x;
+                list_left = left;
+            } else {
+                search_pass<C, SMEM, false>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw), 0.f,
+                                            cnt, mass);
+            }
+            combine_round(cnt, mass);
+            const bool ok0 = (use_cnt ? cnt[0] < top_k : true) && mass[0] < top_p;
+            const bool ok1 = (use_cnt ? cnt[1] < top_k : true) && mass[1] < top_p;
+            const bool ok2 = (use_cnt ? cnt[2] < top_k : true) && mass[2] < top_p;
+            if (ok0) { right = py; }
+            else if (ok1) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; }
+            else if (ok2) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; }
+            else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
+        }
+        // recount at the threshold (sampling.cu:657-680)
+        const float thr = __uint_as_float(left);
         const int slots = (n + 3) >> 2;
 #pragma unroll 2
         for (int s = 0; s < slots; s++) {
@@ -347,11 +836,15 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             }
         }
     }
+    stamp(6);   // search and recount done
+    const bool early_exit = left < right - 1u;
+    const float thr = __uint_as_float(left);
+
     // The reference takes the three totals from block scans; lane 31 of a descending-offset scan
     // holds the same tree value as the butterfly, and the warp values are then added in order.
     {
         const float wsum = warp_tree_sum(gtp);
-        const uint32_t weq = warp_sum_u32(eqk), wgt = warp_sum_u32(gtk);
+        const uint32_t weq = __reduce_add_sync(FULL, eqk), wgt = __reduce_add_sync(FULL, gtk);
         post(make_uint4(__float_as_uint(wsum), weq, wgt, 0), make_uint4(0, 0, 0, 0));
     }
     exchange_sync();
@@ -361,8 +854,8 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     uint32_t seqk, sgtk;
     {
         const uint4 c4 = reinterpret_cast<const uint4*>(mb)[lane * 2];
-        seqk = warp_sum_u32(c4.y);
-        sgtk = warp_sum_u32(c4.z);
+        seqk = __reduce_add_sync(FULL, c4.y);
+        sgtk = __reduce_add_sync(FULL, c4.z);
         float s0 = mb[0].x;
 #pragma unroll
         for (int w = 1; w < kWarps; w++) s0 += mb[w * 2].x;
@@ -381,7 +874,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     const float actual_p = gtp + (thr * eqk) * comp;
     const float incl = warp_scan_desc(actual_p, lane);
     {
-        const float wt = __shfl_sync(0xffffffffu, incl, 31);
+        const float wt = __shfl_sync(FULL, incl, 31);
         post(make_uint4(__float_as_uint(wt), 0, 0, 0), make_uint4(0, 0, 0, 0));
     }
     exchange_sync();
@@ -405,9 +898,10 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             if (w == wg - 1) pre_prev = pre[w];
         }
     }
+    stamp(7);   // totals and lane-pick exchanges done
     const float cumu_p = (wg > 0) ? incl + pre_prev : incl;
     bool u = (randp <= cumu_p);
-    bool u_prev = __shfl_up_sync(0xffffffffu, u, 1);
+    bool u_prev = __shfl_up_sync(FULL, u, 1);
     if (lane == 0) u_prev = (wg > 0) ? (randp <= pre_prev) : false;
     // Exactly one lane sees the 0 -> 1 transition (the scan is non-decreasing); with no
     // transition at all the reference keeps its initial value, lane 0.
@@ -462,12 +956,13 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             const int vw = it * WPC + wl;
             const float cumu_o = (vw > 0) ? oincl[it] + opre[it] : oincl[it];
             const bool uo = (rand2 <= cumu_o);
-            bool uo_prev = __shfl_up_sync(0xffffffffu, uo, 1);
+            bool uo_prev = __shfl_up_sync(FULL, uo, 1);
             if (lane == 0) uo_prev = (vw > 0) ? (rand2 <= opre[it]) : false;
             if (uo != uo_prev) *s_token = (idn_of[it] < V) ? idn_of[it] : 0;
         }
         __syncthreads();
         token = *s_token;
+        stamp(8);   // element pick done
         if (t == 0) {
             p.out[b] = token;
             if (p.dbg_trace) {
@@ -478,6 +973,10 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
                 tr.early_exit = early_exit ? 1u : 0u;
                 tr.rnd[0] = rnd4[0]; tr.rnd[1] = rnd4[1]; tr.rnd[2] = rnd4[2]; tr.rnd[3] = rnd4[3];
                 tr.token = token;
+                tr.path = path;
+                tr.ncand = ncand;
+#pragma unroll
+                for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
                 p.dbg_trace[b] = tr;
             }
         }
@@ -524,6 +1023,7 @@ static DeviceInfo g_dev[64];
 static std::mutex g_mu;
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_cluster_override{0};
+static std::atomic<int> g_path_override{0};
 static thread_local char g_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -584,12 +1084,38 @@ static int get_device(DeviceInfo** out) {
     return RS_OK;
 }
 
+// Rank of the per-warp thread maximum used as the lower bound of the candidate shortcut, and the
+// candidate buffer's float4 slots per lane.  With rank j every warp holds >= j elements above the
+// bound, 32*j in the row: enough to exceed top_k.  Without a usable top_k the loosest bound (the
+// smallest thread maximum) is tried and the kernel checks the mass condition itself.
+static void choose_candidates(long long V, long long top_k, double top_p, int* sel_rank, int* cand_slots) {
+    *sel_rank = 0;
+    *cand_slots = 0;
+    if (g_path_override.load() == 1) return;
+    if (top_k >= V && top_p >= 1.0) return;            // nothing is filtered: the whole row is kept
+    // Beyond top_k ~ 250 the candidate table would outgrow a CTA's stripes; such calls search the whole row.
+    if (top_k < V) {
+        if (top_k + 2 > 256) return;
+        *sel_rank = (int)((top_k + 2 + 31) / 32);
+    } else {
+        *sel_rank = 2;                                  // top-p only: try the ~200 largest; the kernel checks their mass
+    }
+    *cand_slots = (*sel_rank <= 4) ? 2 : 4;
+}
+
+// stripes of one CTA; with candidates they must also be able to hold CTA 0's table (count + entries per lane)
+static int smem_need(int V, int C, int cand_slots) {
+    const int table = cand_slots ? 4 * kLanes * (1 + 4 * cand_slots) : 0;
+    const int slab = slab_bytes(V, C);
+    return kSlabOff + cand_slots * (kLanes / C) * 16 + (slab > table ? slab : table);
+}
+
 // Cluster width per row.  Small batches want the widest portable cluster (each of the 32
 // virtual warps gets a scheduler of its own at 8 CTAs); large batches want as many rows
 // resident as shared memory allows so that one row's load overlaps another row's search.
-static int choose_cluster(const DeviceInfo& di, long long B, int V, bool* use_smem) {
+static int choose_cluster(const DeviceInfo& di, long long B, int V, int cand_slots, bool* use_smem) {
     const int forced = g_cluster_override.load();
-    auto fits = [&](int C) { return kSlabOff + slab_bytes(V, C) <= di.smem_optin; };
+    auto fits = [&](int C) { return smem_need(V, C, cand_slots) <= di.smem_optin; };
     *use_smem = true;
     if (forced) {
         if (fits(forced)) return forced;
@@ -597,7 +1123,7 @@ static int choose_cluster(const DeviceInfo& di, long long B, int V, bool* use_sm
         return 8;
     }
     auto resident_rows = [&](int C) {
-        const int need = kSlabOff + slab_bytes(V, C) + 1024;
+        const int need = smem_need(V, C, cand_slots) + 1024;
         int per_sm = di.smem_sm / need;
         per_sm = per_sm < 2048 / (kLanes / C) ? per_sm : 2048 / (kLanes / C);
         if (per_sm > 32) per_sm = 32;
@@ -639,7 +1165,15 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     int rc = get_device(&di);
     if (rc) return rc;
     bool use_smem = true;
-    const int C = choose_cluster(*di, B, (int)V, &use_smem);
+    int sel_rank = 0, cand_slots = 0;
+    choose_candidates(V, top_k, top_p, &sel_rank, &cand_slots);
+    int C = choose_cluster(*di, B, (int)V, cand_slots, &use_smem);
+    if (!use_smem && cand_slots) {   // the candidate buffer must never push a row off the chip
+        sel_rank = cand_slots = 0;
+        use_smem = true;
+        C = choose_cluster(*di, B, (int)V, 0, &use_smem);
+    }
+    if (!use_smem) sel_rank = cand_slots = 0;
     if (workspace_bytes < (use_smem ? (size_t)256 : ws_bytes(B, V))) return RS_ERR_WORKSPACE;
 
     Params p;
@@ -661,10 +1195,12 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     p.presence = (float)presence;
     p.repetition = (float)repetition;
     p.decay = (float)decay;
+    p.sel_rank = sel_rank;
+    p.cand_slots = cand_slots;
 
     cudaStream_t st = (cudaStream_t)stream;
     if (!use_smem) return launch_one<8, false>(p, kSlabOff, st, *di);
-    const int smem = kSlabOff + slab_bytes((int)V, C);
+    const int smem = smem_need((int)V, C, cand_slots);
     switch (C) {
         case 1: return launch_one<1, true>(p, smem, st, *di);
         case 2: return launch_one<2, true>(p, smem, st, *di);
@@ -745,6 +1281,8 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     p.presence = (float)presence;
     p.repetition = (float)repetition;
     p.decay = (float)decay;
+    p.sel_rank = 0;
+    p.cand_slots = 0;
     return launch_one<8, false>(p, kSlabOff, (cudaStream_t)stream, *di);
 }
 
@@ -831,6 +1369,10 @@ int rs_set_cluster_override(int cluster_ctas) {
     return valid ? rs::g_cluster_override.exchange(cluster_ctas) : rs::g_cluster_override.load();
 }
 
+int rs_set_path_override(int mode) {
+    return (mode == 0 || mode == 1) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
+}
+
 uint64_t rs_kernel_launch_count(void) { return rs::g_launches.load(); }
 
 const char* rs_status_string(int status) {
@@ -845,6 +1387,7 @@ const char* rs_status_string(int status) {
         case RS_ERR_CUDA: return "CUDA runtime error";
         case RS_ERR_TIMEOUT: return "a bounded on-chip wait gave up";
         case RS_ERR_LIMIT: return "size beyond what this entry point supports";
+        case RS_ERR_INTERNAL: return "an invariant of the cutoff search was violated";
     }
     return "unknown status";
 }

@@ -115,6 +115,9 @@ class Abi:
     def set_cluster(self, c):
         return self.L.rs_set_cluster_override(c)
 
+    def set_path(self, mode):
+        return self.L.rs_set_path_override(mode)
+
 
 def kept_set_flips_ok(kept32, d, b, mass_tol=1e-6, tie_tol=4e-6):
     """True when every token whose membership differs between the fp32 kept set and the float64

@@ -62,13 +62,41 @@ def test_setup_rand_bytes_equal_reference_and_oracle(abi, ref):
 def test_ids_and_states_bit_identical_to_reference_kernel(abi, ref, kind, B, V, temp, k, p, seed):
     abi.set_cluster(0)
     lg = make_logits(kind, B, V, seed, torch).cuda()
-    s_ref, s_our = ref.setup_rand(seed, B), abi.setup_rand(seed, B)
-    for call in range(3):                      # consecutive calls advance the states
-        want = _ref_call(ref, lg, s_ref, temp, k, p)
-        got = abi.sample(lg, s_our, temp, k, p)
-        assert torch.equal(got, want), (call, (got != want).nonzero()[:5])
-        assert torch.equal(s_our, s_ref)
+    try:
+        for mode in (0, 1):                        # candidate shortcut (with fallback) / whole-row search only
+            abi.set_path(mode)
+            s_ref, s_our = ref.setup_rand(seed, B), abi.setup_rand(seed, B)
+            for call in range(3):                  # consecutive calls advance the states
+                want = _ref_call(ref, lg, s_ref, temp, k, p)
+                got = abi.sample(lg, s_our, temp, k, p)
+                assert torch.equal(got, want), (mode, call, (got != want).nonzero()[:5])
+                assert torch.equal(s_our, s_ref)
+    finally:
+        abi.set_path(0)
     assert abi.device_status() == 0
+
+
+def test_both_search_strategies_are_exercised(abi):
+    """Peaked / top-k rows must resolve on the candidate list; flat rows (kept set = a third of the row)
+    cannot and must fall back to the whole-row search.  Same ids either way."""
+    cases = [("peaked", 16, 151936, 0.8, 50, 0.9, 0), ("normal3", 16, 65536, 0.8, 50, 0.9, 0),
+             ("normal3", 4, 262144, 1.0, -1, 0.3, 0), ("uniform", 4, 131072, 1.0, -1, 0.5, 1),
+             ("uniform", 4, 32768, 1.0, -1, 1.0, 1), ("equal", 4, 8192, 0.7, 100, 0.25, 1)]
+    for kind, B, V, temp, k, p, want_path in cases:
+        lg = make_logits(kind, B, V, 3, torch).cuda()
+        out_a, _, tr = abi.sample(lg, abi.setup_rand(3, B), temp, k, p, debug=True)
+        assert all(t.path == want_path for t in tr), (kind, [t.path for t in tr])
+        if want_path == 0:
+            assert all(0 < t.ncand < V // 8 for t in tr), (kind, [t.ncand for t in tr])
+        try:
+            abi.set_path(1)
+            out_b, _, tr_b = abi.sample(lg, abi.setup_rand(3, B), temp, k, p, debug=True)
+        finally:
+            abi.set_path(0)
+        assert torch.equal(out_a, out_b)
+        for x, y in zip(tr, tr_b):
+            assert y.path == 1 and x.left == y.left and x.rounds == y.rounds and x.idxt == y.idxt
+            assert x.sum_p == y.sum_p and x.comp == y.comp and x.seqk == y.seqk and x.sgtk == y.sgtk
 
 
 @pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
