@@ -71,13 +71,15 @@ __device__ __forceinline__ float scaled_logit(float l, float pen, bool rep, floa
     return rep ? sanitize((sanitize(l) - pen) * scale) : sanitize(l * scale);
 }
 
-// One search pass over this lane's list in the slab: counts and ordered masses at three pivots;
-// optionally keeps only elements >= keepf (in place, order preserved, tail padded with -1).
+// One search pass over this lane's list in the slab: ordered masses and counts at three pivots
+// (f[3] is ignored here); optionally keeps only elements >= keepf (in place, order preserved, tail
+// padded with -1).  Counts are returned packed: c01 = n(f0) | n(f1) << 16, c23 = n(f2).
 template <int C, bool SMEM, bool COMPACT>
-__device__ __forceinline__ void search_pass(const Row<C, SMEM>& row, int& n, float py, float pz, float pw, float keepf,
-                                            uint32_t cnt[3], float mass[3]) {
+__device__ __forceinline__ void slab_pass(const Row<C, SMEM>& row, int& n, const float (&f)[4], float keepf, float (&m)[4],
+                                          uint32_t& c01, uint32_t& c23) {
     uint32_t cy = 0, cz = 0, cw = 0;
     float my = 0.f, mz = 0.f, mw = 0.f;
+    const float py = f[0], pz = f[1], pw = f[2];
     const int slots = (n + 3) >> 2;
     float b0 = -1.f, b1 = -1.f, b2 = -1.f, b3 = -1.f;
     int q = 0;
@@ -93,11 +95,11 @@ __device__ __forceinline__ void search_pass(const Row<C, SMEM>& row, int& n, flo
             if (p >= pw) { cw++; mw += p; }
             if (COMPACT) {
                 if (p >= keepf) {
-                    const int m = q & 3;
-                    b0 = (m == 0) ? p : b0;
-                    b1 = (m == 1) ? p : b1;
-                    b2 = (m == 2) ? p : b2;
-                    b3 = (m == 3) ? p : b3;
+                    const int k = q & 3;
+                    b0 = (k == 0) ? p : b0;
+                    b1 = (k == 1) ? p : b1;
+                    b2 = (k == 2) ? p : b2;
+                    b3 = (k == 3) ? p : b3;
                     q++;
                     if ((q & 3) == 0) {
                         row.st((q >> 2) - 1, make_float4(b0, b1, b2, b3));
@@ -111,8 +113,9 @@ __device__ __forceinline__ void search_pass(const Row<C, SMEM>& row, int& n, flo
         if (q & 3) row.st(q >> 2, make_float4(b0, b1, b2, b3));
         n = q;
     }
-    cnt[0] = cy; cnt[1] = cz; cnt[2] = cw;
-    mass[0] = my; mass[1] = mz; mass[2] = mw;
+    m[0] = my; m[1] = mz; m[2] = mw; m[3] = 0.f;
+    c01 = cy | (cz << 16);
+    c23 = cw;
 }
 
 // Sanitised scaled logit with the common case (finite product) kept to a multiply and a compare.
@@ -143,7 +146,6 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + kMiscOff);
     int* s_idxt = reinterpret_cast<int*>(smem + kMiscOff + 8);
     int* s_token = reinterpret_cast<int*>(smem + kMiscOff + 12);
-    uint32_t* s_res = reinterpret_cast<uint32_t*>(smem + kMiscOff + 32);   // 8 words: combined round result
     float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
     Row<C, SMEM> row;
     row.slab = SMEM ? reinterpret_cast<float4*>(smem + kSlabOff + p.cand_slots * L * 16)
@@ -191,41 +193,41 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     for (int i = 0; i < 10; i++) ts[i] = 0;
     stamp(0);
 
-    // One search round's reduction: warp partials -> mailboxes -> one warp per CTA combines the 32
-    // entries (counts exactly; masses in warp order 0..31, as thread 0 of the reference does,
-    // sampling.cu:34-42) and hands the six totals to the other warps through shared memory.
-    auto combine_round = [&](uint32_t cnt[3], float mass[3]) {
-#pragma unroll
-        for (int i = 0; i < 3; i++) {
-            cnt[i] = __reduce_add_sync(FULL, cnt[i]);
-            mass[i] = warp_tree_sum(mass[i]);
-        }
-        post(make_uint4(cnt[0], cnt[1], cnt[2], 0),
-             make_uint4(__float_as_uint(mass[0]), __float_as_uint(mass[1]), __float_as_uint(mass[2]), 0));
+    // Row totals of four ordered masses and four counts (packed per lane as c01 = n0 | n1 << 16,
+    // c23 = n2 | n3 << 16; a lane holds at most 1024 elements), plus min / max of two bit patterns.
+    // Order of the masses: xor tree over the 32 lanes of a warp, then the 32 warp values added in warp
+    // order, as thread 0 of the reference does (sampling.cu:34-42).  Every warp of every CTA combines the
+    // 32 mailbox entries itself (lanes 0..3 run the four 32-step chains), so no second barrier is needed.
+    auto totals = [&](const float (&m)[4], uint32_t c01, uint32_t c23, uint32_t mn, uint32_t mxv, uint32_t (&cnt)[4],
+                      float (&mass)[4], uint32_t& vmin, uint32_t& vmax) {
+        const float t0 = warp_tree_sum(m[0]), t1 = warp_tree_sum(m[1]), t2 = warp_tree_sum(m[2]), t3 = warp_tree_sum(m[3]);
+        c01 = __reduce_add_sync(FULL, c01);
+        c23 = __reduce_add_sync(FULL, c23);
+        mn = __reduce_min_sync(FULL, mn);
+        mxv = __reduce_max_sync(FULL, mxv);
+        post(make_uint4(__float_as_uint(t0), __float_as_uint(t1), __float_as_uint(t2), __float_as_uint(t3)),
+             make_uint4(c01, c23, mn, mxv));
         exchange_sync();
-        const float4* m = mbox + phase * 64;
+        const float4* q = mbox + phase * 64;
         phase ^= 1;
-        if (wl == 0) {
-            const uint4 c4 = reinterpret_cast<const uint4*>(m)[lane * 2];
-            const uint32_t c0 = __reduce_add_sync(FULL, c4.x), c1 = __reduce_add_sync(FULL, c4.y),
-                           c2 = __reduce_add_sync(FULL, c4.z);
-            float4 m4 = m[1];
-            float s0 = m4.x, s1 = m4.y, s2 = m4.z;
+        const uint4 e = reinterpret_cast<const uint4*>(q)[lane * 2 + 1];
+        cnt[0] = __reduce_add_sync(FULL, e.x & 0xffffu);
+        cnt[1] = __reduce_add_sync(FULL, e.x >> 16);
+        cnt[2] = __reduce_add_sync(FULL, e.y & 0xffffu);
+        cnt[3] = __reduce_add_sync(FULL, e.y >> 16);
+        vmin = __reduce_min_sync(FULL, e.z);
+        vmax = __reduce_max_sync(FULL, e.w);
+        float sacc = 0.f;
+        if (lane < 4) {
+            const float* col = reinterpret_cast<const float*>(q) + lane;
+            sacc = col[0];
 #pragma unroll
-            for (int w = 1; w < kWarps; w++) {
-                m4 = m[w * 2 + 1];
-                s0 += m4.x; s1 += m4.y; s2 += m4.z;
-            }
-            if (lane == 0) {
-                reinterpret_cast<uint4*>(s_res)[0] = make_uint4(c0, c1, c2, 0);
-                reinterpret_cast<float4*>(s_res)[1] = make_float4(s0, s1, s2, 0.f);
-            }
+            for (int w = 1; w < kWarps; w++) sacc += col[w * 8];
         }
-        __syncthreads();
-        const uint4 rc = reinterpret_cast<const uint4*>(s_res)[0];
-        const float4 rm = reinterpret_cast<const float4*>(s_res)[1];
-        cnt[0] = rc.x; cnt[1] = rc.y; cnt[2] = rc.z;
-        mass[0] = rm.x; mass[1] = rm.y; mass[2] = rm.z;
+        mass[0] = __shfl_sync(FULL, sacc, 0);
+        mass[1] = __shfl_sync(FULL, sacc, 1);
+        mass[2] = __shfl_sync(FULL, sacc, 2);
+        mass[3] = __shfl_sync(FULL, sacc, 3);
     };
 
     // ---- load: bulk async copies of this CTA's stripes; RNG state read meanwhile -------------
@@ -272,10 +274,10 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // thread's own maximum, from which a lower bound for the cutoff is derived below -------------
     float tmax = -INFINITY;
     if (rep) {
-#pragma unroll 2
+#pragma unroll 8
         for (int s = 0; s < Kt; s++) {
             float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
-            const float4 q4 = reinterpret_cast<const float4*>(prow)[s * kLanes + tg];
+            const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
             v.x = scaled_logit(v.x, q4.x, true, p.scale);
             v.y = scaled_logit(v.y, q4.y, true, p.scale);
             v.z = scaled_logit(v.z, q4.z, true, p.scale);
@@ -396,389 +398,116 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // ---- cutoff search (sampling.cu:593-654, :829-878) ---------------------------------------
     const uint32_t top_k = (uint32_t)p.top_k;
     const float top_p = p.top_p;
-    uint32_t left = 0, right = 0, rounds = 0;
-    float gtp = 0.f;
-    uint32_t eqk = 0, gtk = 0;
+    uint32_t left = 0, right = 0, rounds = 0, n_eval = 0;
     uint32_t path = 1;
 
-    if (cand_ok) {
-        // ===== candidate path: the row's few candidates move to CTA 0, which finishes the call alone =====
-        // Every probability above beta_p = beta_e / denom is a candidate, so a pivot above beta_p sees
-        // exactly the elements the reference sees.  A pivot u <= beta_p is not evaluated; instead the
-        // set {p > beta_p} is (pivot u*, the next float after beta_p): if it already holds more than
-        // top_k elements or more than top_p mass, so does the larger set {p >= u}, hence the reference's
-        // test at u fails and its carried state keeps the loop going -- all it uses these values for.
-        const uint32_t beta_p = __float_as_uint(beta_e / denom);
-        // With more than top_k candidates strictly above the bound the replay cannot fail (the cutoff
-        // lies above the bound), so the other CTAs need not wait for its verdict.
-        const bool sure = use_cnt && (nstrict > top_k);
-        if (p.dbg_probs) exchange_sync();   // the dump above still read the stripes that now receive the table
-        // table in CTA 0's (now dead) stripes: count per lane, then values [entry][lane]
-        {
-            const uint32_t tab = map_to_cta(smem_addr(row.slab), 0u);
-            const int m = min(nc, cap);
-            if (C == 1) {
-                reinterpret_cast<uint32_t*>(row.slab)[tg] = (uint32_t)m;
-                for (int i = 0; i < m; i++) reinterpret_cast<float*>(row.slab)[kLanes * (1 + i) + tg] = cand_at(i) / denom;
+    // The reference's loop, replayed with the same pivots and the same decisions.  `lane_eval` returns this
+    // lane's ordered masses / counts for four pivots over whatever list the caller searches.
+    //  * clamp (candidate list only): every probability above beta_p is on the list, so a pivot above beta_p
+    //    sees exactly the elements the reference sees.  A pivot u <= beta_p is not evaluated; instead the set
+    //    {p > beta_p} is (pivot u*, the next float after beta_p): if it already holds more than top_k elements
+    //    or more than top_p mass, so does the larger set {p >= u}, hence the reference's test at u fails and
+    //    its carried state keeps the loop going -- all it uses these values for.  Otherwise: not valid.
+    //  * bounds (candidate list only): once every element strictly inside (left, right) has one and the same
+    //    value v, the remaining rounds need no data: a pivot equal to `left` selects the set of `left`, a pivot
+    //    in (left, v] the set {p >= v}, a pivot above v the set of `right`; they are replayed arithmetically.
+    auto run_search = [&](auto&& lane_eval, const bool clamp, const uint32_t beta_p) -> bool {
+        const uint32_t ustar = clamp ? beta_p + 1u : 0u;
+        left = __float_as_uint(pmin);
+        right = __float_as_uint(pmax) + 1u;
+        rounds = 0;
+        uint32_t cnt_x = (uint32_t)V, cnt_r = 0u;   // counts at left / at right
+        float mass_x = 1.0f, mass_r = 0.f;
+        bool frozen = false, valid = true;
+        uint32_t v_bits = 0, cnt_v = 0;
+        float mass_v = 0.f;
+        while (rounds < 64u) {
+            const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
+            if (!(go && left < right - 1u)) break;
+            rounds++;
+            const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
+            const uint32_t pv[3] = {py, pz, pw};
+            uint32_t cnt[4];
+            float mass[4];
+            if (!frozen) {
+                n_eval++;
+                const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
+                                    __uint_as_float(max(pw, ustar)), __uint_as_float(max(left + 1u, ustar))};
+                float m[4];
+                uint32_t c01, c23, mn, mxv, vmin, vmax;
+                lane_eval(f, left, right, cnt_x, m, c01, c23, mn, mxv);
+                totals(m, c01, c23, mn, mxv, cnt, mass, vmin, vmax);
+                if (clamp && left >= beta_p && vmin >= vmax) {   // one distinct value inside (none: vmin > vmax)
+                    frozen = true;
+                    v_bits = (vmin == vmax) ? vmin : left;
+                    cnt_v = cnt[3];      // the set {p >= left + 1} is {p >= v}
+                    mass_v = mass[3];
+                }
             } else {
-                st_cluster_u32(tab + 4u * tg, (uint32_t)m);
-                for (int i = 0; i < m; i++) st_cluster_u32(tab + 4u * (kLanes * (1 + i) + tg), __float_as_uint(cand_at(i) / denom));
-            }
-        }
-        if (C > 1) {
-            cluster_arrive();
-            if (crank != 0 && sure && !rep) return;   // nothing left to do for this CTA
-            cluster_wait();
-        } else {
-            __syncthreads();
-        }
-        stamp(6);
-        bool valid = true;
-        int token = -1;
-        if (crank == 0) {
-            const uint32_t* tcnt = reinterpret_cast<const uint32_t*>(row.slab);
-            const float* tval = reinterpret_cast<const float*>(row.slab) + kLanes;
-            // CTA-local partials in the (now idle) mailbox area, two alternating buffers:
-            //   pm[buf][pivot 0..3][virtual warp 0..31] fp32 masses, pc[buf][physical warp] counts and bounds
-            float* pm = reinterpret_cast<float*>(mbox);                       // 2 * 128 floats
-            uint4* pc = reinterpret_cast<uint4*>(smem + kMboxOff + 1024);     // 2 * 32 entries
-            int tb = 0;
-            int nci[C];
-            int maxn = 0;
-#pragma unroll
-            for (int i = 0; i < C; i++) {
-                nci[i] = (int)tcnt[t + L * i];
-                maxn = max(maxn, nci[i]);
-            }
-            maxn = __reduce_max_sync(FULL, maxn);
-            // Totals over the row's 1024 virtual lanes for four pivots f[0..3], in the reference's order:
-            // per-lane chain in element order, xor tree over the 32 lanes of a virtual warp, warp totals
-            // added in warp order (sampling.cu:34-42).  The 4*C per-lane sums of a physical warp are
-            // tree-reduced together: at each butterfly level a lane keeps half of the sums and hands the
-            // other half to its partner, which performs exactly the additions of the plain butterfly
-            // (offsets 16, 8, 4, 2, 1) with 31 shuffles instead of 5 per sum.  Also returns the smallest and
-            // largest candidate bit pattern strictly inside (lo, hi).
-            auto eval = [&](const float (&f)[4], uint32_t lo, uint32_t hi, uint32_t oc[4], float om[4], uint32_t& vmin,
-                            uint32_t& vmax) {
-                uint32_t c01 = 0, c23 = 0;   // packed per-thread counts: (f0 | f1 << 16), (f2 | f3 << 16)
-                uint32_t mn = 0xffffffffu, mxv = 0u;
-                constexpr int NB = (C > 8) ? C / 8 : 1;   // batches of 8 virtual warps (32 sums) per tree pass
-                constexpr int NI = (C > 8) ? 8 : C;
-#pragma unroll
-                for (int bt = 0; bt < NB; bt++) {
-                    float v[32];
-#pragma unroll
-                    for (int k = 0; k < 32; k++) v[k] = 0.f;
-                    for (int j = 0; j < maxn; j++) {
-#pragma unroll
-                        for (int ii = 0; ii < NI; ii++) {
-                            const int i = bt * 8 + ii;
-                            if (j < nci[i]) {
-                                const float q = tval[j * kLanes + t + L * i];
-                                const uint32_t qb = __float_as_uint(q);
-                                if (q >= f[0]) { c01 += 1u; v[4 * ii] += q; }
-                                if (q >= f[1]) { c01 += 0x10000u; v[4 * ii + 1] += q; }
-                                if (q >= f[2]) { c23 += 1u; v[4 * ii + 2] += q; }
-                                if (q >= f[3]) { c23 += 0x10000u; v[4 * ii + 3] += q; }
-                                if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) {
-                        const bool up = (lane & o) != 0;
-#pragma unroll
-                        for (int k = 0; k < o; k++) {
-                            const float keep = up ? v[k + o] : v[k];
-                            const float give = up ? v[k] : v[k + o];
-                            v[k] = keep + __shfl_xor_sync(FULL, give, o);
-                        }
-                    }
-                    // lane l now holds the tree total of sum index l = 4 * ii + pivot
-                    if (lane < 4 * NI) pm[tb * 128 + (lane & 3) * 32 + wl + WPC * (bt * 8 + (lane >> 2))] = v[0];
-                }
-                c01 = __reduce_add_sync(FULL, c01);
-                c23 = __reduce_add_sync(FULL, c23);
-                mn = __reduce_min_sync(FULL, mn);
-                mxv = __reduce_max_sync(FULL, mxv);
-                if (lane == 0) pc[tb * 32 + wl] = make_uint4(c01, c23, mn, mxv);
-                __syncthreads();
-                {
-                    const uint4 c4 = (lane < WPC) ? pc[tb * 32 + lane] : make_uint4(0u, 0u, 0xffffffffu, 0u);
-                    const uint32_t a = __reduce_add_sync(FULL, c4.x), bq = __reduce_add_sync(FULL, c4.y);
-                    vmin = __reduce_min_sync(FULL, c4.z);
-                    vmax = __reduce_max_sync(FULL, c4.w);
-                    oc[0] = a & 0xffffu; oc[1] = a >> 16; oc[2] = bq & 0xffffu; oc[3] = bq >> 16;
-                    float sacc = 0.f;
-                    if (lane < 4) {
-                        const float4* q4 = reinterpret_cast<const float4*>(pm + tb * 128 + lane * 32);
-                        float4 x4 = q4[0];
-                        sacc = x4.x; sacc += x4.y; sacc += x4.z; sacc += x4.w;
-#pragma unroll
-                        for (int w4 = 1; w4 < 8; w4++) {
-                            x4 = q4[w4];
-                            sacc += x4.x; sacc += x4.y; sacc += x4.z; sacc += x4.w;
-                        }
-                    }
-                    om[0] = __shfl_sync(FULL, sacc, 0);
-                    om[1] = __shfl_sync(FULL, sacc, 1);
-                    om[2] = __shfl_sync(FULL, sacc, 2);
-                    om[3] = __shfl_sync(FULL, sacc, 3);
-                }
-                tb ^= 1;
-            };
-            const uint32_t ustar = beta_p + 1u;
-            uint32_t n_eval = 0;
-            left = __float_as_uint(pmin);
-            right = __float_as_uint(pmax) + 1u;
-            uint32_t cnt_x = (uint32_t)V, cnt_r = 0u;   // counts at left / at right
-            float mass_x = 1.0f, mass_r = 0.f;
-            // Once every element strictly inside (left, right) has one and the same value v, the remaining
-            // rounds need no data: a pivot equal to `left` selects the set of `left`, a pivot in (left, v]
-            // the set {p >= v}, a pivot above v the set of `right`.  They are then replayed arithmetically.
-            bool frozen = false;
-            uint32_t v_bits = 0, cnt_v = 0;
-            float mass_v = 0.f;
-            while (rounds < 64u) {
-                const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
-                if (!(go && left < right - 1u)) break;
-                rounds++;
-                const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
-                const uint32_t pv[3] = {py, pz, pw};
-                uint32_t cnt[4];
-                float mass[4];
-                if (!frozen) {
-                    n_eval++;
-                    const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
-                                        __uint_as_float(max(pw, ustar)), __uint_as_float(max(left + 1u, ustar))};
-                    uint32_t vmin, vmax;
-                    eval(f, left, right, cnt, mass, vmin, vmax);
-                    if (left >= beta_p && (vmin >= vmax)) {   // one distinct value inside (or none: vmin > vmax)
-                        frozen = true;
-                        v_bits = (vmin == vmax) ? vmin : left;
-                        cnt_v = cnt[3];      // the set {p >= left + 1} is {p >= v}
-                        mass_v = mass[3];
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 3; i++) {
-                        const bool at_left = (pv[i] == left), le_v = (pv[i] <= v_bits);
-                        cnt[i] = at_left ? cnt_x : le_v ? cnt_v : cnt_r;
-                        mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
-                    }
-                }
-                bool ok[3];
 #pragma unroll
                 for (int i = 0; i < 3; i++) {
-                    if (pv[i] <= beta_p) {
-                        ok[i] = false;
-                        if (!((use_cnt && cnt[i] > top_k) || mass[i] > top_p)) valid = false;
-                    } else {
-                        ok[i] = (use_cnt ? cnt[i] < top_k : true) && mass[i] < top_p;
-                    }
+                    const bool at_left = (pv[i] == left), le_v = (pv[i] <= v_bits);
+                    cnt[i] = at_left ? cnt_x : le_v ? cnt_v : cnt_r;
+                    mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
                 }
-                if (!valid) break;
-                if (ok[0]) { right = py; cnt_r = cnt[0]; mass_r = mass[0]; }
-                else if (ok[1]) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; cnt_r = cnt[1]; mass_r = mass[1]; }
-                else if (ok[2]) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; cnt_r = cnt[2]; mass_r = mass[2]; }
-                else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
             }
-            stamp(9);   // replay rounds done
-            valid = valid && (left > beta_p);
-            if (valid) {
-                path = 0;
-                const bool early_exit = left < right - 1u;
-                const float thr = __uint_as_float(left);
-                // recount at the threshold (sampling.cu:657-680): elements above the threshold are those
-                // >= the next float; the three totals have the association of the search masses
-                uint32_t tc[4], d0, d1;
-                float tm[4];
-                const float fr[4] = {__uint_as_float(left + 1u), thr, INFINITY, INFINITY};
-                eval(fr, 0u, 0u, tc, tm, d0, d1);
-                const uint32_t sgtk = tc[0], seqk = tc[1] - tc[0];
-                const float sgtp = tm[0];
-                float comp = 1.0f;   // sampling.cu:690-696, :903-908
-                if (seqk > 0) {
-                    comp = fminf(sanitize((top_p - sgtp) / (thr * seqk)), comp);
-                    if (use_cnt) comp = fminf(sanitize(float(top_k - sgtk) / seqk), comp);
-                    comp = fmaxf(comp, 0.0f);
+            bool ok[3];
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                if (clamp && pv[i] <= beta_p) {
+                    ok[i] = false;
+                    if (!((use_cnt && cnt[i] > top_k) || mass[i] > top_p)) valid = false;
+                } else {
+                    ok[i] = (use_cnt ? cnt[i] < top_k : true) && mass[i] < top_p;
                 }
-                // lane pick (sampling.cu:699-723)
-                float incl[C];
-#pragma unroll
-                for (int i = 0; i < C; i++) {
-                    float g = 0.f;
-                    uint32_t e = 0;
-                    for (int j = 0; j < nci[i]; j++) {
-                        const float q = tval[j * kLanes + t + L * i];
-                        if (q == thr) e++;
-                        if (q > thr) g += q;
-                    }
-                    const float actual_p = g + (thr * e) * comp;
-                    incl[i] = warp_scan_desc(actual_p, lane);
-                    if (lane == 31) s_wtot[wl + WPC * i] = incl[i];
-                }
-                __syncthreads();
-                float pre_prev[C];
-#pragma unroll
-                for (int i = 0; i < C; i++) pre_prev[i] = 0.f;
-                float s0 = 0.f;
-                {
-#pragma unroll
-                    for (int w = 0; w < kWarps; w++) {
-                        s0 = (w == 0) ? s_wtot[0] : s0 + s_wtot[w];
-#pragma unroll
-                        for (int i = 0; i < C; i++)
-                            if (w == wl + WPC * i - 1) pre_prev[i] = s0;
-                    }
-                }
-                const float sum_p = s0;
-                const float randp = sum_p * ux;
-#pragma unroll
-                for (int i = 0; i < C; i++) {
-                    const int vw = wl + WPC * i;
-                    const float cumu_p = (vw > 0) ? incl[i] + pre_prev[i] : incl[i];
-                    const bool u = (randp <= cumu_p);
-                    bool u_prev = __shfl_up_sync(FULL, u, 1);
-                    if (lane == 0) u_prev = (vw > 0) ? (randp <= pre_prev[i]) : false;
-                    if (u != u_prev) *s_idxt = t + L * i;
-                }
-                if (t == 0) {  // advance the stored RNG state by one 4-word block
-                    const uint4 nctr = ctr_next(rng.ctr);
-                    uint4* st = reinterpret_cast<uint4*>(p.states + (long long)b * RS_STATE_BYTES);
-                    st[0] = nctr;
-                    st[1] = philox4x32_10(nctr, rng.key_pos.x, rng.key_pos.y);
-                }
-                __syncthreads();
-                stamp(7);
-                // element pick inside the chosen lane (sampling.cu:725-751)
-                const int idxt = *s_idxt;
-                float oincl[C];
-                int idn_of[C];
-#pragma unroll
-                for (int it = 0; it < C; it++) {
-                    const int vt = it * L + t;
-                    const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
-                    float o0 = 0.f;
-                    if (idn < V) {
-                        const float x = scaled_logit(lrow[idn], rep ? prow[idn] : 0.f, rep, p.scale);
-                        o0 = exp2f(x - mx) / denom;
-                    }
-                    const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
-                    oincl[it] = warp_scan_desc(o, lane);
-                    idn_of[it] = idn;
-                    if (lane == 31) s_wtot[vt >> 5] = oincl[it];
-                }
-                __syncthreads();
-                float opre[C];
-                s0 = 0.f;
-#pragma unroll
-                for (int it = 0; it < C; it++) opre[it] = 0.f;
-#pragma unroll
-                for (int w = 0; w < kWarps; w++) {
-                    s0 = (w == 0) ? s_wtot[0] : s0 + s_wtot[w];
-#pragma unroll
-                    for (int it = 0; it < C; it++)
-                        if (w == it * WPC + wl - 1) opre[it] = s0;
-                }
-                const float sum_o = s0;
-                const float rand2 = sum_o * uy;
-#pragma unroll
-                for (int it = 0; it < C; it++) {
-                    const int vw = it * WPC + wl;
-                    const float cumu_o = (vw > 0) ? oincl[it] + opre[it] : oincl[it];
-                    const bool uo = (rand2 <= cumu_o);
-                    bool uo_prev = __shfl_up_sync(FULL, uo, 1);
-                    if (lane == 0) uo_prev = (vw > 0) ? (rand2 <= opre[it]) : false;
-                    if (uo != uo_prev) *s_token = (idn_of[it] < V) ? idn_of[it] : 0;
-                }
-                __syncthreads();
-                token = *s_token;
-                stamp(8);
-                if (t == 0) {
-                    p.out[b] = token;
-                    if (p.dbg_trace) {
-                        rs_trace tr;
-                        tr.maxu = mx; tr.denom = denom; tr.pmin = pmin; tr.pmax = pmax; tr.threshold = thr; tr.comp = comp;
-                        tr.sgtp = sgtp; tr.sum_p = sum_p; tr.randp = randp; tr.sum_o = sum_o; tr.rand2 = rand2;
-                        tr.left = left; tr.seqk = seqk; tr.sgtk = sgtk; tr.rounds = rounds; tr.idxt = (uint32_t)idxt;
-                        tr.early_exit = early_exit ? 1u : 0u;
-                        tr.rnd[0] = rnd4[0]; tr.rnd[1] = rnd4[1]; tr.rnd[2] = rnd4[2]; tr.rnd[3] = rnd4[3];
-                        tr.token = token;
-                        tr.path = 0;
-                        tr.ncand = ncand;
-#pragma unroll
-                        for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
-                        tr.t_ns[0] = n_eval;
-                        p.dbg_trace[b] = tr;
-                    }
-                }
-            } else if (sure && !rep) {
-                // cannot happen (see `sure`); the other CTAs are gone, so only report it
-                if (t == 0) { atomicExch(p.status, RS_ERR_INTERNAL); p.out[b] = 0; }
             }
-            __syncthreads();   // all reads of the CTA-local partials are done before the mailbox is reused
+            if (!valid) break;
+            if (ok[0]) { right = py; cnt_r = cnt[0]; mass_r = mass[0]; }
+            else if (ok[1]) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; cnt_r = cnt[1]; mass_r = mass[1]; }
+            else if (ok[2]) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; cnt_r = cnt[2]; mass_r = mass[2]; }
+            else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
         }
-        if (sure && !rep) return;
-        // verdict (and the sampled id, which the penalty update needs) to every CTA
-        post(make_uint4(valid ? 1u : 0u, (uint32_t)token, 0, 0), make_uint4(0, 0, 0, 0));
-        exchange_sync();
-        mb = mbox + phase * 64;
-        phase ^= 1;
-        {
-            const uint4 r = reinterpret_cast<const uint4*>(mb)[0];   // CTA 0's first warp is virtual warp 0
-            valid = (r.x != 0u);
-            token = (int)r.y;
-        }
-        if (valid) {
-            if (rep) {   // sampling.cu:427-437
-#pragma unroll 2
-                for (int s = 0; s < Kt; s++) {
-                    const int i4 = s * kLanes + tg;
-                    float4 q4 = reinterpret_cast<float4*>(prow)[i4];
-                    float e[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float old = e[j];
-                        e[j] = fmaf(old, p.decay, (i4 * 4 + j != token) ? 0.f : (old == 0.f ? p.presence : p.repetition));
-                    }
-                    reinterpret_cast<float4*>(prow)[i4] = make_float4(e[0], e[1], e[2], e[3]);
-                }
+        return valid && (!clamp || left > beta_p);
+    };
+
+    float gtp = 0.f;         // this lane's mass above the threshold, its ties with it, its count above
+    uint32_t eqk = 0, gtk = 0;
+    bool done = false;
+    if (cand_ok) {
+        // ===== candidate list: a few elements per lane at most =====
+        const int m_own = min(nc, cap);
+        for (int i = 0; i < m_own; i++) cand_at(i) = cand_at(i) / denom;
+        const uint32_t beta_p = __float_as_uint(beta_e / denom);
+        auto cand_eval = [&](const float (&f)[4], uint32_t lo, uint32_t hi, uint32_t, float (&m)[4], uint32_t& c01,
+                             uint32_t& c23, uint32_t& mn, uint32_t& mxv) {
+            m[0] = m[1] = m[2] = m[3] = 0.f;
+            c01 = c23 = 0u;
+            mn = 0xffffffffu;
+            mxv = 0u;
+            for (int i = 0; i < m_own; i++) {
+                const float q = cand_at(i);
+                const uint32_t qb = __float_as_uint(q);
+                if (q >= f[0]) { c01 += 1u; m[0] += q; }
+                if (q >= f[1]) { c01 += 0x10000u; m[1] += q; }
+                if (q >= f[2]) { c23 += 1u; m[2] += q; }
+                if (q >= f[3]) { c23 += 0x10000u; m[3] += q; }
+                if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
             }
-            return;
-        }
-        // The candidates did not settle the cutoff (too little mass above the bound): bring the row back
-        // (CTA 0's stripes held the table) and fall through to the whole-row search.
-        rounds = 0;
-        if (SMEM) {
-            if (wl == 0) {
-                const int kfull = V4 >> 10, rem = V4 & 1023;
-                const int vl = min(max(rem - (int)crank * L, 0), L);
-                const uint32_t bar = smem_addr(mbar);
-                if (lane == 0) mbar_expect_tx(bar, (uint32_t)(kfull * L + vl) * 16u);
-                __syncwarp();
-                const float4* src = reinterpret_cast<const float4*>(lrow) + crank * L;
-                const uint32_t dst = smem_addr(row.slab);
-                for (int k = lane; k < kfull; k += 32) bulk_g2s(dst + k * L * 16, src + k * kLanes, L * 16, bar);
-                if (lane == 0 && vl > 0) bulk_g2s(dst + kfull * L * 16, src + kfull * kLanes, vl * 16, bar);
-            }
-            if (!mbar_wait_bounded(smem_addr(mbar), 1, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
-            for (int s = 0; s < Kt; s++) {
-                float4 v = row.ld(s);
-                float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (rep) q4 = reinterpret_cast<const float4*>(prow)[s * kLanes + tg];
-                v.x = scaled_logit(v.x, q4.x, rep, p.scale);
-                v.y = scaled_logit(v.y, q4.y, rep, p.scale);
-                v.z = scaled_logit(v.z, q4.z, rep, p.scale);
-                v.w = scaled_logit(v.w, q4.w, rep, p.scale);
-                row.st(s, v);
+        };
+        done = run_search(cand_eval, true, beta_p);
+        if (done) {
+            path = 0;
+            const float thr = __uint_as_float(left);
+            for (int i = 0; i < m_own; i++) {
+                const float q = cand_at(i);
+                if (q == thr) eqk++;
+                if (q > thr) { gtk++; gtp += q; }
             }
         }
     }
-
-    // ===== whole-row path: every CTA searches its own stripes; partials meet in the mailboxes =====
-    {
-        // pass 3: p = exp2f(x - max) / denom (sampling.cu:573-590), in place.
+    if (!done) {
+        // ===== whole row: pass 3, p = exp2f(x - max) / denom (sampling.cu:573-590), in place; then the search
+        // over every lane's full list, dropping elements below `left` as the bracket rises =====
 #pragma unroll 2
         for (int s = 0; s < Kt; s++) {
             float4 v = row.ld(s);
@@ -788,40 +517,23 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             v.w = exp2f(v.w - mx) / denom;
             row.st(s, v);
         }
-        left = __float_as_uint(pmin);
-        right = __float_as_uint(pmax) + 1u;
-        rounds = 0;
-        uint32_t cnt_x = (uint32_t)V;
-        float mass_x = 1.0f;
         int n = Kt * 4;                      // live elements of this lane's list
         uint32_t list_total = (uint32_t)V;   // live elements over the whole row
-        uint32_t list_left = left;           // the list holds exactly the elements >= list_left
-        while (rounds < 64u) {
-            const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
-            if (!(go && left < right - 1u)) break;
-            rounds++;
-            const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pw = (pz + right) >> 1;
-            uint32_t cnt[3];
-            float mass[3];
-            const bool compact = (left != list_left) && (cnt_x * 2u <= list_total);
+        uint32_t list_left = __float_as_uint(pmin);   // the list holds exactly the elements >= list_left
+        auto slab_eval = [&](const float (&f)[4], uint32_t lo, uint32_t, uint32_t cnt_lo, float (&m)[4], uint32_t& c01,
+                             uint32_t& c23, uint32_t& mn, uint32_t& mxv) {
+            mn = 0u;
+            mxv = 1u;   // bounds are not tracked here
+            const bool compact = (lo != list_left) && (cnt_lo * 2u <= list_total);
             if (compact) {
-                search_pass<C, SMEM, true>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw),
-                                           __uint_as_float(left), cnt, mass);
-                list_total = cnt_x;
-                list_left = left;
+                slab_pass<C, SMEM, true>(row, n, f, __uint_as_float(lo), m, c01, c23);
+                list_total = cnt_lo;
+                list_left = lo;
             } else {
-                search_pass<C, SMEM, false>(row, n, __uint_as_float(py), __uint_as_float(pz), __uint_as_float(pw), 0.f,
-                                            cnt, mass);
+                slab_pass<C, SMEM, false>(row, n, f, 0.f, m, c01, c23);
             }
-            combine_round(cnt, mass);
-            const bool ok0 = (use_cnt ? cnt[0] < top_k : true) && mass[0] < top_p;
-            const bool ok1 = (use_cnt ? cnt[1] < top_k : true) && mass[1] < top_p;
-            const bool ok2 = (use_cnt ? cnt[2] < top_k : true) && mass[2] < top_p;
-            if (ok0) { right = py; }
-            else if (ok1) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; }
-            else if (ok2) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; }
-            else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
-        }
+        };
+        run_search(slab_eval, false, 0u);
         // recount at the threshold (sampling.cu:657-680)
         const float thr = __uint_as_float(left);
         const int slots = (n + 3) >> 2;
@@ -840,26 +552,18 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     const bool early_exit = left < right - 1u;
     const float thr = __uint_as_float(left);
 
-    // The reference takes the three totals from block scans; lane 31 of a descending-offset scan
-    // holds the same tree value as the butterfly, and the warp values are then added in order.
-    {
-        const float wsum = warp_tree_sum(gtp);
-        const uint32_t weq = __reduce_add_sync(FULL, eqk), wgt = __reduce_add_sync(FULL, gtk);
-        post(make_uint4(__float_as_uint(wsum), weq, wgt, 0), make_uint4(0, 0, 0, 0));
-    }
-    exchange_sync();
-    mb = mbox + phase * 64;
-    phase ^= 1;
+    // The reference takes the three totals from block scans; lane 31 of a descending-offset scan holds the
+    // same tree value as the butterfly, and the warp values are then added in warp order.
     float sgtp;
     uint32_t seqk, sgtk;
     {
-        const uint4 c4 = reinterpret_cast<const uint4*>(mb)[lane * 2];
-        seqk = __reduce_add_sync(FULL, c4.y);
-        sgtk = __reduce_add_sync(FULL, c4.z);
-        float s0 = mb[0].x;
-#pragma unroll
-        for (int w = 1; w < kWarps; w++) s0 += mb[w * 2].x;
-        sgtp = s0;
+        const float m[4] = {gtp, 0.f, 0.f, 0.f};
+        uint32_t cnt[4], d0, d1;
+        float mass[4];
+        totals(m, gtk | (eqk << 16), 0u, 0u, 0u, cnt, mass, d0, d1);
+        sgtp = mass[0];
+        sgtk = cnt[0];
+        seqk = cnt[1];
     }
 
     // ---- compensation factor for the boundary ties (sampling.cu:690-696, :903-908) -----------
@@ -977,6 +681,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
                 tr.ncand = ncand;
 #pragma unroll
                 for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
+                tr.t_ns[0] = n_eval;
                 p.dbg_trace[b] = tr;
             }
         }
@@ -985,10 +690,10 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // ---- penalties: decay everything, add the hit on the sampled id (sampling.cu:427-437).
     // The sampled id lies in the owner CTA's own stripes, so no cross-CTA hand-off is needed. ---
     if (rep) {
-#pragma unroll 2
+#pragma unroll 4
         for (int s = 0; s < Kt; s++) {
             const int i4 = s * kLanes + tg;
-            float4 q4 = reinterpret_cast<float4*>(prow)[i4];
+            float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + i4);
             float e[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -1093,7 +798,7 @@ static void choose_candidates(long long V, long long top_k, double top_p, int* s
     *cand_slots = 0;
     if (g_path_override.load() == 1) return;
     if (top_k >= V && top_p >= 1.0) return;            // nothing is filtered: the whole row is kept
-    // Beyond top_k ~ 250 the candidate table would outgrow a CTA's stripes; such calls search the whole row.
+    // Beyond top_k ~ 250 the candidate lists stop being short; such calls search the whole row.
     if (top_k < V) {
         if (top_k + 2 > 256) return;
         *sel_rank = (int)((top_k + 2 + 31) / 32);
@@ -1103,12 +808,7 @@ static void choose_candidates(long long V, long long top_k, double top_p, int* s
     *cand_slots = (*sel_rank <= 4) ? 2 : 4;
 }
 
-// stripes of one CTA; with candidates they must also be able to hold CTA 0's table (count + entries per lane)
-static int smem_need(int V, int C, int cand_slots) {
-    const int table = cand_slots ? 4 * kLanes * (1 + 4 * cand_slots) : 0;
-    const int slab = slab_bytes(V, C);
-    return kSlabOff + cand_slots * (kLanes / C) * 16 + (slab > table ? slab : table);
-}
+static int smem_need(int V, int C, int cand_slots) { return kSlabOff + cand_slots * (kLanes / C) * 16 + slab_bytes(V, C); }
 
 // Cluster width per row.  Small batches want the widest portable cluster (each of the 32
 // virtual warps gets a scheduler of its own at 8 CTAs); large batches want as many rows
