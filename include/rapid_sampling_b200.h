@@ -57,9 +57,11 @@ typedef struct rs_trace {
  */
 int rs_setup_rand(void* states_device, uint64_t seed, int64_t B, int64_t first_row, void* stream);
 
-/* Device scratch a call with this shape may need (rows too large for on-chip storage fall back
- * to a B*V fp32 scratch, the counterpart of the reference's `probs`, sampling.cu:488, :1014),
- * plus a status word.  Never 0. */
+/* Device scratch a call with this shape may need, plus a status word.  Never 0.  Batches that fit on chip at
+ * once need only the status word (256 bytes); larger batches and rows too large for on-chip storage run the
+ * streaming variant, whose fallback uses a B*V fp32 scratch (the counterpart of the reference's `probs`,
+ * sampling.cu:488, :1014).  A call given less than this runs on chip when the row fits, else fails with
+ * RS_ERR_WORKSPACE. */
 size_t rs_workspace_bytes(int64_t B, int64_t V);
 
 /*
@@ -133,8 +135,9 @@ int rs_device_status(void* workspace_device, void* stream);
  * choice.  Benchmarking aid; returns the previous value. */
 int rs_set_cluster_override(int cluster_ctas);
 
-/* Search strategy: 0 = automatic (candidate shortcut with whole-row fallback), 1 = always search the whole
- * row.  Results are identical; testing / benchmarking aid.  Returns the previous value. */
+/* Strategy override: 0 = automatic, 1 = always search the whole row (no candidate shortcut), 2 = always the
+ * streaming variant, 3 = always the on-chip variant when the row fits.  Results are identical; testing /
+ * benchmarking aid.  Returns the previous value. */
 int rs_set_path_override(int mode);
 
 /* Number of sampler kernels launched through this library since it was loaded. */

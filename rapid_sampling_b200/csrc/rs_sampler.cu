@@ -157,6 +157,25 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     const int cap = p.cand_slots * 4;
     auto cand_at = [&](int i) -> float& { return cand[((i >> 2) * L + t) * 4 + (i & 3)]; };
 
+    // x = sanitised scaled logit of slot s: kept in the shared-memory stripes, or (streaming variant) read
+    // again from global memory -- the same functions on the same inputs, hence the same bits
+    auto xload = [&](int s) -> float4 {
+        if (SMEM) return row.ld(s);
+        float4 v = __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
+        if (rep) {
+            const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
+            v.x = scaled_logit(v.x, q4.x, true, p.scale);
+            v.y = scaled_logit(v.y, q4.y, true, p.scale);
+            v.z = scaled_logit(v.z, q4.z, true, p.scale);
+            v.w = scaled_logit(v.w, q4.w, true, p.scale);
+        } else {
+            v.x = scaled_fast(v.x, p.scale);
+            v.y = scaled_fast(v.y, p.scale);
+            v.z = scaled_fast(v.z, p.scale);
+            v.w = scaled_fast(v.w, p.scale);
+        }
+        return v;
+    };
     const uint32_t mbox_a = smem_addr(mbox);
     int phase = 0;
     // Posts this warp's 32-byte entry into every CTA's mailbox (values are warp-uniform).
@@ -276,25 +295,25 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     if (rep) {
 #pragma unroll 8
         for (int s = 0; s < Kt; s++) {
-            float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
+            float4 v = SMEM ? row.ld(s) : __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
             v.x = scaled_logit(v.x, q4.x, true, p.scale);
             v.y = scaled_logit(v.y, q4.y, true, p.scale);
             v.z = scaled_logit(v.z, q4.z, true, p.scale);
             v.w = scaled_logit(v.w, q4.w, true, p.scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
-            row.st(s, v);
+            if (SMEM) row.st(s, v);
         }
     } else {
-#pragma unroll 4
+#pragma unroll 8
         for (int s = 0; s < Kt; s++) {
-            float4 v = SMEM ? row.ld(s) : reinterpret_cast<const float4*>(lrow)[s * kLanes + tg];
+            float4 v = SMEM ? row.ld(s) : __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
             v.x = scaled_fast(v.x, p.scale);
             v.y = scaled_fast(v.y, p.scale);
             v.z = scaled_fast(v.z, p.scale);
             v.w = scaled_fast(v.w, p.scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
-            row.st(s, v);
+            if (SMEM) row.st(s, v);
         }
     }
     stamp(2);   // pass 1 done
@@ -324,7 +343,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         beta_x = warp_min(e.y);   // every warp holds >= sel_rank elements >= beta_x
     }
     stamp(3);   // first exchange done
-    const bool try_cand = (sel_rank > 0) && SMEM;
+    const bool try_cand = (sel_rank > 0);
     // Candidates are defined in the domain of e = exp2f(x - max): division by the denominator is
     // monotone, so {e >= beta_e} contains every element whose probability exceeds beta_e / denom.
     const float beta_e = try_cand ? exp2f(beta_x - mx) : INFINITY;
@@ -333,9 +352,9 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // elements with e >= beta_e are appended, in order, to this lane's candidate list -----------
     float acc = 0.f, emin = INFINITY, emax = -INFINITY;
     int nc = 0, ns = 0;   // candidates, and those strictly above the bound
-#pragma unroll 2
+#pragma unroll (SMEM ? 2 : 4)
     for (int s = 0; s < Kt; s++) {
-        float4 v = row.ld(s);
+        float4 v = xload(s);
         v.x = exp2f(v.x - mx);
         v.y = exp2f(v.y - mx);
         v.z = exp2f(v.z - mx);
@@ -385,7 +404,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     if (p.dbg_probs) {   // test instrumentation: the probabilities of the whole row
         float* dprow = p.dbg_probs + (long long)b * V;
         for (int s = 0; s < Kt; s++) {
-            float4 v = row.ld(s);
+            float4 v = xload(s);
             v.x = exp2f(v.x - mx) / denom;
             v.y = exp2f(v.y - mx) / denom;
             v.z = exp2f(v.z - mx) / denom;
@@ -508,9 +527,9 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     if (!done) {
         // ===== whole row: pass 3, p = exp2f(x - max) / denom (sampling.cu:573-590), in place; then the search
         // over every lane's full list, dropping elements below `left` as the bracket rises =====
-#pragma unroll 2
+#pragma unroll (SMEM ? 2 : 4)
         for (int s = 0; s < Kt; s++) {
-            float4 v = row.ld(s);
+            float4 v = xload(s);
             v.x = exp2f(v.x - mx) / denom;
             v.y = exp2f(v.y - mx) / denom;
             v.z = exp2f(v.z - mx) / denom;
@@ -810,18 +829,25 @@ static void choose_candidates(long long V, long long top_k, double top_p, int* s
 
 static int smem_need(int V, int C, int cand_slots) { return kSlabOff + cand_slots * (kLanes / C) * 16 + slab_bytes(V, C); }
 
-// Cluster width per row.  Small batches want the widest portable cluster (each of the 32
-// virtual warps gets a scheduler of its own at 8 CTAs); large batches want as many rows
-// resident as shared memory allows so that one row's load overlaps another row's search.
-static int choose_cluster(const DeviceInfo& di, long long B, int V, int cand_slots, bool* use_smem) {
-    const int forced = g_cluster_override.load();
+// Which kernel variant serves a call.
+//  * on-chip: the row stays in the cluster's shared memory (one HBM read, lowest latency).  Used while the
+//    whole batch is resident at once; beyond that rows would queue for shared memory.
+//  * streaming: nothing but the candidate lists is kept on chip; the row is read twice (the second time from
+//    L2), any number of rows is in flight, and a row whose candidates do not settle the cutoff falls back to a
+//    global scratch row (the counterpart of the reference's `probs`, sampling.cu:488).  Needs B*V floats.
+struct Plan {
+    int C;
+    bool smem;
+    int sel_rank, cand_slots;
+    size_t ws;
+};
+static size_t ws_bytes(long long B, long long V) { return 256 + (size_t)B * (size_t)V * sizeof(float); }
+
+static Plan make_plan(const DeviceInfo& di, long long B, int V, int sel_rank, int cand_slots, size_t ws_avail) {
+    Plan pl;
+    pl.sel_rank = sel_rank;
+    pl.cand_slots = cand_slots;
     auto fits = [&](int C) { return smem_need(V, C, cand_slots) <= di.smem_optin; };
-    *use_smem = true;
-    if (forced) {
-        if (fits(forced)) return forced;
-        *use_smem = false;
-        return 8;
-    }
     auto resident_rows = [&](int C) {
         const int need = smem_need(V, C, cand_slots) + 1024;
         int per_sm = di.smem_sm / need;
@@ -829,21 +855,17 @@ static int choose_cluster(const DeviceInfo& di, long long B, int V, int cand_slo
         if (per_sm > 32) per_sm = 32;
         return (long long)di.sms * per_sm / C;
     };
-    if (fits(8) && B <= resident_rows(8)) return 8;
-    int best = 0;
-    long long best_rows = -1;
-    for (int C : {8, 4, 2, 1}) {
-        if (!fits(C)) continue;
-        const long long r = resident_rows(C);
-        if (r > best_rows) { best_rows = r; best = C; }
-    }
-    if (best) return best;
-    if (fits(16)) return 16;
-    *use_smem = false;
-    return 8;
+    const int forced = g_cluster_override.load();
+    const int mode = g_path_override.load();
+    const bool can_stream = ws_avail >= ws_bytes(B, V);
+    auto streaming = [&]() { pl.C = 8; pl.smem = false; pl.ws = ws_bytes(B, V); return pl; };
+    auto onchip = [&](int C) { pl.C = C; pl.smem = true; pl.ws = 256; return pl; };
+    if (forced) return fits(forced) ? onchip(forced) : streaming();
+    if (mode == 2) return streaming();
+    if (fits(8) && (B <= resident_rows(8) || mode == 3 || !can_stream)) return onchip(8);
+    if (!fits(8) && fits(16) && (B <= resident_rows(16) || mode == 3 || !can_stream)) return onchip(16);
+    return streaming();
 }
-
-static size_t ws_bytes(long long B, long long V) { return 256 + (size_t)B * (size_t)V * sizeof(float); }
 
 static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, float* penalties, void* states, int32_t* out,
                        double temperature, int64_t top_k, double top_p, double presence, double repetition, double decay,
@@ -864,17 +886,12 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     DeviceInfo* di = nullptr;
     int rc = get_device(&di);
     if (rc) return rc;
-    bool use_smem = true;
     int sel_rank = 0, cand_slots = 0;
     choose_candidates(V, top_k, top_p, &sel_rank, &cand_slots);
-    int C = choose_cluster(*di, B, (int)V, cand_slots, &use_smem);
-    if (!use_smem && cand_slots) {   // the candidate buffer must never push a row off the chip
-        sel_rank = cand_slots = 0;
-        use_smem = true;
-        C = choose_cluster(*di, B, (int)V, 0, &use_smem);
-    }
-    if (!use_smem) sel_rank = cand_slots = 0;
-    if (workspace_bytes < (use_smem ? (size_t)256 : ws_bytes(B, V))) return RS_ERR_WORKSPACE;
+    const Plan pl = make_plan(*di, B, (int)V, sel_rank, cand_slots, workspace_bytes);
+    if (workspace_bytes < pl.ws) return RS_ERR_WORKSPACE;
+    const bool use_smem = pl.smem;
+    const int C = pl.C;
 
     Params p;
     p.logits = logits + (T - 1) * V;
@@ -899,7 +916,7 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     p.cand_slots = cand_slots;
 
     cudaStream_t st = (cudaStream_t)stream;
-    if (!use_smem) return launch_one<8, false>(p, kSlabOff, st, *di);
+    if (!use_smem) return launch_one<8, false>(p, kSlabOff + cand_slots * (kLanes / 8) * 16, st, *di);
     const int smem = smem_need((int)V, C, cand_slots);
     switch (C) {
         case 1: return launch_one<1, true>(p, smem, st, *di);
@@ -1004,10 +1021,13 @@ int rs_setup_rand(void* states_device, uint64_t seed, int64_t B, int64_t first_r
 }
 
 size_t rs_workspace_bytes(int64_t B, int64_t V) {
-    if (B <= 0 || V <= 0) return 256;
-    // Only rows that exceed the widest cluster's shared memory need the global scratch row.
-    const bool may_fit = rs::kSlabOff + rs::slab_bytes((int)V, 16) <= 227 * 1024;
-    return may_fit ? 256 : rs::ws_bytes(B, V);
+    if (B <= 0 || V <= 0 || V > 1048576) return 256;
+    rs::DeviceInfo b200;   // the library is built for B200 only: 148 SMs, 227 KiB per CTA, 228 KiB per SM
+    b200.sms = 148;
+    b200.smem_optin = 232448;
+    b200.smem_sm = 233472;
+    // sized for the widest candidate buffer, so that any top_k / top_p of a later call is covered
+    return rs::make_plan(b200, B, (int)V, 8, 4, ~(size_t)0).ws;
 }
 
 int rs_sample(const float* logits_device, int64_t B, int64_t T, int64_t V, float* penalties_device, void* states_device,
@@ -1070,7 +1090,7 @@ int rs_set_cluster_override(int cluster_ctas) {
 }
 
 int rs_set_path_override(int mode) {
-    return (mode == 0 || mode == 1) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
+    return (mode >= 0 && mode <= 3) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
 }
 
 uint64_t rs_kernel_launch_count(void) { return rs::g_launches.load(); }

@@ -44,8 +44,9 @@ def test_argument_errors_need_no_gpu():
     assert L.rs_sample(C.c_void_p(260), 1, 1, 1024, None, dummy, dummy, 1.0, -1, 0.5, 0.0, 0.0, 0.0, dummy, 256, None) == abi.RS_ERR_POINTER
     assert L.rs_setup_rand(None, 0, 4, 0, None) == abi.RS_ERR_POINTER
     assert L.rs_setup_rand(dummy, 0, 0, 0, None) == abi.RS_ERR_BATCH
-    assert L.rs_workspace_bytes(64, 151936) == 256                       # fits on chip: status word only
-    assert L.rs_workspace_bytes(2, 1048576) == 256 + 2 * 1048576 * 4     # global scratch row fallback
+    assert L.rs_workspace_bytes(4, 131072) == 256                        # whole batch on chip: status word only
+    assert L.rs_workspace_bytes(64, 151936) == 256 + 64 * 151936 * 4     # more rows than fit at once: streaming
+    assert L.rs_workspace_bytes(2, 1048576) == 256 + 2 * 1048576 * 4     # row too large for on-chip storage
     assert abi.status_string(abi.RS_ERR_VOCAB).startswith("Vocabulary size must be multiple of 4")
     assert L.rs_set_cluster_override(3) == 0 and L.rs_set_cluster_override(0) == 0
 
