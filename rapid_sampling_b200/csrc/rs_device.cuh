@@ -123,6 +123,12 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint4 v) {
 __device__ __forceinline__ void st_cluster_u32(uint32_t addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
+// Remote 4-byte store whose completion is counted on an mbarrier of the destination CTA.
+__device__ __forceinline__ void st_async_u32(uint32_t addr, uint32_t v, uint32_t remote_bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u32 [%0], %1, [%2];" ::"r"(addr), "r"(v),
+                 "r"(remote_bar)
+                 : "memory");
+}
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 

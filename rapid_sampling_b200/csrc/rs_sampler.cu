@@ -47,10 +47,11 @@ struct Params {
 };
 
 // shared-memory map (bytes)
-constexpr int kMboxOff = 0;        // 2 buffers x 32 entries x 32 B
-constexpr int kMboxBuf = 1024;
-constexpr int kMiscOff = 2048;     // mbarrier, small scalars, 32 warp totals
-constexpr int kSlabOff = 2560;
+constexpr int kXWords = 10;                      // words each warp contributes to an exchange
+constexpr int kMboxOff = 0;                      // 2 buffers of [kXWords][32 warps] words
+constexpr int kMboxBuf = kXWords * 32 * 4;
+constexpr int kMiscOff = 2 * kMboxBuf;           // mbarriers, small scalars, 32 warp totals
+constexpr int kSlabOff = kMiscOff + 256;
 constexpr uint32_t kWaitPolls = 1u << 22;
 
 __host__ __device__ constexpr int slab_bytes(int V, int C) { return ((V / 4 + 1023) / 1024) * (1024 / C) * 16; }
@@ -142,8 +143,8 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     const float* lrow = p.logits + (long long)b * p.row_stride;
     float* prow = rep ? p.penalties + (long long)b * V : nullptr;
 
-    float4* mbox = reinterpret_cast<float4*>(smem + kMboxOff);
     uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + kMiscOff);
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + kMiscOff + 16);   // two mailbox barriers
     int* s_idxt = reinterpret_cast<int*>(smem + kMiscOff + 8);
     int* s_token = reinterpret_cast<int*>(smem + kMiscOff + 12);
     float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
@@ -176,26 +177,49 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         }
         return v;
     };
-    const uint32_t mbox_a = smem_addr(mbox);
+    // ---- exchange of warp values across the cluster ----------------------------------------------------
+    // Every warp contributes kXWords words; word k of (virtual) warp w lands at box[k * 32 + w] in EVERY CTA's
+    // mailbox.  Lane l supplies word l >> 3 (a), word 4 + (l >> 3) (b) and, for l < 16, word 8 + (l >> 3) (c).
+    // The words travel as remote stores that count their bytes on an mbarrier of the destination CTA, so a
+    // CTA only waits for its own mailbox to fill (bounded poll) -- no cluster-wide barrier.  Two mailboxes
+    // alternate: a CTA can post exchange n+2 only after it has received everybody's n+1, which each CTA
+    // sends after it has finished reading n.
     int phase = 0;
-    // Posts this warp's 32-byte entry into every CTA's mailbox (values are warp-uniform).
-    auto post = [&](uint4 a, uint4 c2) {
+    uint32_t xpar = 0;
+    auto exchange = [&](uint32_t a, uint32_t bq, uint32_t c2) -> const uint32_t* {
+        uint32_t* box = reinterpret_cast<uint32_t*>(smem + kMboxOff + phase * kMboxBuf);
+        const int k = lane >> 3, r = lane & 7;
         if (C == 1) {
-            if (lane == 0) {
-                reinterpret_cast<uint4*>(mbox)[phase * 64 + wg * 2] = a;
-                reinterpret_cast<uint4*>(mbox)[phase * 64 + wg * 2 + 1] = c2;
+            if (r == 0) {
+                box[k * 32 + wg] = a;
+                box[(4 + k) * 32 + wg] = bq;
+                if (lane < 16) box[(8 + k) * 32 + wg] = c2;
             }
-        } else if (lane < C) {
-            const uint32_t dst = map_to_cta(mbox_a + phase * kMboxBuf + wg * 32, (uint32_t)lane);
-            st_cluster_v4(dst, a);
-            st_cluster_v4(dst + 16, c2);
+            __syncthreads();
+        } else {
+            const uint32_t bar = smem_addr(xbar + phase);
+            if (t == 0) mbar_expect_tx(bar, (uint32_t)kMboxBuf);
+#pragma unroll
+            for (int rr = 0; rr < (C > 8 ? 2 : 1); rr++) {
+                const uint32_t dst_cta = (uint32_t)(r + 8 * rr);
+                if (dst_cta < (uint32_t)C) {
+                    const uint32_t base = map_to_cta(smem_addr(box), dst_cta);
+                    const uint32_t rbar = map_to_cta(bar, dst_cta);
+                    st_async_u32(base + (k * 32 + wg) * 4, a, rbar);
+                    st_async_u32(base + ((4 + k) * 32 + wg) * 4, bq, rbar);
+                    if (lane < 16) st_async_u32(base + ((8 + k) * 32 + wg) * 4, c2, rbar);
+                }
+            }
+            if (!mbar_wait_bounded(bar, (xpar >> phase) & 1u, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
         }
+        xpar ^= (1u << phase);
+        phase ^= 1;
+        return box;
     };
-    auto exchange_sync = [&]() {
-        if (C == 1) __syncthreads();
-        else { cluster_arrive(); cluster_wait(); }
+    const int xk = lane >> 3;   // which of four values this lane forwards
+    auto pick4 = [&](uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) -> uint32_t {
+        return xk == 0 ? v0 : xk == 1 ? v1 : xk == 2 ? v2 : v3;
     };
-    const float4* mb;  // mailbox buffer to read after a sync
     // phase timestamps (ns) for the trace: test instrumentation only
     uint32_t ts[10];
     const bool want_ts = (p.dbg_trace != nullptr);
@@ -214,45 +238,56 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
 
     // Row totals of four ordered masses and four counts (packed per lane as c01 = n0 | n1 << 16,
     // c23 = n2 | n3 << 16; a lane holds at most 1024 elements), plus min / max of two bit patterns.
-    // Order of the masses: xor tree over the 32 lanes of a warp, then the 32 warp values added in warp
-    // order, as thread 0 of the reference does (sampling.cu:34-42).  Every warp of every CTA combines the
-    // 32 mailbox entries itself (lanes 0..3 run the four 32-step chains), so no second barrier is needed.
+    // Order of the masses: xor tree over the 32 lanes of a warp (offsets 16, 8, 4, 2, 1), then the 32 warp
+    // values added in warp order, as thread 0 of the reference does (sampling.cu:34-42).  The four trees
+    // share shuffles: at offsets 16 and 8 a lane keeps half of the sums and hands the other half to its
+    // partner -- the same additions as four separate butterflies -- so that lane l ends with sum l >> 3.
+    // Every warp of every CTA then combines the 32 mailbox columns itself: lanes 0..7 run the eight
+    // 32-step chains (counts travel as exact floats), so no second synchronisation is needed.
     auto totals = [&](const float (&m)[4], uint32_t c01, uint32_t c23, uint32_t mn, uint32_t mxv, uint32_t (&cnt)[4],
                       float (&mass)[4], uint32_t& vmin, uint32_t& vmax) {
-        const float t0 = warp_tree_sum(m[0]), t1 = warp_tree_sum(m[1]), t2 = warp_tree_sum(m[2]), t3 = warp_tree_sum(m[3]);
+        float x;
+        {
+            const bool up16 = (lane & 16) != 0, up8 = (lane & 8) != 0;
+            const float a0 = (up16 ? m[2] : m[0]) + __shfl_xor_sync(FULL, up16 ? m[0] : m[2], 16);
+            const float a1 = (up16 ? m[3] : m[1]) + __shfl_xor_sync(FULL, up16 ? m[1] : m[3], 16);
+            x = (up8 ? a1 : a0) + __shfl_xor_sync(FULL, up8 ? a0 : a1, 8);
+            x = x + __shfl_xor_sync(FULL, x, 4);
+            x = x + __shfl_xor_sync(FULL, x, 2);
+            x = x + __shfl_xor_sync(FULL, x, 1);
+        }
         c01 = __reduce_add_sync(FULL, c01);
         c23 = __reduce_add_sync(FULL, c23);
         mn = __reduce_min_sync(FULL, mn);
         mxv = __reduce_max_sync(FULL, mxv);
-        post(make_uint4(__float_as_uint(t0), __float_as_uint(t1), __float_as_uint(t2), __float_as_uint(t3)),
-             make_uint4(c01, c23, mn, mxv));
-        exchange_sync();
-        const float4* q = mbox + phase * 64;
-        phase ^= 1;
-        const uint4 e = reinterpret_cast<const uint4*>(q)[lane * 2 + 1];
-        cnt[0] = __reduce_add_sync(FULL, e.x & 0xffffu);
-        cnt[1] = __reduce_add_sync(FULL, e.x >> 16);
-        cnt[2] = __reduce_add_sync(FULL, e.y & 0xffffu);
-        cnt[3] = __reduce_add_sync(FULL, e.y >> 16);
-        vmin = __reduce_min_sync(FULL, e.z);
-        vmax = __reduce_max_sync(FULL, e.w);
+        const float cf = __uint2float_rn(pick4(c01 & 0xffffu, c01 >> 16, c23 & 0xffffu, c23 >> 16));
+        const uint32_t* box = exchange(__float_as_uint(x), __float_as_uint(cf), xk == 0 ? mn : mxv);
+        vmin = __reduce_min_sync(FULL, box[8 * 32 + lane]);
+        vmax = __reduce_max_sync(FULL, box[9 * 32 + lane]);
         float sacc = 0.f;
-        if (lane < 4) {
-            const float* col = reinterpret_cast<const float*>(q) + lane;
-            sacc = col[0];
+        if (lane < 8) {
+            const float4* col = reinterpret_cast<const float4*>(box + lane * 32);
+            float4 q = col[0];
+            sacc = q.x; sacc += q.y; sacc += q.z; sacc += q.w;
 #pragma unroll
-            for (int w = 1; w < kWarps; w++) sacc += col[w * 8];
+            for (int w4 = 1; w4 < 8; w4++) {
+                q = col[w4];
+                sacc += q.x; sacc += q.y; sacc += q.z; sacc += q.w;
+            }
         }
-        mass[0] = __shfl_sync(FULL, sacc, 0);
-        mass[1] = __shfl_sync(FULL, sacc, 1);
-        mass[2] = __shfl_sync(FULL, sacc, 2);
-        mass[3] = __shfl_sync(FULL, sacc, 3);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            mass[i] = __shfl_sync(FULL, sacc, i);
+            cnt[i] = __float2uint_rn(__shfl_sync(FULL, sacc, 4 + i));
+        }
     };
 
     // ---- load: bulk async copies of this CTA's stripes; RNG state read meanwhile -------------
     if (SMEM) {
         if (t == 0) {
             mbar_init(smem_addr(mbar), 1);
+            mbar_init(smem_addr(xbar), 1);
+            mbar_init(smem_addr(xbar + 1), 1);
             fence_mbar_init();
             *s_idxt = 0;
             *s_token = 0;
@@ -270,7 +305,13 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             if (lane == 0 && vl > 0) bulk_g2s(dst + kfull * L * 16, src + kfull * kLanes, vl * 16, bar);
         }
     } else {
-        if (t == 0) { *s_idxt = 0; *s_token = 0; }
+        if (t == 0) {
+            mbar_init(smem_addr(xbar), 1);
+            mbar_init(smem_addr(xbar + 1), 1);
+            fence_mbar_init();
+            *s_idxt = 0;
+            *s_token = 0;
+        }
         __syncthreads();
     }
     if (C > 1) cluster_arrive();  // peers must be running before their mailboxes are written
@@ -332,15 +373,11 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         wsel = __shfl_sync(FULL, tmax, __ffs(m) - 1);
     }
     if (C > 1) cluster_wait();
-    post(make_uint4(__float_as_uint(mx), __float_as_uint(wsel), 0, 0), make_uint4(0, 0, 0, 0));
-    exchange_sync();
-    mb = mbox + phase * 64;
-    phase ^= 1;
     float beta_x;
     {
-        const float4 e = mb[lane * 2];
-        mx = warp_max(e.x);
-        beta_x = warp_min(e.y);   // every warp holds >= sel_rank elements >= beta_x
+        const uint32_t* box = exchange(pick4(__float_as_uint(mx), __float_as_uint(wsel), 0u, 0u), 0u, 0u);
+        mx = warp_max(__uint_as_float(box[lane]));
+        beta_x = warp_min(__uint_as_float(box[32 + lane]));   // every warp holds >= sel_rank elements >= beta_x
     }
     stamp(3);   // first exchange done
     const bool try_cand = (sel_rank > 0);
@@ -383,21 +420,18 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     emax = warp_max(emax);
     const unsigned overflow = __any_sync(FULL, nc > cap) ? 1u : 0u;
     const uint32_t wnc = __reduce_add_sync(FULL, (uint32_t)nc), wns = __reduce_add_sync(FULL, (uint32_t)ns);
-    post(make_uint4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow), make_uint4(wnc, wns, 0, 0));
-    exchange_sync();
-    mb = mbox + phase * 64;
-    phase ^= 1;
     float denom;
     bool cand_ok;
     uint32_t ncand, nstrict;
     {
-        const float4 e = mb[lane * 2];
-        denom = warp_tree_sum(e.x);  // tree over the 32 warp partials (sampling.cu:29-33)
-        emin = warp_min(e.y);
-        emax = warp_max(e.z);
-        cand_ok = try_cand && (__reduce_add_sync(FULL, __float_as_uint(e.w)) == 0u);
-        ncand = __reduce_add_sync(FULL, reinterpret_cast<const uint4*>(mb)[lane * 2 + 1].x);
-        nstrict = __reduce_add_sync(FULL, reinterpret_cast<const uint4*>(mb)[lane * 2 + 1].y);
+        const uint32_t* box = exchange(pick4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow),
+                                       pick4(wnc, wns, 0u, 0u), 0u);
+        denom = warp_tree_sum(__uint_as_float(box[lane]));  // tree over the 32 warp partials (sampling.cu:29-33)
+        emin = warp_min(__uint_as_float(box[32 + lane]));
+        emax = warp_max(__uint_as_float(box[64 + lane]));
+        cand_ok = try_cand && (__reduce_add_sync(FULL, box[96 + lane]) == 0u);
+        ncand = __reduce_add_sync(FULL, box[128 + lane]);
+        nstrict = __reduce_add_sync(FULL, box[160 + lane]);
     }
     // division is monotone, so the row's min/max probability are the quotients of min/max e
     const float pmin = emin / denom, pmax = emax / denom;
@@ -419,6 +453,8 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     const float top_p = p.top_p;
     uint32_t left = 0, right = 0, rounds = 0, n_eval = 0;
     uint32_t path = 1;
+    uint32_t conv_cnt = 0, conv_left_cnt = 0;   // counts at `right` / `left` and ordered mass at `right` on return
+    float conv_mass = 0.f;
 
     // The reference's loop, replayed with the same pivots and the same decisions.  `lane_eval` returns this
     // lane's ordered masses / counts for four pivots over whatever list the caller searches.
@@ -430,7 +466,8 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     //  * bounds (candidate list only): once every element strictly inside (left, right) has one and the same
     //    value v, the remaining rounds need no data: a pivot equal to `left` selects the set of `left`, a pivot
     //    in (left, v] the set {p >= v}, a pivot above v the set of `right`; they are replayed arithmetically.
-    auto run_search = [&](auto&& lane_eval, const bool clamp, const uint32_t beta_p) -> bool {
+    auto run_search = [&](auto&& lane_eval, const bool clamp, const uint32_t beta_p, const bool sure_cnt,
+                          const uint32_t n_above) -> bool {
         const uint32_t ustar = clamp ? beta_p + 1u : 0u;
         left = __float_as_uint(pmin);
         right = __float_as_uint(pmax) + 1u;
@@ -448,7 +485,12 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             const uint32_t pv[3] = {py, pz, pw};
             uint32_t cnt[4];
             float mass[4];
-            if (!frozen) {
+            if (clamp && sure_cnt && pw <= beta_p) {
+                // All three pivots lie at or below the bound, and more than top_k elements are known to lie
+                // strictly above it: every test fails, the loop moves on, no data is needed.
+                cnt[0] = cnt[1] = cnt[2] = n_above;
+                mass[0] = mass[1] = mass[2] = 0.f;
+            } else if (!frozen) {
                 n_eval++;
                 const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
                                     __uint_as_float(max(pw, ustar)), __uint_as_float(max(left + 1u, ustar))};
@@ -486,6 +528,9 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             else if (ok[2]) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; cnt_r = cnt[2]; mass_r = mass[2]; }
             else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
         }
+        conv_cnt = cnt_r;
+        conv_mass = mass_r;
+        conv_left_cnt = cnt_x;
         return valid && (!clamp || left > beta_p);
     };
 
@@ -513,7 +558,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
                 if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
             }
         };
-        done = run_search(cand_eval, true, beta_p);
+        done = run_search(cand_eval, true, beta_p, use_cnt && nstrict > top_k, nstrict);
         if (done) {
             path = 0;
             const float thr = __uint_as_float(left);
@@ -552,7 +597,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
                 slab_pass<C, SMEM, false>(row, n, f, 0.f, m, c01, c23);
             }
         };
-        run_search(slab_eval, false, 0u);
+        run_search(slab_eval, false, 0u, false, 0u);
         // recount at the threshold (sampling.cu:657-680)
         const float thr = __uint_as_float(left);
         const int slots = (n + 3) >> 2;
@@ -575,7 +620,13 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // same tree value as the butterfly, and the warp values are then added in warp order.
     float sgtp;
     uint32_t seqk, sgtk;
-    {
+    if (path == 0 && !early_exit) {
+        // The bracket closed (right == left + 1): the set at `right` is exactly {p > threshold}, and its count
+        // and ordered mass were carried along by the search; the ties are the rest of the set at `left`.
+        sgtp = conv_mass;
+        sgtk = conv_cnt;
+        seqk = conv_left_cnt - conv_cnt;
+    } else {
         const float m[4] = {gtp, 0.f, 0.f, 0.f};
         uint32_t cnt[4], d0, d1;
         float mass[4];
@@ -596,23 +647,23 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // ---- lane pick (sampling.cu:699-723) -----------------------------------------------------
     const float actual_p = gtp + (thr * eqk) * comp;
     const float incl = warp_scan_desc(actual_p, lane);
-    {
-        const float wt = __shfl_sync(FULL, incl, 31);
-        post(make_uint4(__float_as_uint(wt), 0, 0, 0), make_uint4(0, 0, 0, 0));
-    }
-    exchange_sync();
-    mb = mbox + phase * 64;
-    phase ^= 1;
+    const uint32_t* lbox = exchange(__float_as_uint(__shfl_sync(FULL, incl, 31)), 0u, 0u);   // word 0: warp total
     float pre_prev = 0.f, sum_p;   // prefix of the warps before mine; total
     int own_w = -1;                // first warp whose inclusive prefix reaches randp
     float randp;
     {
         // sequential prefix over the warp totals (sampling.cu:85-92)
-        float s0 = mb[0].x;
+        const float4* wt4 = reinterpret_cast<const float4*>(lbox);
         float pre[kWarps];
-        pre[0] = s0;
+        float s0 = 0.f;
 #pragma unroll
-        for (int w = 1; w < kWarps; w++) { s0 += mb[w * 2].x; pre[w] = s0; }
+        for (int w4 = 0; w4 < 8; w4++) {
+            const float4 q = wt4[w4];
+            s0 = (w4 == 0) ? q.x : s0 + q.x; pre[4 * w4] = s0;
+            s0 += q.y; pre[4 * w4 + 1] = s0;
+            s0 += q.z; pre[4 * w4 + 2] = s0;
+            s0 += q.w; pre[4 * w4 + 3] = s0;
+        }
         sum_p = s0;
         randp = sum_p * ux;
 #pragma unroll
