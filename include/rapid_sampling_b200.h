@@ -128,6 +128,41 @@ int rs_sample_static_scratch(const float* logits_device, int64_t B, int64_t T, i
                              void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
                              double presence_penalty, double repetition_penalty, double penalty_decay, void* stream);
 
+/*
+ * Vocab-parallel sampling: every GPU holds V_local = V_global / world columns of each row, as a tensor-parallel
+ * lm_head produces them.  No counterpart in the reference (single GPU only, no collective in sampling.cu); the
+ * sampling semantics are those of its kernels evaluated on the union of the shards.  The call is cut into
+ * stages; between two stages the host reduces a small region of the workspace across ranks (NCCL):
+ *
+ *   stage            then reduce (op) over ranks             workspace region (offsets from rs_vp_layout, floats)
+ *   RS_VP_MAX        MAX   B floats                          [0] row maxima
+ *   RS_VP_SUM        SUM   B floats                          [1] softmax denominators
+ *   RS_VP_ROUND r    SUM   B*15*2 floats (round r's slice)   [2] + r*B*30: counts and masses at 15 pivots, r = 0..7
+ *   RS_VP_TALLY      SUM   B*4 floats                        [3] count above / mass above / ties at the threshold
+ *   RS_VP_WEIGHT     SUM   B*world floats                    [4] kept weight per shard (owner election)
+ *   RS_VP_PICK       MAX   B int32                           [5] sampled id + 1 (0 from non-owners)
+ *   RS_VP_PENALTY    --                                      updates this shard's penalty columns in place
+ *
+ * Every rank holds a replica of `states` (same seed) and advances it identically.  Results are deterministic and
+ * identical on all ranks; they are not bit-identical to the single-GPU kernel (different summation order).
+ */
+#define RS_VP_ROUNDS 8
+enum { RS_VP_MAX = 0, RS_VP_SUM = 1, RS_VP_ROUND = 2, RS_VP_TALLY = 3, RS_VP_WEIGHT = 4, RS_VP_PICK = 5, RS_VP_PENALTY = 6 };
+typedef struct rs_vp_call {
+    const float* logits;      /* device, (B, T, V_local) contiguous: this rank's columns; position T-1 is read   */
+    float* penalties;         /* device, (B, V_local) or NULL                                                    */
+    void* states;             /* device, B * RS_STATE_BYTES, a replica of the same states on every rank          */
+    void* workspace;          /* device, rs_vp_workspace_bytes(B, world) bytes                                   */
+    void* stream;             /* cudaStream_t                                                                    */
+    int64_t B, T, V_local, V_global, col0;   /* col0 = global index of this shard's first column               */
+    int64_t top_k;
+    double temperature, top_p, presence_penalty, repetition_penalty, penalty_decay;
+    int32_t rank, world;
+} rs_vp_call;
+size_t rs_vp_workspace_bytes(int64_t B, int32_t world);
+int rs_vp_layout(int64_t B, int32_t world, int64_t offsets_floats[6]);
+int rs_vp_stage(const rs_vp_call* call, int32_t stage, int32_t round);
+
 /* Reads the device status word of `workspace_device` (synchronises `stream`): RS_OK or RS_ERR_TIMEOUT. */
 int rs_device_status(void* workspace_device, void* stream);
 

@@ -38,12 +38,12 @@ def _run(cmd, verbose):
 
 
 def build_lib(force=False, verbose=False, ptxas_v=False):
-    srcs = [os.path.join(CSRC, "rs_sampler.cu"), os.path.join(CSRC, "rs_device.cuh"),
-            os.path.join(INCLUDE, "rapid_sampling_b200.h")]
+    srcs = [os.path.join(CSRC, "rs_sampler.cu"), os.path.join(CSRC, "rs_vocab_parallel.cu"),
+            os.path.join(CSRC, "rs_device.cuh"), os.path.join(INCLUDE, "rapid_sampling_b200.h")]
     if not force and _newer(LIB, srcs):
         return LIB
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_v else []) + ["-shared", "-o", LIB, srcs[0]]
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_v else []) + ["-shared", "-o", LIB, srcs[0], srcs[1]]
     _run(cmd, verbose or ptxas_v)
     return LIB
 

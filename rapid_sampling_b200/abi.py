@@ -17,7 +17,7 @@ RS_STATE_BYTES = 64
 RS_STATIC_SCRATCH_FLOATS = 4194304
 
 SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_static_scratch",
-           "rs_device_status", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_status_string",
+           "rs_device_status", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_stage", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
 
@@ -27,6 +27,17 @@ class Trace(C.Structure):
                [(n, C.c_uint32) for n in ("left", "seqk", "sgtk", "rounds", "idxt", "early_exit")] + \
                [("rnd", C.c_uint32 * 4), ("token", C.c_int32), ("path", C.c_uint32), ("ncand", C.c_uint32), ("t_ns", C.c_uint32 * 10)]
 
+
+class VpCall(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("penalties", C.c_void_p), ("states", C.c_void_p), ("workspace", C.c_void_p),
+                ("stream", C.c_void_p), ("B", C.c_int64), ("T", C.c_int64), ("V_local", C.c_int64),
+                ("V_global", C.c_int64), ("col0", C.c_int64), ("top_k", C.c_int64), ("temperature", C.c_double),
+                ("top_p", C.c_double), ("presence_penalty", C.c_double), ("repetition_penalty", C.c_double),
+                ("penalty_decay", C.c_double), ("rank", C.c_int32), ("world", C.c_int32)]
+
+
+VP_MAX, VP_SUM, VP_ROUND, VP_TALLY, VP_WEIGHT, VP_PICK, VP_PENALTY = range(7)
+VP_ROUNDS = 8
 
 _lib = None
 
@@ -48,6 +59,10 @@ def load():
     L.rs_sample_debug.argtypes = common + [vp, C.c_size_t, vp, vp, vp]
     L.rs_sample_host.argtypes = common + [vp, vp, vp, C.c_size_t, vp]
     L.rs_sample_static_scratch.argtypes = common + [vp]
+    L.rs_vp_workspace_bytes.argtypes = [i64, C.c_int32]
+    L.rs_vp_workspace_bytes.restype = C.c_size_t
+    L.rs_vp_layout.argtypes = [i64, C.c_int32, C.POINTER(C.c_int64)]
+    L.rs_vp_stage.argtypes = [C.POINTER(VpCall), C.c_int32, C.c_int32]
     L.rs_device_status.argtypes = [vp, vp]
     L.rs_set_cluster_override.argtypes = [C.c_int]
     L.rs_set_path_override.argtypes = [C.c_int]

@@ -1,0 +1,100 @@
+"""Vocab-parallel sampling across the GPUs of one node: each rank holds V/N columns of every row.
+
+The driver below owns the SEQUENCE of stages and collectives; the per-shard arithmetic is done by a
+`compute` object -- the CUDA kernels behind ``rs_vp_stage`` (default), or any object with the same
+``stage(name, round)`` method operating on the same workspace regions (the CPU test-suite plugs a numpy
+model in and runs the driver over gloo).  One sampling call = 13 small collectives:
+
+    MAX(row maxima) . SUM(denominators) . 8 x SUM(counts and masses at 15 pivots) . SUM(threshold tallies) .
+    SUM(kept weight per shard) . MAX(sampled id + 1)
+
+Every rank derives the same search bracket, the same owner shard and the same id from the same reduced
+numbers; nothing but those numbers crosses the links.  The reference has no multi-GPU mode (no collective
+anywhere in sampling.cu); the semantics are those of its kernels on the union of the shards.
+"""
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import abi
+
+STAGES = ("max", "sum", "round", "tally", "weight", "pick", "penalty")
+
+
+class CudaCompute:
+    """Runs the stages with the library's kernels on the current CUDA device."""
+
+    def __init__(self):
+        self.L = abi.load()
+        self.call = abi.VpCall()
+
+    def bind(self, s, logits, states, penalties, temperature, top_k, top_p, presence, repetition, decay):
+        c = self.call
+        c.logits, c.states, c.workspace = logits.data_ptr(), states.data_ptr(), s.ws.data_ptr()
+        c.penalties = penalties.data_ptr() if penalties is not None else None
+        c.stream = torch.cuda.current_stream().cuda_stream
+        c.B, c.T, c.V_local, c.V_global, c.col0 = s.B, s.T, s.V_local, s.V_global, s.col0
+        c.top_k, c.temperature, c.top_p = top_k, temperature, top_p
+        c.presence_penalty, c.repetition_penalty, c.penalty_decay = presence, repetition, decay
+        c.rank, c.world = s.rank, s.world
+
+    def stage(self, name, rnd=0):
+        rc = self.L.rs_vp_stage(C.byref(self.call), STAGES.index(name), rnd)
+        if rc != 0:
+            if rc in (abi.RS_ERR_VOCAB, abi.RS_ERR_BATCH, abi.RS_ERR_TEMPERATURE):
+                raise ValueError(abi.status_string(rc))
+            raise RuntimeError(abi.status_string(rc))
+
+
+class VocabParallelSampler:
+    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1):
+        if V_global % world or (V_global // world) % 4:
+            raise ValueError("V=%d cannot be split into %d shards of a multiple of 4 columns" % (V_global, world))
+        self.B, self.T, self.V_global, self.rank, self.world, self.group = B, T, V_global, rank, world, group
+        self.V_local = V_global // world
+        self.col0 = rank * self.V_local
+        L = abi.load()
+        off = (C.c_int64 * 6)()
+        L.rs_vp_layout(B, world, off)
+        n = L.rs_vp_workspace_bytes(B, world) // 4
+        self.ws = torch.zeros(n, dtype=torch.float32, device=device)
+        o = [int(x) for x in off]
+        R, P = abi.VP_ROUNDS, 15
+        self.gmax = self.ws[o[0]:o[0] + B]
+        self.gsum = self.ws[o[1]:o[1] + B]
+        self.tallies = [self.ws[o[2] + r * B * P * 2:o[2] + (r + 1) * B * P * 2] for r in range(R)]
+        self.gtally = self.ws[o[3]:o[3] + B * 4]
+        self.weights = self.ws[o[4]:o[4] + B * world]
+        self.ids = self.ws[o[5]:o[5] + B].view(torch.int32)
+        self.compute = compute or CudaCompute()
+
+    def _reduce(self, t, op):
+        if self.world > 1:
+            dist.all_reduce(t, op=op, group=self.group)
+
+    def sample(self, logits, states, temperature, top_k, top_p, penalties=None, presence_penalty=0.0,
+               repetition_penalty=0.0, penalty_decay=0.0):
+        """logits: this rank's (B, V_local) or (B, T, V_local) fp32 shard; states: replica of setup_rand(seed, B).
+        Returns int32 (B,) global token ids, identical on every rank; states / penalties updated in place."""
+        assert logits.shape[-1] == self.V_local and logits.dtype == torch.float32
+        assert (logits.shape[1] if logits.dim() == 3 else 1) == self.T
+        c = self.compute
+        c.bind(self, logits, states, penalties, float(temperature), int(top_k), float(top_p), float(presence_penalty),
+               float(repetition_penalty), float(penalty_decay))
+        c.stage("max")
+        self._reduce(self.gmax, dist.ReduceOp.MAX)
+        c.stage("sum")
+        self._reduce(self.gsum, dist.ReduceOp.SUM)
+        for r in range(abi.VP_ROUNDS):
+            c.stage("round", r)
+            self._reduce(self.tallies[r], dist.ReduceOp.SUM)
+        c.stage("tally")
+        self._reduce(self.gtally, dist.ReduceOp.SUM)
+        c.stage("weight")
+        self._reduce(self.weights, dist.ReduceOp.SUM)
+        c.stage("pick")
+        self._reduce(self.ids, dist.ReduceOp.MAX)
+        if penalties is not None:
+            c.stage("penalty")
+        return self.ids - 1

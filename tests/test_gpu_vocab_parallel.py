@@ -1,0 +1,170 @@
+"""GPU: the vocab-parallel kernels (rs_vp_stage through the C ABI).  N ranks are emulated on one GPU by running
+every rank's stage back to back and reducing their workspace regions by hand -- the same numbers NCCL would
+deliver -- so the multi-rank arithmetic is checked without several GPUs.  With >= 2 GPUs visible the real NCCL
+path is exercised as well."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import kept_set_flips_ok, make_logits
+from oracle import cpu_ref
+
+pytestmark = pytest.mark.gpu
+
+
+def emulated_sample(samplers, shards, states, temp, k, p, pens=None):
+    """Drives N single-process 'ranks' through the stage sequence of VocabParallelSampler.sample."""
+    from rapid_sampling_b200 import abi
+    N = len(samplers)
+    for r, s in enumerate(samplers):
+        s.compute.bind(s, shards[r], states[r], None if pens is None else pens[r], temp, k, p, 0.1, 0.2, 0.5)
+
+    def step(name, rnd, region, op):
+        for s in samplers:
+            s.compute.stage(name, rnd)
+        if region is not None:
+            stack = torch.stack([region(s) for s in samplers])
+            red = stack.max(dim=0).values if op == "max" else stack.sum(dim=0)
+            for s in samplers:
+                region(s).copy_(red)
+    step("max", 0, lambda s: s.gmax, "max")
+    step("sum", 0, lambda s: s.gsum, "sum")
+    for r in range(abi.VP_ROUNDS):
+        step("round", r, lambda s, r=r: s.tallies[r], "sum")
+    step("tally", 0, lambda s: s.gtally, "sum")
+    step("weight", 0, lambda s: s.weights, "sum")
+    step("pick", 0, lambda s: s.ids, "max")
+    if pens is not None:
+        step("penalty", 0, None, None)
+    return [s.ids - 1 for s in samplers]
+
+
+@pytest.mark.parametrize("N", [1, 2, 8])
+def test_emulated_ranks_agree_and_match_float64_kept_set(abi, N):
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    B, V = 8, 32768
+    full = make_logits("peaked", B, V, 4, torch)
+    samplers = [VocabParallelSampler(B, V, r, N) for r in range(N)]
+    shards = [full[:, s.col0:s.col0 + s.V_local].contiguous().cuda() for s in samplers]
+    states = [abi.setup_rand(9, B) for _ in range(N)]
+    pens = [torch.zeros(B, s.V_local, device="cuda") for s in samplers]
+    pen64 = torch.zeros(B, V)
+    for temp, k, p in [(0.8, 50, 0.9), (1.0, -1, 0.5), (1.0, -1, 1.0), (0.7, 1, 0.0)]:
+        ids = emulated_sample(samplers, shards, states, temp, k, p, pens)
+        torch.cuda.synchronize()
+        for r in range(1, N):
+            assert torch.equal(ids[r], ids[0])
+            assert torch.equal(states[r], states[0])
+        d = cpu_ref.distribution(full, temp, k, p, penalties=pen64)
+        got = ids[0].cpu().numpy()
+        for b in range(B):
+            assert 0 <= got[b] < V
+            # the sampled id lies in the float64 kept set, or ties with its boundary within fp32 rounding
+            assert bool(d["kept"][b][got[b]]) or abs(float(d["probs"][b][got[b]]) - float(d["v"][b])) <= 1e-5 * float(d["v"][b])
+        hit = torch.zeros(B, V)
+        for b in range(B):
+            hit[b, got[b]] = 0.1 if pen64[b, got[b]] == 0 else 0.2
+        pen64 = pen64 * 0.5 + hit
+        cat = torch.cat([x.cpu() for x in pens], dim=1)
+        assert torch.allclose(cat, pen64, rtol=1e-6, atol=0)
+
+
+def test_threshold_matches_single_gpu_kernel(abi):
+    """Same kept set as the single-GPU sampler (whose threshold is bit-identical to the reference's)."""
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    B, V, N = 4, 65536, 4
+    full = make_logits("normal3", B, V, 6, torch)
+    _, probs, tr = abi.sample(full.cuda(), abi.setup_rand(1, B), 0.9, -1, 0.8, debug=True)
+    samplers = [VocabParallelSampler(B, V, r, N) for r in range(N)]
+    shards = [full[:, s.col0:s.col0 + s.V_local].contiguous().cuda() for s in samplers]
+    emulated_sample(samplers, shards, [abi.setup_rand(1, B) for _ in range(N)], 0.9, -1, 0.8)
+    torch.cuda.synchronize()
+    d = cpu_ref.distribution(full, 0.9, -1, 0.8)
+    s0 = samplers[0]
+    g = s0.gtally.cpu().numpy().reshape(B, 4)
+    for b in range(B):
+        kept_single = int((probs[b] >= tr[b].threshold).sum())
+        kept_vp = int(g[b, 0] + g[b, 2])
+        assert abs(kept_single - kept_vp) <= 2           # summation order may move the boundary by a token
+        assert abs(kept_vp - int(d["kept"][b].sum())) <= 2
+
+
+def test_chi_square_vocab_parallel(abi):
+    """10^6 draws through 4 emulated ranks against the float64 sampling weights."""
+    from scipy import stats
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    V, R, CALLS, N = 8192, 1000, 1000, 4
+    row = make_logits("normal3", 1, V, 71, torch)
+    full = row.expand(R, V).contiguous()
+    samplers = [VocabParallelSampler(R, V, r, N) for r in range(N)]
+    shards = [full[:, s.col0:s.col0 + s.V_local].contiguous().cuda() for s in samplers]
+    states = [abi.setup_rand(5, R) for _ in range(N)]
+    hist = torch.zeros(V, dtype=torch.int64, device="cuda")
+    for _ in range(CALLS):
+        ids = emulated_sample(samplers, shards, states, 0.9, 64, 0.9)
+        hist += torch.bincount(ids[0].long(), minlength=V)
+    hist = hist.cpu().numpy().astype(np.float64)
+    w = cpu_ref.distribution(row, 0.9, 64, 0.9)["weights"][0].numpy()
+    exp = w / w.sum() * R * CALLS
+    assert hist[exp == 0].sum() <= 2          # a boundary tie may admit a token the float64 set excludes
+    order = np.argsort(-exp)
+    e, o = exp[order], hist[order]
+    ce, cobs, ae, ao = [], [], 0.0, 0.0
+    for ei, oi in zip(e, o):
+        if ei == 0:
+            break
+        ae += ei; ao += oi
+        if ae >= 5:
+            ce.append(ae); cobs.append(ao); ae = ao = 0.0
+    if ae > 0:
+        ce[-1] += ae; cobs[-1] += ao
+    ce, cobs = np.array(ce), np.array(cobs)
+    chi2 = ((cobs - ce) ** 2 / ce).sum()
+    assert stats.chi2.sf(chi2, len(ce) - 1) > 1e-4, chi2
+
+
+def _nccl_worker(rank, world, port, q):
+    import os, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path.insert(0, root); sys.path.insert(0, os.path.join(root, "tests"))
+    import torch.distributed as dist
+    from helpers import Abi, make_logits as ml
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    B, V = 8, 65536
+    full = ml("peaked", B, V, 4, torch)
+    s = VocabParallelSampler(B, V, rank, world)
+    shard = full[:, s.col0:s.col0 + s.V_local].contiguous().cuda()
+    st = Abi().setup_rand(9, B)
+    out = [s.sample(shard, st, 0.8, 50, 0.9).cpu().numpy() for _ in range(3)]
+    q.put((rank, out))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_nccl_two_gpus_match_emulation(abi):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    sk = socket.socket(); sk.bind(("127.0.0.1", 0)); port = sk.getsockname()[1]; sk.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_nccl_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    B, V = 8, 65536
+    full = make_logits("peaked", B, V, 4, torch)
+    samplers = [VocabParallelSampler(B, V, r, 2) for r in range(2)]
+    shards = [full[:, s.col0:s.col0 + s.V_local].contiguous().cuda() for s in samplers]
+    states = [abi.setup_rand(9, B) for _ in range(2)]
+    for call in range(3):
+        want = emulated_sample(samplers, shards, states, 0.8, 50, 0.9)[0].cpu().numpy()
+        assert np.array_equal(res[0][call], want) and np.array_equal(res[1][call], want)
