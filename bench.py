@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 L2_BYTES = 126 * 1000 * 1000
 # per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of sampler_kernel from the ncu
 # captures summarised under profiles/, keyed by workload; None where no capture exists.
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {"C2": 1.114e6, "C3": 38.99e6, "C4": 160.8e6}
 
 
 def workload(name):
@@ -163,6 +163,67 @@ def cpu_torch_f64(w, budget_s=6.0, max_calls=16):
             "cpu_count": os.cpu_count()}
 
 
+def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch, dist):
+    """Strong scaling over the vocabulary: the batch is fixed, every rank streams V/N columns of every row and the
+    cutoff search is reduced over NVLink (13 small NCCL collectives per call)."""
+    from rapid_sampling_b200.sharding import setup_rand_rows
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    B, T, V = w["B"], w["T"], w["V"]
+    s = VocabParallelSampler(B, V, rank, world, T=T)
+    pool_n = 2 if V * B * T * 4 // world > 256 * 2 ** 20 else 4
+    pool = []
+    for i in range(pool_n):   # the same full tensor on every rank (same seed), sliced: shards of one logical row set
+        full = gen_logits(dict(w, T=1), w["seed"] + 1000 * i, dev, torch)
+        shard = full[:, s.col0:s.col0 + s.V_local]
+        pool.append((shard.unsqueeze(1).expand(B, T, s.V_local).contiguous() if T > 1 else shard.contiguous()))
+        del full
+    states = setup_rand_rows(w["seed"], 0, B)
+    pen = torch.zeros(B, s.V_local, device=dev) if w["rep"] else None
+
+    def call(lg):
+        return s.sample(lg, states, w["temperature"], w["top_k"], w["top_p"], penalties=pen, presence_penalty=0.1,
+                        repetition_penalty=0.1, penalty_decay=0.95)
+    for i in range(Wm):
+        call(pool[i % pool_n])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(K):
+        call(pool[i % pool_n])
+    e1.record()
+    torch.cuda.synchronize()
+    total_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t[0])
+    clk = clocks.stop()
+    if rank == 0:
+        ms = total_ms / K
+        alg = 4 * V * B            # logits of the read position, once, over all shards
+        peak = 6650.0
+        try:
+            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        except Exception:
+            pass
+        ach = alg / (ms * 1e-3) / 1e9
+        line = dict(base, impl="ours", scaling="strong", value=B * K / (total_ms * 1e-3), ms_per_step=ms, median_us=ms * 1e3,
+                    clocks=clk, gpu_launches=K * 13,
+                    roofline={"bound": "hbm", "kernel": "vp_round_kernel (x8) + 5 stage kernels", "achieved": ach,
+                              "peak": peak * world, "unit": "GB/s", "frac": ach / (peak * world),
+                              "algorithmic_bytes_per_launch": alg, "traffic": None,
+                              "note": "12 streaming passes per call and 13 latency-bound collectives"})
+        line["config"]["parallelism"] = "vocab-parallel x%d (V/N = %d columns per GPU, NCCL all-reduce per search round)" % (world, V // world)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -171,6 +232,7 @@ def main():
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--vp", action="store_true", help="vocab-parallel: every rank holds V/N columns of every row")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -200,6 +262,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+
+    if a.vp:
+        return bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch, dist)
 
     if a.impl == "ours":
         import rapid_sampling_b200 as rs
