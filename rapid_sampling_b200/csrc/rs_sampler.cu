@@ -124,6 +124,29 @@ __device__ __forceinline__ float scaled_fast(float l, float scale) {
     const float x = l * scale;
     return (fabsf(x) <= FLT_MAX) ? x : sanitize(x);
 }
+// The rare path, kept out of line so that the streaming loops stay short.
+__device__ __forceinline__ float4 sanitize4(float4 v) {
+    return make_float4(sanitize(v.x), sanitize(v.y), sanitize(v.z), sanitize(v.w));
+}
+// Four scaled logits; a single test per group finds any Inf / NaN product (x * 0 is NaN exactly for those).
+__device__ __forceinline__ float4 scaled4(float4 l, float scale) {
+    float4 v = make_float4(l.x * scale, l.y * scale, l.z * scale, l.w * scale);
+    const float probe = fmaf(v.w, 0.f, fmaf(v.z, 0.f, fmaf(v.y, 0.f, v.x * 0.f)));
+    if (probe != probe) v = sanitize4(v);
+    return v;
+}
+// Appends the candidates of one float4 group to the lane's list (rare; out of line).
+__device__ __forceinline__ void append_candidates(float4 v, float beta_e, float* list, int stride4, int cap, int& nc, int& ns) {
+    const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        if (e[j] >= beta_e) {
+            if (nc < cap) list[(nc >> 2) * stride4 + (nc & 3)] = e[j];
+            nc++;
+            ns += (e[j] > beta_e) ? 1 : 0;
+        }
+    }
+}
 
 template <int C, bool SMEM>
 __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
@@ -170,10 +193,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
             v.z = scaled_logit(v.z, q4.z, true, p.scale);
             v.w = scaled_logit(v.w, q4.w, true, p.scale);
         } else {
-            v.x = scaled_fast(v.x, p.scale);
-            v.y = scaled_fast(v.y, p.scale);
-            v.z = scaled_fast(v.z, p.scale);
-            v.w = scaled_fast(v.w, p.scale);
+            v = scaled4(v, p.scale);
         }
         return v;
     };
@@ -349,10 +369,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
 #pragma unroll 8
         for (int s = 0; s < Kt; s++) {
             float4 v = SMEM ? row.ld(s) : __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
-            v.x = scaled_fast(v.x, p.scale);
-            v.y = scaled_fast(v.y, p.scale);
-            v.z = scaled_fast(v.z, p.scale);
-            v.w = scaled_fast(v.w, p.scale);
+            v = scaled4(v, p.scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
             if (SMEM) row.st(s, v);
         }
@@ -402,17 +419,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         const float hi = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
         emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
         emax = fmaxf(emax, hi);
-        if (hi >= beta_e) {
-            const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                if (e[j] >= beta_e) {
-                    if (nc < cap) cand_at(nc) = e[j];
-                    nc++;
-                    ns += (e[j] > beta_e) ? 1 : 0;
-                }
-            }
-        }
+        if (hi >= beta_e) append_candidates(v, beta_e, cand + t * 4, L * 4, cap, nc, ns);
     }
     stamp(4);   // pass 2 done
     acc = warp_tree_sum(acc);
