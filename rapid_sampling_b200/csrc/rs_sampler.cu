@@ -406,9 +406,7 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     // elements with e >= beta_e are appended, in order, to this lane's candidate list -----------
     float acc = 0.f, emin = INFINITY, emax = -INFINITY;
     int nc = 0, ns = 0;   // candidates, and those strictly above the bound
-#pragma unroll (SMEM ? 2 : 4)
-    for (int s = 0; s < Kt; s++) {
-        float4 v = xload(s);
+    auto pass2_slot = [&](float4 v) {
         v.x = exp2f(v.x - mx);
         v.y = exp2f(v.y - mx);
         v.z = exp2f(v.z - mx);
@@ -420,6 +418,49 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
         emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
         emax = fmaxf(emax, hi);
         if (hi >= beta_e) append_candidates(v, beta_e, cand + t * 4, L * 4, cap, nc, ns);
+    };
+    if (SMEM) {
+#pragma unroll 2
+        for (int s = 0; s < Kt; s++) pass2_slot(row.ld(s));
+    } else {
+        // streaming variant: the loads of a group of slots are issued together, then consumed in order
+        const float4* l4 = reinterpret_cast<const float4*>(lrow) + tg;
+        if (rep) {
+            constexpr int G = 4;
+            const float4* q4p = reinterpret_cast<const float4*>(prow) + tg;
+            for (int s0 = 0; s0 < Kt; s0 += G) {
+                float4 lb[G], qb[G];
+#pragma unroll
+                for (int j = 0; j < G; j++) {
+                    if (s0 + j < Kt) {
+                        lb[j] = __ldg(l4 + (s0 + j) * kLanes);
+                        qb[j] = __ldcg(q4p + (s0 + j) * kLanes);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < G; j++) {
+                    if (s0 + j < Kt) {
+                        float4 v = lb[j];
+                        v.x = scaled_logit(v.x, qb[j].x, true, p.scale);
+                        v.y = scaled_logit(v.y, qb[j].y, true, p.scale);
+                        v.z = scaled_logit(v.z, qb[j].z, true, p.scale);
+                        v.w = scaled_logit(v.w, qb[j].w, true, p.scale);
+                        pass2_slot(v);
+                    }
+                }
+            }
+        } else {
+            constexpr int G = 8;
+            for (int s0 = 0; s0 < Kt; s0 += G) {
+                float4 lb[G];
+#pragma unroll
+                for (int j = 0; j < G; j++)
+                    if (s0 + j < Kt) lb[j] = __ldg(l4 + (s0 + j) * kLanes);
+#pragma unroll
+                for (int j = 0; j < G; j++)
+                    if (s0 + j < Kt) pass2_slot(scaled4(lb[j], p.scale));
+            }
+        }
     }
     stamp(4);   // pass 2 done
     acc = warp_tree_sum(acc);
