@@ -149,7 +149,7 @@ __device__ __forceinline__ void append_candidates(float4 v, float beta_e, float*
 }
 
 template <int C, bool SMEM>
-__global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
+__global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler_kernel(const Params p) {
     constexpr int L = kLanes / C;
     constexpr int WPC = L / 32;  // warps per CTA
     constexpr unsigned FULL = 0xffffffffu;
@@ -400,86 +400,104 @@ __global__ void __launch_bounds__(kLanes / C) sampler_kernel(const Params p) {
     const bool try_cand = (sel_rank > 0);
     // Candidates are defined in the domain of e = exp2f(x - max): division by the denominator is
     // monotone, so {e >= beta_e} contains every element whose probability exceeds beta_e / denom.
-    const float beta_e = try_cand ? exp2f(beta_x - mx) : INFINITY;
+    float beta_e = try_cand ? exp2f(beta_x - mx) : INFINITY;
 
     // ---- pass 2: e = exp2f(x - max), ordered denominator (sampling.cu:560-572); min/max of e;
-    // elements with e >= beta_e are appended, in order, to this lane's candidate list -----------
-    float acc = 0.f, emin = INFINITY, emax = -INFINITY;
-    int nc = 0, ns = 0;   // candidates, and those strictly above the bound
-    auto pass2_slot = [&](float4 v) {
-        v.x = exp2f(v.x - mx);
-        v.y = exp2f(v.y - mx);
-        v.z = exp2f(v.z - mx);
-        v.w = exp2f(v.w - mx);
-        float em = 0.f;
-        em += v.x; em += v.y; em += v.z; em += v.w;
-        acc += em;
-        const float hi = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-        emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
-        emax = fmaxf(emax, hi);
-        if (hi >= beta_e) append_candidates(v, beta_e, cand + t * 4, L * 4, cap, nc, ns);
-    };
-    if (SMEM) {
-#pragma unroll 2
-        for (int s = 0; s < Kt; s++) pass2_slot(row.ld(s));
-    } else {
-        // streaming variant: the loads of a group of slots are issued together, then consumed in order
-        const float4* l4 = reinterpret_cast<const float4*>(lrow) + tg;
-        if (rep) {
-            constexpr int G = 4;
-            const float4* q4p = reinterpret_cast<const float4*>(prow) + tg;
-            for (int s0 = 0; s0 < Kt; s0 += G) {
-                float4 lb[G], qb[G];
-#pragma unroll
-                for (int j = 0; j < G; j++) {
-                    if (s0 + j < Kt) {
-                        lb[j] = __ldg(l4 + (s0 + j) * kLanes);
-                        qb[j] = __ldcg(q4p + (s0 + j) * kLanes);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < G; j++) {
-                    if (s0 + j < Kt) {
-                        float4 v = lb[j];
-                        v.x = scaled_logit(v.x, qb[j].x, true, p.scale);
-                        v.y = scaled_logit(v.y, qb[j].y, true, p.scale);
-                        v.z = scaled_logit(v.z, qb[j].z, true, p.scale);
-                        v.w = scaled_logit(v.w, qb[j].w, true, p.scale);
-                        pass2_slot(v);
-                    }
-                }
-            }
-        } else {
-            constexpr int G = 8;
-            for (int s0 = 0; s0 < Kt; s0 += G) {
-                float4 lb[G];
-#pragma unroll
-                for (int j = 0; j < G; j++)
-                    if (s0 + j < Kt) lb[j] = __ldg(l4 + (s0 + j) * kLanes);
-#pragma unroll
-                for (int j = 0; j < G; j++)
-                    if (s0 + j < Kt) pass2_slot(scaled4(lb[j], p.scale));
-            }
-        }
-    }
-    stamp(4);   // pass 2 done
-    acc = warp_tree_sum(acc);
-    emin = warp_min(emin);
-    emax = warp_max(emax);
-    const unsigned overflow = __any_sync(FULL, nc > cap) ? 1u : 0u;
-    const uint32_t wnc = __reduce_add_sync(FULL, (uint32_t)nc), wns = __reduce_add_sync(FULL, (uint32_t)ns);
-    float denom;
+    // elements with e >= beta_e are appended, in order, to this lane's candidate list.  When the list
+    // looks too thin to settle the cutoff (not more than top_k strictly above the bound, and about less than
+    // top_p of the mass), the bound is lowered 16-fold and the pass repeated, at most twice. -----------
+    float acc, emin, emax, csum, denom;
+    int nc, ns;   // candidates, and those strictly above the bound
     bool cand_ok;
     uint32_t ncand, nstrict;
-    {
+    auto pass2 = [&](const bool last) -> bool {
+            acc = 0.f; emin = INFINITY; emax = -INFINITY;
+            nc = 0; ns = 0; csum = 0.f;
+        auto pass2_slot = [&](float4 v) {
+            v.x = exp2f(v.x - mx);
+            v.y = exp2f(v.y - mx);
+            v.z = exp2f(v.z - mx);
+            v.w = exp2f(v.w - mx);
+            float em = 0.f;
+            em += v.x; em += v.y; em += v.z; em += v.w;
+            acc += em;
+            const float hi = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+            emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
+            emax = fmaxf(emax, hi);
+            if (hi >= beta_e) {
+                append_candidates(v, beta_e, cand + t * 4, L * 4, cap, nc, ns);
+                csum += (v.x >= beta_e ? v.x : 0.f) + (v.y >= beta_e ? v.y : 0.f) + (v.z >= beta_e ? v.z : 0.f) +
+                        (v.w >= beta_e ? v.w : 0.f);
+            }
+        };
+        if (SMEM) {
+    #pragma unroll 2
+            for (int s = 0; s < Kt; s++) pass2_slot(row.ld(s));
+        } else {
+            // streaming variant: the loads of a group of slots are issued together, then consumed in order
+            const float4* l4 = reinterpret_cast<const float4*>(lrow) + tg;
+            if (rep) {
+                constexpr int G = 4;
+                const float4* q4p = reinterpret_cast<const float4*>(prow) + tg;
+                for (int s0 = 0; s0 < Kt; s0 += G) {
+                    float4 lb[G], qb[G];
+    #pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        if (s0 + j < Kt) {
+                            lb[j] = __ldg(l4 + (s0 + j) * kLanes);
+                            qb[j] = __ldcg(q4p + (s0 + j) * kLanes);
+                        }
+                    }
+    #pragma unroll
+                    for (int j = 0; j < G; j++) {
+                        if (s0 + j < Kt) {
+                            float4 v = lb[j];
+                            v.x = scaled_logit(v.x, qb[j].x, true, p.scale);
+                            v.y = scaled_logit(v.y, qb[j].y, true, p.scale);
+                            v.z = scaled_logit(v.z, qb[j].z, true, p.scale);
+                            v.w = scaled_logit(v.w, qb[j].w, true, p.scale);
+                            pass2_slot(v);
+                        }
+                    }
+                }
+            } else {
+                constexpr int G = 8;
+                for (int s0 = 0; s0 < Kt; s0 += G) {
+                    float4 lb[G];
+    #pragma unroll
+                    for (int j = 0; j < G; j++)
+                        if (s0 + j < Kt) lb[j] = __ldg(l4 + (s0 + j) * kLanes);
+    #pragma unroll
+                    for (int j = 0; j < G; j++)
+                        if (s0 + j < Kt) pass2_slot(scaled4(lb[j], p.scale));
+                }
+            }
+        }
+        stamp(4);   // pass 2 done
+        acc = warp_tree_sum(acc);
+        emin = warp_min(emin);
+        emax = warp_max(emax);
+        const unsigned overflow = __any_sync(FULL, nc > cap) ? 1u : 0u;
+        const uint32_t wnc = __reduce_add_sync(FULL, (uint32_t)nc), wns = __reduce_add_sync(FULL, (uint32_t)ns);
+        csum = warp_tree_sum(csum);
         const uint32_t* box = exchange(pick4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow),
-                                       pick4(wnc, wns, 0u, 0u), 0u);
+                                       pick4(wnc, wns, __float_as_uint(csum), 0u), 0u);
         denom = warp_tree_sum(__uint_as_float(box[lane]));  // tree over the 32 warp partials (sampling.cu:29-33)
         emin = warp_min(__uint_as_float(box[32 + lane]));
         emax = warp_max(__uint_as_float(box[64 + lane]));
         cand_ok = try_cand && (__reduce_add_sync(FULL, box[96 + lane]) == 0u);
         ncand = __reduce_add_sync(FULL, box[128 + lane]);
         nstrict = __reduce_add_sync(FULL, box[160 + lane]);
+        const float cmass = warp_tree_sum(__uint_as_float(box[192 + lane])) / denom;   // any order: a forecast only
+        const bool enough = (use_cnt && nstrict > (uint32_t)p.top_k) || cmass > p.top_p * 1.001f;
+        return !cand_ok || enough || last || !(beta_e > 0.f);
+    };
+    if (!pass2(false)) {
+        beta_e *= 0.0625f;
+        if (!pass2(false)) {
+            beta_e *= 0.0625f;
+            pass2(true);
+        }
     }
     // division is monotone, so the row's min/max probability are the quotients of min/max e
     const float pmin = emin / denom, pmax = emax / denom;
@@ -957,7 +975,8 @@ static Plan make_plan(const DeviceInfo& di, long long B, int V, int sel_rank, in
     const int forced = g_cluster_override.load();
     const int mode = g_path_override.load();
     const bool can_stream = ws_avail >= ws_bytes(B, V);
-    auto streaming = [&]() { pl.C = 8; pl.smem = false; pl.ws = ws_bytes(B, V); return pl; };
+    // the streaming variant has shared memory to spare: room for 32 candidates per lane, so that lowered bounds fit
+    auto streaming = [&]() { pl.C = 8; pl.smem = false; pl.ws = ws_bytes(B, V); if (pl.cand_slots) pl.cand_slots = 8; return pl; };
     auto onchip = [&](int C) { pl.C = C; pl.smem = true; pl.ws = 256; return pl; };
     if (forced) return fits(forced) ? onchip(forced) : streaming();
     if (mode == 2) return streaming();
@@ -991,6 +1010,7 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     if (workspace_bytes < pl.ws) return RS_ERR_WORKSPACE;
     const bool use_smem = pl.smem;
     const int C = pl.C;
+    cand_slots = pl.cand_slots;
 
     Params p;
     p.logits = logits + (T - 1) * V;
