@@ -93,6 +93,20 @@ int rs_sample_debug(const float* logits_device, int64_t B, int64_t T, int64_t V,
                     float* probs_device, rs_trace* trace_device);
 
 /*
+ * rs_sample / rs_sample_debug for logits stored as fp32, fp16 or bf16.  The reference accepts fp32 only and throws
+ * for anything else (sampling.cu:452, :976); a model head usually emits 16-bit logits, so this entry point reads
+ * them directly (half the HBM bytes per row) and widens each value exactly to fp32 before the first operation --
+ * the result is bit-identical to calling the fp32 entry point on `logits.float()`.  Rows need 8-byte alignment
+ * for the 16-bit types.  probs_device / trace_device may be NULL.
+ */
+enum { RS_DTYPE_F32 = 0, RS_DTYPE_F16 = 1, RS_DTYPE_BF16 = 2 };
+int rs_sample_typed(const void* logits_device, int32_t logits_dtype, int64_t B, int64_t T, int64_t V,
+                    float* penalties_device, void* states_device, int32_t* out_device, double temperature, int64_t top_k,
+                    double top_p, double presence_penalty, double repetition_penalty, double penalty_decay,
+                    void* workspace_device, size_t workspace_bytes, void* stream, float* probs_device,
+                    rs_trace* trace_device);
+
+/*
  * Host-buffer convenience around rs_sample for callers that hold logits in (pinned) host memory:
  * copies logits[:, T-1, :] to `staging_device` (B*V floats), samples, copies the ids back to
  * out_host and synchronises `stream`.  Penalties and states stay on the device.

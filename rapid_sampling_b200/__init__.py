@@ -45,9 +45,22 @@ def batch_sampling_repetition_temperature_topk_topp(logits, penalties, states, p
         logits, penalties, states, presence_penalty, repetition_penalty, penalty_decay, temperature, top_k, top_p)
 
 
+def batch_sampling_temperature_topk_topp_any(logits, states, temperature, top_k, top_p):
+    """Same call for fp32, fp16 or bf16 logits (the reference accepts fp32 only, sampling.cu:976). 16-bit logits are
+    read directly and widened exactly, so the ids equal those of the fp32 call on ``logits.float()``."""
+    return _load_ext().batch_sampling_temperature_topk_topp_any(logits, states, temperature, top_k, top_p)
+
+
+def batch_sampling_repetition_temperature_topk_topp_any(logits, penalties, states, presence_penalty, repetition_penalty,
+                                                        penalty_decay, temperature, top_k, top_p):
+    return _load_ext().batch_sampling_repetition_temperature_topk_topp_any(
+        logits, penalties, states, presence_penalty, repetition_penalty, penalty_decay, temperature, top_k, top_p)
+
+
 def kernel_launch_count():
     return _load_ext().kernel_launch_count()
 
 
 __all__ = ["setup_rand", "batch_sampling_temperature_topk_topp", "batch_sampling_repetition_temperature_topk_topp",
+           "batch_sampling_temperature_topk_topp_any", "batch_sampling_repetition_temperature_topk_topp_any",
            "kernel_launch_count"]

@@ -18,6 +18,8 @@
 // No tensor cores: nothing here is a contraction.  The bound is HBM bandwidth (4 bytes per
 // logit, 12 with penalties) for large batches and launch + barrier latency for tiny ones.
 #include "rs_device.cuh"
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "../../include/rapid_sampling_b200.h"
 
 #include <atomic>
@@ -31,7 +33,8 @@ namespace rs {
 enum Kind : int { kTopP = 0, kGeneral = 1, kRepetition = 2 };
 
 struct Params {
-    const float* logits;     // already offset to position T-1 of row 0
+    const void* logits;      // already offset to position T-1 of row 0; fp32, fp16 or bf16 (dtype)
+    int dtype;               // RS_DTYPE_F32 / F16 / BF16 of the logits
     long long row_stride;    // elements between consecutive rows (T*V)
     float* penalties;        // (B,V) or null
     unsigned char* states;   // B*64
@@ -148,7 +151,7 @@ __device__ __forceinline__ void append_candidates(float4 v, float beta_e, float*
     }
 }
 
-template <int C, bool SMEM>
+template <int C, bool SMEM, bool LOWP>
 __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler_kernel(const Params p) {
     constexpr int L = kLanes / C;
     constexpr int WPC = L / 32;  // warps per CTA
@@ -163,7 +166,28 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     const int Kt = (tg < V4) ? ((V4 - tg + kLanes - 1) >> 10) : 0;
     const bool rep = (p.kind == kRepetition);
     const bool use_cnt = (p.kind != kTopP);
-    const float* lrow = p.logits + (long long)b * p.row_stride;
+    const int dtype = LOWP ? p.dtype : RS_DTYPE_F32;   // fp32 rows keep a kernel of their own: no type tests in its loops
+    const char* lrow_b = reinterpret_cast<const char*>(p.logits) + (long long)b * p.row_stride * (dtype == RS_DTYPE_F32 ? 4 : 2);
+    const float* lrow = reinterpret_cast<const float*>(lrow_b);   // valid as such for fp32 logits only
+    // four consecutive logits (group g of the row) / one logit, converted exactly to fp32
+    auto ldrow4 = [&](int g) -> float4 {
+        if (!LOWP) return __ldg(reinterpret_cast<const float4*>(lrow_b) + g);
+        const uint2 r = __ldg(reinterpret_cast<const uint2*>(lrow_b) + g);
+        if (dtype == RS_DTYPE_F16) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+            return make_float4(a.x, a.y, c.x, c.y);
+        }
+        return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                           __uint_as_float(r.y & 0xffff0000u));
+    };
+    auto ldrow1 = [&](int i) -> float {
+        if (!LOWP) return reinterpret_cast<const float*>(lrow_b)[i];
+        const unsigned short h = reinterpret_cast<const unsigned short*>(lrow_b)[i];
+        if (dtype == RS_DTYPE_F16) return __half2float(__ushort_as_half(h));
+        return __uint_as_float((uint32_t)h << 16);
+    };
+    constexpr bool bulk_load = SMEM && !LOWP;   // 16-bit logits are staged through registers
     float* prow = rep ? p.penalties + (long long)b * V : nullptr;
 
     uint64_t* mbar = reinterpret_cast<uint64_t*>(smem + kMiscOff);
@@ -185,7 +209,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     // again from global memory -- the same functions on the same inputs, hence the same bits
     auto xload = [&](int s) -> float4 {
         if (SMEM) return row.ld(s);
-        float4 v = __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
+        float4 v = ldrow4(s * kLanes + tg);
         if (rep) {
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
             v.x = scaled_logit(v.x, q4.x, true, p.scale);
@@ -313,7 +337,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
             *s_token = 0;
         }
         __syncthreads();
-        if (wl == 0) {
+        if (wl == 0 && bulk_load) {
             const int kfull = V4 >> 10, rem = V4 & 1023;
             const int vl = min(max(rem - (int)crank * L, 0), L);
             const uint32_t bar = smem_addr(mbar);
@@ -345,7 +369,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     rng_peek2(rng, r0, r1, rnd4);
     const float ux = u01(r0), uy = u01(r1);
 
-    if (SMEM) {
+    if (bulk_load) {
         if (!mbar_wait_bounded(smem_addr(mbar), 0, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
     }
 
@@ -356,7 +380,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     if (rep) {
 #pragma unroll 8
         for (int s = 0; s < Kt; s++) {
-            float4 v = SMEM ? row.ld(s) : __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
+            float4 v = bulk_load ? row.ld(s) : ldrow4(s * kLanes + tg);
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
             v.x = scaled_logit(v.x, q4.x, true, p.scale);
             v.y = scaled_logit(v.y, q4.y, true, p.scale);
@@ -368,7 +392,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     } else {
 #pragma unroll 8
         for (int s = 0; s < Kt; s++) {
-            float4 v = SMEM ? row.ld(s) : __ldg(reinterpret_cast<const float4*>(lrow) + s * kLanes + tg);
+            float4 v = bulk_load ? row.ld(s) : ldrow4(s * kLanes + tg);
             v = scaled4(v, p.scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
             if (SMEM) row.st(s, v);
@@ -435,7 +459,6 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
             for (int s = 0; s < Kt; s++) pass2_slot(row.ld(s));
         } else {
             // streaming variant: the loads of a group of slots are issued together, then consumed in order
-            const float4* l4 = reinterpret_cast<const float4*>(lrow) + tg;
             if (rep) {
                 constexpr int G = 4;
                 const float4* q4p = reinterpret_cast<const float4*>(prow) + tg;
@@ -444,7 +467,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     #pragma unroll
                     for (int j = 0; j < G; j++) {
                         if (s0 + j < Kt) {
-                            lb[j] = __ldg(l4 + (s0 + j) * kLanes);
+                            lb[j] = ldrow4((s0 + j) * kLanes + tg);
                             qb[j] = __ldcg(q4p + (s0 + j) * kLanes);
                         }
                     }
@@ -466,7 +489,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
                     float4 lb[G];
     #pragma unroll
                     for (int j = 0; j < G; j++)
-                        if (s0 + j < Kt) lb[j] = __ldg(l4 + (s0 + j) * kLanes);
+                        if (s0 + j < Kt) lb[j] = ldrow4((s0 + j) * kLanes + tg);
     #pragma unroll
                     for (int j = 0; j < G; j++)
                         if (s0 + j < Kt) pass2_slot(scaled4(lb[j], p.scale));
@@ -769,7 +792,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
             const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
             float o0 = 0.f;
             if (idn < V) {
-                const float x = scaled_logit(lrow[idn], rep ? prow[idn] : 0.f, rep, p.scale);
+                const float x = scaled_logit(ldrow1(idn), rep ? prow[idn] : 0.f, rep, p.scale);
                 o0 = exp2f(x - mx) / denom;
             }
             const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
@@ -858,7 +881,7 @@ __global__ void setup_rand_kernel(unsigned char* states, unsigned long long seed
 struct DeviceInfo {
     bool ready = false;
     int sms = 0, smem_optin = 0, smem_sm = 0;
-    bool attr_set[6][2] = {};
+    bool attr_set[10][2] = {};
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_mu;
@@ -874,19 +897,19 @@ static int cuda_fail(cudaError_t e, const char* what) {
 
 static int cidx(int C) { return C == 1 ? 0 : C == 2 ? 1 : C == 4 ? 2 : C == 8 ? 3 : 4; }
 
-template <int C, bool SMEM>
-static int launch_one(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
-    auto kern = sampler_kernel<C, SMEM>;
+template <int C, bool SMEM, bool LOWP>
+static int launch_typed(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
+    auto kern = sampler_kernel<C, SMEM, LOWP>;
     {
         std::lock_guard<std::mutex> lk(g_mu);
-        if (!di.attr_set[cidx(C)][SMEM ? 1 : 0]) {
+        if (!di.attr_set[cidx(C) + (LOWP ? 5 : 0)][SMEM ? 1 : 0]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.smem_optin);
             if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
             if (C > 8) {
                 e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
                 if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(cluster)");
             }
-            di.attr_set[cidx(C)][SMEM ? 1 : 0] = true;
+            di.attr_set[cidx(C) + (LOWP ? 5 : 0)][SMEM ? 1 : 0] = true;
         }
     }
     cudaLaunchConfig_t cfg;
@@ -906,6 +929,12 @@ static int launch_one(const Params& p, int smem, cudaStream_t stream, DeviceInfo
     if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx(sampler)");
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return RS_OK;
+}
+
+template <int C, bool SMEM>
+static int launch_one(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
+    return p.dtype == RS_DTYPE_F32 ? launch_typed<C, SMEM, false>(p, smem, stream, di)
+                                   : launch_typed<C, SMEM, true>(p, smem, stream, di);
 }
 
 static int get_device(DeviceInfo** out) {
@@ -985,7 +1014,7 @@ static Plan make_plan(const DeviceInfo& di, long long B, int V, int sel_rank, in
     return streaming();
 }
 
-static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, float* penalties, void* states, int32_t* out,
+static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int64_t V, float* penalties, void* states, int32_t* out,
                        double temperature, int64_t top_k, double top_p, double presence, double repetition, double decay,
                        void* workspace, size_t workspace_bytes, void* stream, float* dbg_probs, rs_trace* dbg_trace) {
     // checks and remaps of the reference's host functions (sampling.cu:458-486, :982-1011)
@@ -993,8 +1022,10 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     if (!(B > 0 && T > 0)) return RS_ERR_BATCH;
     if (!(temperature >= 0.001 && temperature <= 1000)) return RS_ERR_TEMPERATURE;
     if (B > (1ll << 24)) return RS_ERR_LIMIT;
+    if (dtype != RS_DTYPE_F32 && dtype != RS_DTYPE_F16 && dtype != RS_DTYPE_BF16) return RS_ERR_DTYPE;
     if (!logits || !states || !out || !workspace) return RS_ERR_POINTER;
-    if (((uintptr_t)logits & 15) || ((uintptr_t)states & 15) || ((uintptr_t)penalties & 15) || ((uintptr_t)workspace & 255))
+    if (((uintptr_t)logits & (dtype == RS_DTYPE_F32 ? 15 : 7)) || ((uintptr_t)states & 15) || ((uintptr_t)penalties & 15) ||
+        ((uintptr_t)workspace & 255))
         return RS_ERR_POINTER;
     if (top_k <= 0 || top_k > V) top_k = V;
     if (top_p < 0 || top_p > 1) top_p = 1;
@@ -1013,7 +1044,8 @@ static int sample_impl(const float* logits, int64_t B, int64_t T, int64_t V, flo
     cand_slots = pl.cand_slots;
 
     Params p;
-    p.logits = logits + (T - 1) * V;
+    p.logits = (const char*)logits + (T - 1) * V * (dtype == RS_DTYPE_F32 ? 4 : 2);
+    p.dtype = dtype;
     p.row_stride = (long long)T * V;
     p.penalties = penalties;
     p.states = (unsigned char*)states;
@@ -1100,6 +1132,7 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     if (rc) return rc;
     Params p;
     p.logits = logits + (T - 1) * V;
+    p.dtype = RS_DTYPE_F32;
     p.row_stride = (long long)T * V;
     p.penalties = penalties;
     p.states = (unsigned char*)states;
@@ -1153,7 +1186,7 @@ int rs_sample(const float* logits_device, int64_t B, int64_t T, int64_t V, float
               int32_t* out_device, double temperature, int64_t top_k, double top_p, double presence_penalty,
               double repetition_penalty, double penalty_decay, void* workspace_device, size_t workspace_bytes,
               void* stream) {
-    return rs::sample_impl(logits_device, B, T, V, penalties_device, states_device, out_device, temperature, top_k, top_p,
+    return rs::sample_impl(logits_device, RS_DTYPE_F32, B, T, V, penalties_device, states_device, out_device, temperature, top_k, top_p,
                            presence_penalty, repetition_penalty, penalty_decay, workspace_device, workspace_bytes, stream,
                            nullptr, nullptr);
 }
@@ -1162,7 +1195,7 @@ int rs_sample_debug(const float* logits_device, int64_t B, int64_t T, int64_t V,
                     void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
                     double presence_penalty, double repetition_penalty, double penalty_decay, void* workspace_device,
                     size_t workspace_bytes, void* stream, float* probs_device, rs_trace* trace_device) {
-    return rs::sample_impl(logits_device, B, T, V, penalties_device, states_device, out_device, temperature, top_k, top_p,
+    return rs::sample_impl(logits_device, RS_DTYPE_F32, B, T, V, penalties_device, states_device, out_device, temperature, top_k, top_p,
                            presence_penalty, repetition_penalty, penalty_decay, workspace_device, workspace_bytes, stream,
                            probs_device, trace_device);
 }
@@ -1183,7 +1216,7 @@ int rs_sample_host(const float* logits_host, int64_t B, int64_t T, int64_t V, fl
                               (size_t)T * V * sizeof(float), (size_t)V * sizeof(float), (size_t)B, cudaMemcpyHostToDevice, st);
     }
     if (e != cudaSuccess) return rs::cuda_fail(e, "logits H2D");
-    int rc = rs::sample_impl(staging_device, B, 1, V, penalties_device, states_device, out_device, temperature, top_k,
+    int rc = rs::sample_impl(staging_device, RS_DTYPE_F32, B, 1, V, penalties_device, states_device, out_device, temperature, top_k,
                              top_p, presence_penalty, repetition_penalty, penalty_decay, workspace_device,
                              workspace_bytes, stream, nullptr, nullptr);
     if (rc) return rc;
@@ -1192,6 +1225,15 @@ int rs_sample_host(const float* logits_host, int64_t B, int64_t T, int64_t V, fl
     e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return rs::cuda_fail(e, "cudaStreamSynchronize");
     return RS_OK;
+}
+
+int rs_sample_typed(const void* logits_device, int32_t logits_dtype, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                    void* states_device, int32_t* out_device, double temperature, int64_t top_k, double top_p,
+                    double presence_penalty, double repetition_penalty, double penalty_decay, void* workspace_device,
+                    size_t workspace_bytes, void* stream, float* probs_device, rs_trace* trace_device) {
+    return rs::sample_impl(logits_device, logits_dtype, B, T, V, penalties_device, states_device, out_device, temperature,
+                           top_k, top_p, presence_penalty, repetition_penalty, penalty_decay, workspace_device,
+                           workspace_bytes, stream, probs_device, trace_device);
 }
 
 int rs_device_status(void* workspace_device, void* stream) {

@@ -32,8 +32,10 @@ at::Tensor& workspace_for(int device, cudaStream_t stream, size_t bytes) {
 }
 
 at::Tensor sample_common(at::Tensor& logits, at::Tensor* penalties, at::Tensor& states, double presence,
-                         double repetition, double decay, double temperature, int64_t top_k, double top_p) {
-    if (logits.dtype() != at::kFloat)
+                         double repetition, double decay, double temperature, int64_t top_k, double top_p,
+                         bool any_dtype = false) {
+    const bool lowp = any_dtype && (logits.dtype() == at::kHalf || logits.dtype() == at::kBFloat16);
+    if (logits.dtype() != at::kFloat && !lowp)
         throw std::invalid_argument("Logits tensor must be of type float32 (FP32), got " +
                                     std::string(logits.dtype().name()) + " !\n");
     if (!logits.is_cuda() || !states.is_cuda()) throw std::invalid_argument("logits and states must be CUDA tensors !\n");
@@ -62,8 +64,10 @@ at::Tensor sample_common(at::Tensor& logits, at::Tensor* penalties, at::Tensor& 
     const size_t wsb = rs_workspace_bytes(B, V);
     at::Tensor& ws = workspace_for(dev, stream, wsb);
     at::Tensor out = at::empty({B > 0 ? B : 0}, at::TensorOptions().dtype(at::kInt).device(logits.device()));
-    const int rc = rs_sample(logits.data_ptr<float>(), B, T, V, pen, states.data_ptr(), out.data_ptr<int32_t>(), temperature,
-                             top_k, top_p, presence, repetition, decay, ws.data_ptr(), (size_t)ws.numel(), stream);
+    const int dt = logits.dtype() == at::kHalf ? RS_DTYPE_F16 : logits.dtype() == at::kBFloat16 ? RS_DTYPE_BF16 : RS_DTYPE_F32;
+    const int rc = rs_sample_typed(logits.data_ptr(), dt, B, T, V, pen, states.data_ptr(), out.data_ptr<int32_t>(), temperature,
+                                   top_k, top_p, presence, repetition, decay, ws.data_ptr(), (size_t)ws.numel(), stream,
+                                   nullptr, nullptr);
     if (rc == RS_ERR_VOCAB) fail(rc, ", got " + std::to_string(V));
     if (rc == RS_ERR_BATCH) fail(rc, ", got B=" + std::to_string(B) + ", T=" + std::to_string(T));
     if (rc == RS_ERR_TEMPERATURE) fail(rc, ", got " + std::to_string(temperature));
@@ -94,6 +98,17 @@ at::Tensor batch_sampling_repetition_temperature_topk_topp(at::Tensor& logits, a
                          top_k, top_p);
 }
 
+// The same two calls for fp32, fp16 or bf16 logits (the reference's functions above stay fp32-only, as the reference's).
+at::Tensor sample_any(at::Tensor& logits, at::Tensor& states, double temperature, int64_t top_k, double top_p) {
+    return sample_common(logits, nullptr, states, 0.0, 0.0, 0.0, temperature, top_k, top_p, true);
+}
+at::Tensor sample_repetition_any(at::Tensor& logits, at::Tensor& penalties, at::Tensor& states, double presence_penalty,
+                                 double repetition_penalty, double penalty_decay, double temperature, int64_t top_k,
+                                 double top_p) {
+    return sample_common(logits, &penalties, states, presence_penalty, repetition_penalty, penalty_decay, temperature,
+                         top_k, top_p, true);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     namespace py = pybind11;
     m.def("setup_rand", &setup_rand, py::arg("seed"), py::arg("B"));
@@ -103,6 +118,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("top_p"));
     m.def("batch_sampling_temperature_topk_topp", &batch_sampling_temperature_topk_topp, py::arg("logits"),
           py::arg("states"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"));
+    m.def("batch_sampling_temperature_topk_topp_any", &sample_any, py::arg("logits"), py::arg("states"),
+          py::arg("temperature"), py::arg("top_k"), py::arg("top_p"));
+    m.def("batch_sampling_repetition_temperature_topk_topp_any", &sample_repetition_any, py::arg("logits"),
+          py::arg("penalties"), py::arg("states"), py::arg("presence_penalty"), py::arg("repetition_penalty"),
+          py::arg("penalty_decay"), py::arg("temperature"), py::arg("top_k"), py::arg("top_p"));
     m.def("kernel_launch_count", []() { return rs_kernel_launch_count(); });
     m.def("version", []() { return std::string(rs_version()); });
 }

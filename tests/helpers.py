@@ -90,6 +90,13 @@ class Abi:
         out = torch.empty(max(B, 0), dtype=torch.int32, device="cuda")
         ws = self.workspace(max(B, 1), max(V, 4))
         pen = penalties.data_ptr() if penalties is not None else None
+        if logits.dtype != torch.float32:     # 16-bit logits go through the typed entry point
+            dt = {torch.float16: self.abi.RS_DTYPE_F16, torch.bfloat16: self.abi.RS_DTYPE_BF16}[logits.dtype]
+            rc = self.L.rs_sample_typed(logits.data_ptr(), dt, B, T, V, pen, states.data_ptr(), out.data_ptr(), temperature,
+                                        top_k, top_p, presence, repetition, decay, ws.data_ptr(), ws.numel(), self.stream(),
+                                        None, None)
+            assert rc == 0, self.abi.status_string(rc)
+            return out
         if debug:
             probs = torch.empty(B, V, dtype=torch.float32, device="cuda")
             trace = torch.zeros(B * C.sizeof(self.abi.Trace), dtype=torch.uint8, device="cuda")

@@ -285,3 +285,39 @@ def test_host_buffer_entry_point(abi):
                               staging.data_ptr(), out_dev.data_ptr(), ws.data_ptr(), ws.numel(), abi.stream())
     assert rc == 0
     assert torch.equal(out_host, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_sixteen_bit_logits_equal_reference_on_widened_logits(abi, ref, dtype):
+    """fp16 / bf16 logits are read directly and widened exactly: ids, states and penalties must equal the
+    reference kernel run on ``logits.float()`` (the reference itself rejects 16-bit input, sampling.cu:976)."""
+    try:
+        for kind, B, V, temp, k, p, rep in [("peaked", 16, 151936, 0.8, 50, 0.9, False), ("normal3", 4, 262144, 1.0, -1, 0.3, False),
+                                            ("uniform", 4, 32768, 1.0, -1, 0.5, False), ("normal3", 32, 65536, 0.8, 50, 0.9, True),
+                                            ("special", 4, 50304, 1.3, 100, 0.9, False)]:
+            lg16 = make_logits(kind, B, V, 23, torch).to(dtype).cuda()
+            lg32 = lg16.float()
+            for mode in (0, 2, 3):
+                abi.set_path(mode)
+                s_ref, s_our = ref.setup_rand(2, B), abi.setup_rand(2, B)
+                pen_ref = torch.zeros(B, V, device="cuda") if rep else None
+                pen_our = torch.zeros(B, V, device="cuda") if rep else None
+                for _ in range(2):
+                    want = _ref_call(ref, lg32, s_ref, temp, k, p, pen_ref)
+                    got = abi.sample(lg16, s_our, temp, k, p, penalties=pen_our, presence=0.1, repetition=0.1, decay=0.95)
+                    assert torch.equal(got, want), (kind, mode)
+                assert torch.equal(s_our, s_ref)
+                if rep:
+                    assert torch.equal(pen_our, pen_ref)
+    finally:
+        abi.set_path(0)
+
+
+def test_sixteen_bit_logits_through_the_torch_api(ref):
+    import rapid_sampling_b200 as rs
+    lg = make_logits("peaked", 8, 65536, 3, torch).to(torch.bfloat16).cuda()
+    a = rs.batch_sampling_temperature_topk_topp_any(lg, rs.setup_rand(4, 8), 0.8, 50, 0.9)
+    b = ref.batch_sampling_temperature_topk_topp(lg.float(), ref.setup_rand(4, 8), 0.8, 50, 0.9)
+    assert torch.equal(a, b)
+    with pytest.raises(ValueError, match="float32"):      # the reference-named call stays fp32-only
+        rs.batch_sampling_temperature_topk_topp(lg, rs.setup_rand(4, 8), 0.8, 50, 0.9)
