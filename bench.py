@@ -232,6 +232,7 @@ def main():
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"], help="storage type of the logits (ours only)")
     ap.add_argument("--vp", action="store_true", help="vocab-parallel: every rank holds V/N columns of every row")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -286,18 +287,23 @@ def main():
         launches = lambda: 0  # noqa: E731
 
     # input pool larger than L2 so that every step reads its logits from HBM
-    row_bytes = B * T * V * 4
+    esz = 4 if (a.impl != "ours" or a.dtype == "f32") else 2
+    row_bytes = B * T * V * esz
     pool_n = max(2, min(256, -(-int(1.6 * L2_BYTES) // row_bytes)))
     if a.config == "C5":
         pool_n = 2
-    pool = [gen_logits(w, w["seed"] + 1000 * i + 7 * rank, dev, torch) for i in range(pool_n)]
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[a.dtype if a.impl == "ours" else "f32"]
+    pool = [gen_logits(w, w["seed"] + 1000 * i + 7 * rank, dev, torch).to(tdt) for i in range(pool_n)]
     pen = torch.zeros(B, V, device=dev) if w["rep"] else None
+
+    lowp = (a.impl == "ours" and a.dtype != "f32")
+    f_plain = ext.batch_sampling_temperature_topk_topp_any if lowp else ext.batch_sampling_temperature_topk_topp
+    f_rep = ext.batch_sampling_repetition_temperature_topk_topp_any if lowp else ext.batch_sampling_repetition_temperature_topk_topp
 
     def call(lg):
         if w["rep"]:
-            return ext.batch_sampling_repetition_temperature_topk_topp(lg, pen, states, 0.1, 0.1, 0.95, w["temperature"],
-                                                                       w["top_k"], w["top_p"])
-        return ext.batch_sampling_temperature_topk_topp(lg, states, w["temperature"], w["top_k"], w["top_p"])
+            return f_rep(lg, pen, states, 0.1, 0.1, 0.95, w["temperature"], w["top_k"], w["top_p"])
+        return f_plain(lg, states, w["temperature"], w["top_k"], w["top_p"])
 
     def sync_all():
         torch.cuda.synchronize()
@@ -353,7 +359,7 @@ def main():
     host_pool = [last(pool[i]).cpu().pin_memory() for i in range(host_n)]
     e2e = None
     if host_pool is not None:
-        stage = torch.empty(B, V, device=dev)
+        stage = torch.empty(B, V, device=dev, dtype=tdt)
         ke = max(3, min(K, 200))
 
         def e2e_step(i):
@@ -371,7 +377,7 @@ def main():
             t = torch.tensor([dt], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t[0])
-        e2e = {"value": world * B * ke / dt, "unit": "rows/s", "h2d_bytes_per_step": B * V * 4, "d2h_bytes_per_step": 4 * B,
+        e2e = {"value": world * B * ke / dt, "unit": "rows/s", "h2d_bytes_per_step": B * V * esz, "d2h_bytes_per_step": 4 * B,
                "steps": ke, "ms_per_step": dt / ke * 1e3}
     clk = clocks.stop()
 
@@ -380,7 +386,7 @@ def main():
             dist.destroy_process_group()
         return
     ms_per_step = total_ms / K
-    alg_bytes = (12 if w["rep"] else 4) * V * B            # logits read once (+ penalties read + write)
+    alg_bytes = ((8 if w["rep"] else 0) + esz) * V * B     # logits read once (+ fp32 penalties read + write)
     peak, peak_src = 6650.0, "fallback"
     try:
         peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
@@ -388,6 +394,7 @@ def main():
     except Exception:
         pass
     achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
+    base["dtype"] = "f32" if esz == 4 else a.dtype + " logits, fp32 arithmetic"
     line = dict(base, impl=a.impl, value=world * B * K / (total_ms * 1e-3), ms_per_step=ms_per_step,
                 median_us=median_us, p10_us=lat[len(lat) // 10], p90_us=lat[(len(lat) * 9) // 10],
                 wall_sync_median_us=wall_median_us, clocks=clk, e2e=e2e, gpu_launches=int(gpu_launches),
