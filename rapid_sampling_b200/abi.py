@@ -18,7 +18,7 @@ RS_DTYPE_F32, RS_DTYPE_F16, RS_DTYPE_BF16 = 0, 1, 2
 RS_STATIC_SCRATCH_FLOATS = 4194304
 
 SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_typed", "rs_sample_static_scratch",
-           "rs_device_status", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_stage", "rs_status_string",
+           "rs_device_status", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_fast_layout", "rs_vp_stage", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
 
@@ -39,6 +39,7 @@ class VpCall(C.Structure):
 
 VP_MAX, VP_SUM, VP_ROUND, VP_TALLY, VP_WEIGHT, VP_PICK, VP_PENALTY = range(7)
 VP_ROUNDS = 8
+VPF_MAX, VPF_SUM, VPF_COMPACT, VPF_FINISH, VPF_ADVANCE = 10, 11, 12, 13, 14
 
 _lib = None
 
@@ -64,6 +65,7 @@ def load():
     L.rs_vp_workspace_bytes.argtypes = [i64, C.c_int32]
     L.rs_vp_workspace_bytes.restype = C.c_size_t
     L.rs_vp_layout.argtypes = [i64, C.c_int32, C.POINTER(C.c_int64)]
+    L.rs_vp_fast_layout.argtypes = [i64, i64, C.c_int32, C.POINTER(C.c_int64)]
     L.rs_vp_stage.argtypes = [C.POINTER(VpCall), C.c_int32, C.c_int32]
     L.rs_device_status.argtypes = [vp, vp]
     L.rs_set_cluster_override.argtypes = [C.c_int]

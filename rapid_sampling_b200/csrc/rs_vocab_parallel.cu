@@ -316,13 +316,374 @@ static VpLayout vp_layout(long long B, int world) {
     return l;
 }
 
+
+// =====================================================================================================
+// Fast protocol: 3 collectives.  Each shard extracts a short candidate list (every element above a bound
+// derived from per-thread maxima, as in the single-GPU kernel), the lists are all-gathered, and every rank
+// finishes the row redundantly on the union -- cutoff search, tie weight, owner-free pick -- from identical
+// data, so the id needs no exchange.  A row whose candidates cannot settle the cutoff (too little mass or too
+// few elements above the bound, or a list overflow) is flagged; the driver then repeats the call with the
+// staged protocol above.
+//   vpf_max     per (row, sub-block): max of x, candidate bound            -> all-reduce MAX  [B][S][2]
+//   vpf_sum     per (row, sub-block): denominator partial, candidates       -> all-reduce SUM  [B][S][4]
+//   vpf_compact per row: ordered list of (e, column)                        -> all-gather      [B][Lmax][2] + counts
+//   vpf_finish  per row, on every rank: threshold, weights, pick; validity flag
+// =====================================================================================================
+constexpr int kFCap = 8;        // candidates a thread may hold per sub-block
+constexpr int kFLmax = 2048;    // candidates a rank may contribute per row
+constexpr int kFMaxSub = 8;
+
+struct FSub { int g0, g1; };    // float4 groups [g0, g1) of the shard handled by a sub-block
+__device__ __forceinline__ FSub f_sub(int n, int S, int s) {
+    const int G = n >> 2, per = (G + S - 1) / S;
+    FSub r;
+    r.g0 = min(s * per, G);
+    r.g1 = min(r.g0 + per, G);
+    return r;
+}
+__device__ __forceinline__ float4 vp_x4(const VpRow& r, int g, float scale) {
+    float4 v = reinterpret_cast<const float4*>(r.logits)[g];
+    if (r.penalties) {
+        const float4 q = reinterpret_cast<const float4*>(r.penalties)[g];
+        v.x = sanitize((sanitize(v.x) - q.x) * scale); v.y = sanitize((sanitize(v.y) - q.y) * scale);
+        v.z = sanitize((sanitize(v.z) - q.z) * scale); v.w = sanitize((sanitize(v.w) - q.w) * scale);
+    } else {
+        v.x = sanitize(v.x * scale); v.y = sanitize(v.y * scale); v.z = sanitize(v.z * scale); v.w = sanitize(v.w * scale);
+    }
+    return v;
+}
+
+__global__ void __launch_bounds__(kVpThreads) vpf_max_kernel(const float* logits, long long row_stride, float* penalties, int n,
+                                                             float scale, int S, int sel_rank, float* stat1) {
+    __shared__ float sh[64];
+    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x, lane = t & 31, w = t >> 5;
+    const VpRow r = vp_row(logits, row_stride, penalties, n, b);
+    const FSub sb = f_sub(n, S, s);
+    float tmax = -INFINITY;
+    for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
+        const float4 v = vp_x4(r, g, scale);
+        tmax = fmaxf(fmaxf(tmax, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+    }
+    // the warp's sel_rank-th largest thread maximum; the minimum over warps bounds >= 32 * sel_rank elements
+    int rank = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        const float o = __shfl_sync(0xffffffffu, tmax, i);
+        rank += (o > tmax || (o == tmax && i < lane)) ? 1 : 0;
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, rank == sel_rank - 1);
+    const float wsel = __shfl_sync(0xffffffffu, tmax, __ffs(m) - 1);
+    const float wmax = warp_max(tmax);
+    if (lane == 0) { sh[w] = wmax; sh[32 + w] = wsel; }
+    __syncthreads();
+    if (t < 32) {
+        const float mx = warp_max(sh[t]), bd = warp_min(sh[32 + t]);
+        if (t == 0) { stat1[(b * S + s) * 2] = mx; stat1[(b * S + s) * 2 + 1] = -bd; }
+    }
+}
+
+__device__ __forceinline__ void f_bounds(const float* stat1, int S, int b, float& gmax, float& beta_x) {
+    float mx = -INFINITY, nb = -INFINITY;
+    for (int s = 0; s < S; s++) { mx = fmaxf(mx, stat1[(b * S + s) * 2]); nb = fmaxf(nb, stat1[(b * S + s) * 2 + 1]); }
+    gmax = mx;
+    beta_x = -nb;
+}
+
+__global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits, long long row_stride, float* penalties, int n,
+                                                             float scale, int S, const float* stat1, float* stat2,
+                                                             uint32_t* tcnt, uint32_t* tent, long long col0) {
+    __shared__ float sh[32];
+    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x;
+    const VpRow r = vp_row(logits, row_stride, penalties, n, b);
+    const FSub sb = f_sub(n, S, s);
+    float gmax, beta_x;
+    f_bounds(stat1, S, b, gmax, beta_x);
+    float acc = 0.f, csum = 0.f;
+    uint32_t nc = 0;
+    uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
+    for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
+        const float4 v = vp_x4(r, g, scale);
+        const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float e = exp2f(x[j] - gmax);
+            acc += e;
+            if (x[j] >= beta_x) {
+                if (nc < kFCap) { ent[nc * 2] = __float_as_uint(e); ent[nc * 2 + 1] = (uint32_t)(col0 + 4 * g + j); }
+                nc++;
+                csum += e;
+            }
+        }
+    }
+    tcnt[(size_t)(b * S + s) * kVpThreads + t] = nc;
+    const float d = vp_block_sum(acc, sh), cm = vp_block_sum(csum, sh), cn = vp_block_sum((float)nc, sh),
+                ov = vp_block_sum(nc > kFCap ? 1.f : 0.f, sh);
+    if (t == 0) {
+        float* o = stat2 + (size_t)(b * S + s) * 4;
+        o[0] = d; o[1] = cm; o[2] = cn; o[3] = ov;
+    }
+}
+
+// Ordered compaction of a row's per-thread lists (sub-block, thread, entry) into one list for the all-gather.
+__global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, const uint32_t* tcnt, const uint32_t* tent,
+                                                                 uint32_t* send /* [B][Lmax][2] */, uint32_t* send_cnt) {
+    __shared__ uint32_t sh[32];
+    __shared__ uint32_t s_base;
+    const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
+    if (t == 0) s_base = 0;
+    __syncthreads();
+    for (int s = 0; s < S; s++) {
+        const uint32_t raw = tcnt[(size_t)(b * S + s) * kVpThreads + t];
+        const uint32_t c = min(raw, (uint32_t)kFCap);
+        uint32_t incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) sh[w] = incl;
+        __syncthreads();
+        uint32_t pre = s_base;
+        for (int k = 0; k < w; k++) pre += sh[k];
+        const uint32_t off = pre + incl - c;
+        const uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
+        for (uint32_t i = 0; i < c; i++) {
+            if (off + i < (uint32_t)kFLmax) {
+                send[((size_t)b * kFLmax + off + i) * 2] = ent[i * 2];
+                send[((size_t)b * kFLmax + off + i) * 2 + 1] = ent[i * 2 + 1];
+            }
+        }
+        __syncthreads();
+        if (t == 0) {
+            uint32_t tot = s_base;
+            for (int k = 0; k < 32; k++) tot += sh[k];
+            s_base = tot;
+        }
+        __syncthreads();
+    }
+    if (t == 0) send_cnt[b] = s_base;   // may exceed Lmax: the finishing kernel treats that as an overflow
+}
+
+// block-wide fixed-order sums of NV per-thread values at once: warp trees, then threads 0..NV-1 add the 32 warp values
+template <int NV>
+__device__ __forceinline__ void f_block_sums(float (&v)[NV], float* sh /* [32][NV] + [NV] */) {
+    const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+#pragma unroll
+    for (int i = 0; i < NV; i++) v[i] = warp_tree_sum(v[i]);
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < NV; i++) sh[w * NV + i] = v[i];
+    }
+    __syncthreads();
+    if (t < NV) {
+        float a = sh[t];
+        for (int k = 1; k < 32; k++) a += sh[k * NV + t];
+        sh[32 * NV + t] = a;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NV; i++) v[i] = sh[32 * NV + i];
+}
+
+__global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, const float* stat1, const float* stat2,
+                                                                const uint32_t* gath /* [world][B][Lmax][2] */,
+                                                                const uint32_t* gath_cnt /* [world][B] */, float top_k,
+                                                                float top_p, int use_p, const unsigned char* states,
+                                                                int* ids, int* valid) {
+    __shared__ float sh[32 * 30 + 32];
+    __shared__ float s_scan[32];
+    __shared__ int s_hit;
+    const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
+    float gmax, beta_x;
+    f_bounds(stat1, S, b, gmax, beta_x);
+    float denom = 0.f, ovf = 0.f;
+    for (int s = 0; s < S; s++) { denom += stat2[(size_t)(b * S + s) * 4]; ovf += stat2[(size_t)(b * S + s) * 4 + 3]; }
+    bool ok_row = (ovf == 0.f);
+    uint32_t M = 0;
+    for (int r = 0; r < world; r++) {
+        const uint32_t c = gath_cnt[r * B + b];
+        if (c > (uint32_t)kFLmax) ok_row = false;
+        M += min(c, (uint32_t)kFLmax);
+    }
+    // flat position -> (rank, entry); each thread owns a contiguous block of q positions (keeps list order)
+    const uint32_t q = (M + kVpThreads - 1) / kVpThreads;
+    const uint32_t p0 = min((uint32_t)t * q, M), p1 = min(p0 + q, M);
+    auto entry = [&](uint32_t pos, float& pr, uint32_t& col) {
+        uint32_t r = 0, rem = pos;
+        for (;;) {
+            const uint32_t c = min(gath_cnt[r * B + b], (uint32_t)kFLmax);
+            if (rem < c) break;
+            rem -= c;
+            r++;
+        }
+        const uint32_t* e = gath + (((size_t)r * B + b) * kFLmax + rem) * 2;
+        pr = __uint_as_float(e[0]) / denom;
+        col = e[1];
+    };
+    const uint32_t beta_p = __float_as_uint(exp2f(beta_x - gmax) / denom);
+    // 16-ary search over (beta_p, 1.0]; the set at beta_p + 1 must already fail the test, else the list is too thin
+    uint32_t left = beta_p + 1u, right = 0x3f800001u;
+    {
+        float v[2] = {0.f, 0.f};
+        for (uint32_t pos = p0; pos < p1; pos++) {
+            float pr; uint32_t col;
+            entry(pos, pr, col);
+            if (__float_as_uint(pr) >= left) { v[0] += 1.f; v[1] += pr; }
+        }
+        f_block_sums<2>(v, sh);
+        const bool okl = (v[0] < top_k) && (v[1] < top_p);
+        if (okl) ok_row = false;
+    }
+    for (int round = 0; round < RS_VP_ROUNDS && right - left > 1u; round++) {
+        uint32_t piv[kVpPivots];
+        vp_pivots(left, right, piv);
+        float v[30];
+#pragma unroll
+        for (int j = 0; j < 30; j++) v[j] = 0.f;
+        for (uint32_t pos = p0; pos < p1; pos++) {
+            float pr; uint32_t col;
+            entry(pos, pr, col);
+            const uint32_t pb = __float_as_uint(pr);
+#pragma unroll
+            for (int j = 0; j < kVpPivots; j++)
+                if (pb >= piv[j]) { v[2 * j] += 1.f; v[2 * j + 1] += pr; }
+        }
+        f_block_sums<30>(v, sh);
+        uint32_t nl = left, nr = right;
+        bool found = false;
+#pragma unroll
+        for (int j = 0; j < kVpPivots; j++) {
+            const bool okj = (v[2 * j] < top_k) && (v[2 * j + 1] < top_p);
+            if (!okj) nl = piv[j];
+            else if (!found) { nr = piv[j]; found = true; }
+        }
+        left = nl;
+        right = nr;
+    }
+    const float thr = __uint_as_float(left);
+    float tl[3] = {0.f, 0.f, 0.f};
+    for (uint32_t pos = p0; pos < p1; pos++) {
+        float pr; uint32_t col;
+        entry(pos, pr, col);
+        if (pr > thr) { tl[0] += 1.f; tl[1] += pr; }
+        if (pr == thr) tl[2] += 1.f;
+    }
+    f_block_sums<3>(tl, sh);
+    const float gt4[4] = {tl[0], tl[1], tl[2], 0.f};
+    const float comp = vp_comp(gt4, thr, top_k, use_p ? top_p : 0.f, use_p != 0);
+    // weights in list order; block scan; the first position whose running weight reaches u * total
+    float wsum = 0.f;
+    for (uint32_t pos = p0; pos < p1; pos++) {
+        float pr; uint32_t col;
+        entry(pos, pr, col);
+        wsum += vp_weight_of(pr, thr, comp);
+    }
+    const float incl = warp_scan_desc(wsum, lane);
+    if (lane == 31) s_scan[w] = incl;
+    if (t == 0) s_hit = 0x7fffffff;
+    __syncthreads();
+    float pre = 0.f, total = 0.f;
+    for (int k = 0; k < 32; k++) { if (k < w) pre += s_scan[k]; total += s_scan[k]; }
+    RngWords rng;
+    {
+        const uint4* st = reinterpret_cast<const uint4*>(states + (long long)b * RS_STATE_BYTES);
+        rng.ctr = st[0]; rng.block = st[1]; rng.key_pos = st[2];
+    }
+    uint32_t r0, r1, r4[4];
+    rng_peek2(rng, r0, r1, r4);
+    const float target = total * u01(r0);
+    float run = pre + incl - wsum;   // weight before this thread's block
+    int last_kept = -1;
+    for (uint32_t pos = p0; pos < p1; pos++) {
+        float pr; uint32_t col;
+        entry(pos, pr, col);
+        const float wv = vp_weight_of(pr, thr, comp);
+        if (wv > 0.f) {
+            run += wv;
+            last_kept = (int)pos;
+            if (target <= run) { atomicMin(&s_hit, (int)pos); break; }
+        }
+    }
+    __syncthreads();
+    if (s_hit == 0x7fffffff) {   // rounding only: the last kept position
+        __syncthreads();
+        if (t == 0) s_hit = -1;
+        __syncthreads();
+        if (last_kept >= 0) atomicMax(&s_hit, last_kept);
+        __syncthreads();
+    }
+    if (t == 0) {
+        int id = 0;
+        if (s_hit >= 0 && M > 0) {
+            float pr; uint32_t col;
+            entry((uint32_t)s_hit, pr, col);
+            id = (int)col;
+        } else {
+            ok_row = false;
+        }
+        ids[b] = id + 1;
+        valid[b] = ok_row ? 1 : 0;
+    }
+}
+
+// every rank advances its replica of the RNG states by one block (after a fast-protocol call that was valid)
+__global__ void vpf_advance_kernel(unsigned char* states, int B) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    uint4* st = reinterpret_cast<uint4*>(states + (long long)b * RS_STATE_BYTES);
+    const uint4 nctr = ctr_next(st[0]);
+    const uint4 key = st[2];
+    st[0] = nctr;
+    st[1] = philox4x32_10(nctr, key.x, key.y);
+}
+
+struct VpfLayout { size_t stat1, stat2, tcnt, tent, send, send_cnt, gath, gath_cnt, ids, valid, total; };
+static VpfLayout vpf_layout(long long B, int world, int S) {
+    VpfLayout l;
+    size_t o = 0;
+    auto take = [&](size_t n) { size_t at = o; o += (n + 63) & ~(size_t)63; return at; };
+    l.stat1 = take((size_t)B * S * 2);
+    l.stat2 = take((size_t)B * S * 4);
+    l.tcnt = take((size_t)B * S * kVpThreads);
+    l.tent = take((size_t)B * S * kVpThreads * kFCap * 2);
+    l.send = take((size_t)B * kFLmax * 2);
+    l.send_cnt = take(B);
+    l.gath = take((size_t)world * B * kFLmax * 2);
+    l.gath_cnt = take((size_t)world * B);
+    l.ids = take(B);
+    l.valid = take(B);
+    l.total = o;
+    return l;
+}
+// sub-blocks per row: enough CTAs to fill the GPU, but every thread keeps >= 16 float4 groups so that its maximum
+// is a meaningful sample (the candidate bound comes from thread maxima)
+static int vpf_subblocks(long long B, long long n) {
+    long long S = 296 / (B > 0 ? B : 1);
+    const long long by_work = (n / 4) / (1024 * 16);
+    if (S > by_work) S = by_work;
+    return S < 1 ? 1 : (S > kFMaxSub ? kFMaxSub : (int)S);
+}
+
 }  // namespace rs
 
 extern "C" {
 
 size_t rs_vp_workspace_bytes(int64_t B, int32_t world) {
     if (B <= 0 || world <= 0) return 0;
-    return rs::vp_layout(B, world).total * sizeof(float);
+    return (rs::vp_layout(B, world).total + rs::vpf_layout(B, world, rs::kFMaxSub).total) * sizeof(float);
+}
+
+int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets_floats[10]) {
+    if (B <= 0 || world <= 0 || !offsets_floats) return RS_ERR_BATCH;
+    const size_t base = rs::vp_layout(B, world).total;
+    const int S = rs::vpf_subblocks(B, V_local);
+    const rs::VpfLayout l = rs::vpf_layout(B, world, S);
+    const size_t o[10] = {l.stat1, l.stat2, l.send, l.send_cnt, l.gath, l.gath_cnt, l.ids, l.valid, (size_t)S, (size_t)rs::kFLmax};
+    for (int i = 0; i < 8; i++) offsets_floats[i] = (int64_t)(base + o[i]);
+    offsets_floats[8] = (int64_t)o[8];
+    offsets_floats[9] = (int64_t)o[9];
+    return RS_OK;
 }
 
 int rs_vp_layout(int64_t B, int32_t world, int64_t offsets_floats[6]) {
@@ -387,11 +748,36 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
         case RS_VP_PENALTY:
             if (c->penalties) {
                 const long long tot = (long long)B * n;
+                const int* idsrc = (round == 1) ? (const int*)(ws + l.total + vpf_layout(B, c->world, vpf_subblocks(B, n)).ids)
+                                                : (const int*)(ws + l.ids);   // round 1: ids of the fast protocol
                 vp_penalty_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(
-                    c->penalties, (int)n, (int)B, (const int*)(ws + l.ids), (long long)c->col0, (float)c->presence_penalty,
+                    c->penalties, (int)n, (int)B, idsrc, (long long)c->col0, (float)c->presence_penalty,
                     (float)c->repetition_penalty, (float)c->penalty_decay);
             }
             break;
+        case RS_VPF_MAX: case RS_VPF_SUM: case RS_VPF_COMPACT: case RS_VPF_FINISH: case RS_VPF_ADVANCE: {
+            const int S = vpf_subblocks(B, n);
+            const VpfLayout f = vpf_layout(B, c->world, S);
+            float* fw = ws + l.total;
+            uint32_t* uw = reinterpret_cast<uint32_t*>(fw);
+            int sel_rank = 2;                                   // top-p only: try the ~64 largest of every sub-block
+            if (top_k < V) sel_rank = (int)((top_k + 2 + 31) / 32);
+            if (sel_rank > 32) sel_rank = 32;
+            if (stage == RS_VPF_MAX)
+                vpf_max_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, sel_rank, fw + f.stat1);
+            else if (stage == RS_VPF_SUM)
+                vpf_sum_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
+                                                                fw + f.stat2, uw + f.tcnt, uw + f.tent, (long long)c->col0);
+            else if (stage == RS_VPF_COMPACT)
+                vpf_compact_kernel<<<grid, kVpThreads, 0, st>>>(S, uw + f.tcnt, uw + f.tent, uw + f.send, uw + f.send_cnt);
+            else if (stage == RS_VPF_FINISH)
+                vpf_finish_kernel<<<grid, kVpThreads, 0, st>>>((int)B, S, c->world, fw + f.stat1, fw + f.stat2, uw + f.gath,
+                                                               uw + f.gath_cnt, fk, fp, use_p, (const unsigned char*)c->states,
+                                                               (int*)(uw + f.ids), (int*)(uw + f.valid));
+            else
+                vpf_advance_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((unsigned char*)c->states, (int)B);
+            break;
+        }
         default:
             return RS_ERR_LIMIT;
     }

@@ -3,7 +3,12 @@
 The driver below owns the SEQUENCE of stages and collectives; the per-shard arithmetic is done by a
 `compute` object -- the CUDA kernels behind ``rs_vp_stage`` (default), or any object with the same
 ``stage(name, round)`` method operating on the same workspace regions (the CPU test-suite plugs a numpy
-model in and runs the driver over gloo).  One sampling call = 13 small collectives:
+model in and runs the driver over gloo).
+
+Fast protocol (default): 2 all-reduces + 1 all-gather.  Every shard extracts a short candidate list (elements above
+a bound derived from per-thread maxima), the lists are all-gathered and every rank finishes the row on the union
+from identical data -- no id exchange.  If some row's list cannot settle its cutoff (flagged on the device, read by
+the host) the call is repeated with the staged protocol: 13 small collectives:
 
     MAX(row maxima) . SUM(denominators) . 8 x SUM(counts and masses at 15 pivots) . SUM(threshold tallies) .
     SUM(kept weight per shard) . MAX(sampled id + 1)
@@ -19,7 +24,8 @@ import torch.distributed as dist
 
 from . import abi
 
-STAGES = ("max", "sum", "round", "tally", "weight", "pick", "penalty")
+STAGES = {"max": 0, "sum": 1, "round": 2, "tally": 3, "weight": 4, "pick": 5, "penalty": 6,
+          "f_max": 10, "f_sum": 11, "f_compact": 12, "f_finish": 13, "f_advance": 14}
 
 
 class CudaCompute:
@@ -40,7 +46,7 @@ class CudaCompute:
         c.rank, c.world = s.rank, s.world
 
     def stage(self, name, rnd=0):
-        rc = self.L.rs_vp_stage(C.byref(self.call), STAGES.index(name), rnd)
+        rc = self.L.rs_vp_stage(C.byref(self.call), STAGES[name], rnd)
         if rc != 0:
             if rc in (abi.RS_ERR_VOCAB, abi.RS_ERR_BATCH, abi.RS_ERR_TEMPERATURE):
                 raise ValueError(abi.status_string(rc))
@@ -48,7 +54,7 @@ class CudaCompute:
 
 
 class VocabParallelSampler:
-    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1):
+    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1, fast=True):
         if V_global % world or (V_global // world) % 4:
             raise ValueError("V=%d cannot be split into %d shards of a multiple of 4 columns" % (V_global, world))
         self.B, self.T, self.V_global, self.rank, self.world, self.group = B, T, V_global, rank, world, group
@@ -68,10 +74,49 @@ class VocabParallelSampler:
         self.weights = self.ws[o[4]:o[4] + B * world]
         self.ids = self.ws[o[5]:o[5] + B].view(torch.int32)
         self.compute = compute or CudaCompute()
+        # fast protocol (3 collectives): regions behind the staged protocol's
+        self.fast = fast
+        fo = (C.c_int64 * 10)()
+        L.rs_vp_fast_layout(B, self.V_local, world, fo)
+        f = [int(x) for x in fo]
+        S, Lmax = f[8], f[9]
+        self.f_stat1 = self.ws[f[0]:f[0] + B * S * 2]
+        self.f_stat2 = self.ws[f[1]:f[1] + B * S * 4]
+        self.f_send = self.ws[f[2]:f[2] + B * Lmax * 2]
+        self.f_send_cnt = self.ws[f[3]:f[3] + B]
+        self.f_gath = self.ws[f[4]:f[4] + world * B * Lmax * 2]
+        self.f_gath_cnt = self.ws[f[5]:f[5] + world * B]
+        self.f_ids = self.ws[f[6]:f[6] + B].view(torch.int32)
+        self.f_valid = self.ws[f[7]:f[7] + B].view(torch.int32)
+        self.last_protocol = None
 
     def _reduce(self, t, op):
         if self.world > 1:
             dist.all_reduce(t, op=op, group=self.group)
+
+    def _gather(self, out, inp):
+        if self.world > 1:
+            dist.all_gather_into_tensor(out, inp, group=self.group)
+        else:
+            out.copy_(inp)
+
+    def _sample_fast(self, penalties):
+        """Three collectives; returns ids, or None when some row's candidate list could not settle its cutoff."""
+        c = self.compute
+        c.stage("f_max")
+        self._reduce(self.f_stat1, dist.ReduceOp.MAX)
+        c.stage("f_sum")
+        self._reduce(self.f_stat2, dist.ReduceOp.SUM)
+        c.stage("f_compact")
+        self._gather(self.f_gath, self.f_send)
+        self._gather(self.f_gath_cnt, self.f_send_cnt)
+        c.stage("f_finish")
+        if int(self.f_valid.min().item()) == 0:      # the one host synchronisation of the fast protocol
+            return None
+        c.stage("f_advance")
+        if penalties is not None:
+            c.stage("penalty", 1)
+        return self.f_ids - 1
 
     def sample(self, logits, states, temperature, top_k, top_p, penalties=None, presence_penalty=0.0,
                repetition_penalty=0.0, penalty_decay=0.0):
@@ -82,6 +127,11 @@ class VocabParallelSampler:
         c = self.compute
         c.bind(self, logits, states, penalties, float(temperature), int(top_k), float(top_p), float(presence_penalty),
                float(repetition_penalty), float(penalty_decay))
+        if self.fast:
+            ids = self._sample_fast(penalties)
+            self.last_protocol = "fast" if ids is not None else "staged"
+            if ids is not None:
+                return ids
         c.stage("max")
         self._reduce(self.gmax, dist.ReduceOp.MAX)
         c.stage("sum")

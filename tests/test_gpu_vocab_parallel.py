@@ -12,12 +12,37 @@ from oracle import cpu_ref
 pytestmark = pytest.mark.gpu
 
 
-def emulated_sample(samplers, shards, states, temp, k, p, pens=None):
+def emulated_sample(samplers, shards, states, temp, k, p, pens=None, fast=True):
     """Drives N single-process 'ranks' through the stage sequence of VocabParallelSampler.sample."""
     from rapid_sampling_b200 import abi
     N = len(samplers)
     for r, s in enumerate(samplers):
         s.compute.bind(s, shards[r], states[r], None if pens is None else pens[r], temp, k, p, 0.1, 0.2, 0.5)
+    if fast:
+        def fstep(name, region=None, op=None, rnd=0):
+            for s in samplers:
+                s.compute.stage(name, rnd)
+            if region is not None:
+                stack = torch.stack([region(s) for s in samplers])
+                red = stack.max(dim=0).values if op == "max" else stack.sum(dim=0)
+                for s in samplers:
+                    region(s).copy_(red)
+        fstep("f_max", lambda s: s.f_stat1, "max")
+        fstep("f_sum", lambda s: s.f_stat2, "sum")
+        fstep("f_compact")
+        for s in samplers:          # the all-gather
+            s.f_gath.copy_(torch.cat([x.f_send for x in samplers]))
+            s.f_gath_cnt.copy_(torch.cat([x.f_send_cnt for x in samplers]))
+        fstep("f_finish")
+        torch.cuda.synchronize()
+        if all(int(s.f_valid.min()) == 1 for s in samplers):
+            fstep("f_advance")
+            if pens is not None:
+                fstep("penalty", rnd=1)
+            emulated_sample.last = "fast"
+            return [s.f_ids - 1 for s in samplers]
+        assert all(int(s.f_valid.min()) == 0 for s in samplers)      # every rank reaches the same verdict
+    emulated_sample.last = "staged"
 
     def step(name, rnd, region, op):
         for s in samplers:
@@ -49,8 +74,10 @@ def test_emulated_ranks_agree_and_match_float64_kept_set(abi, N):
     states = [abi.setup_rand(9, B) for _ in range(N)]
     pens = [torch.zeros(B, s.V_local, device="cuda") for s in samplers]
     pen64 = torch.zeros(B, V)
+    used = []
     for temp, k, p in [(0.8, 50, 0.9), (1.0, -1, 0.5), (1.0, -1, 1.0), (0.7, 1, 0.0)]:
         ids = emulated_sample(samplers, shards, states, temp, k, p, pens)
+        used.append(emulated_sample.last)
         torch.cuda.synchronize()
         for r in range(1, N):
             assert torch.equal(ids[r], ids[0])
@@ -67,6 +94,7 @@ def test_emulated_ranks_agree_and_match_float64_kept_set(abi, N):
         pen64 = pen64 * 0.5 + hit
         cat = torch.cat([x.cpu() for x in pens], dim=1)
         assert torch.allclose(cat, pen64, rtol=1e-6, atol=0)
+    assert used[0] == "fast" and used[2] == "staged"      # peaked top-k rows settle on candidates; 'keep everything' cannot
 
 
 def test_threshold_matches_single_gpu_kernel(abi):
@@ -77,7 +105,7 @@ def test_threshold_matches_single_gpu_kernel(abi):
     _, probs, tr = abi.sample(full.cuda(), abi.setup_rand(1, B), 0.9, -1, 0.8, debug=True)
     samplers = [VocabParallelSampler(B, V, r, N) for r in range(N)]
     shards = [full[:, s.col0:s.col0 + s.V_local].contiguous().cuda() for s in samplers]
-    emulated_sample(samplers, shards, [abi.setup_rand(1, B) for _ in range(N)], 0.9, -1, 0.8)
+    emulated_sample(samplers, shards, [abi.setup_rand(1, B) for _ in range(N)], 0.9, -1, 0.8, fast=False)
     torch.cuda.synchronize()
     d = cpu_ref.distribution(full, 0.9, -1, 0.8)
     s0 = samplers[0]

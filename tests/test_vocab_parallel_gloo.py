@@ -22,7 +22,7 @@ def _worker(rank, world, port, q):
     dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
     B, V = 6, 4096
     full = make_logits("normal3", B, V, 5, torch)
-    s = VocabParallelSampler(B, V, rank, world, device="cpu", compute=NumpyCompute())
+    s = VocabParallelSampler(B, V, rank, world, device="cpu", compute=NumpyCompute(), fast=False)   # staged protocol
     shard = full[:, s.col0:s.col0 + s.V_local].contiguous()
     states = torch.from_numpy(co.setup_rand(17, B))
     pen = torch.zeros(B, s.V_local)
