@@ -213,12 +213,12 @@ def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch,
             pass
         ach = alg / (ms * 1e-3) / 1e9
         line = dict(base, impl="ours", scaling="strong", value=B * K / (total_ms * 1e-3), ms_per_step=ms, median_us=ms * 1e3,
-                    clocks=clk, gpu_launches=K * 13,
-                    roofline={"bound": "hbm", "kernel": "vp_round_kernel (x8) + 5 stage kernels", "achieved": ach,
+                    clocks=clk, gpu_launches=K * (6 if s.last_protocol == "fast" else 19), protocol=s.last_protocol,
+                    roofline={"bound": "hbm", "kernel": "vpf_* stage kernels (fast protocol: 3 passes over the shard, 3 collectives)", "achieved": ach,
                               "peak": peak * world, "unit": "GB/s", "frac": ach / (peak * world),
                               "algorithmic_bytes_per_launch": alg, "traffic": None,
-                              "note": "12 streaming passes per call and 13 latency-bound collectives"})
-        line["config"]["parallelism"] = "vocab-parallel x%d (V/N = %d columns per GPU, NCCL all-reduce per search round)" % (world, V // world)
+                              "note": "latency-bound: collectives and one host check per call"})
+        line["config"]["parallelism"] = "vocab-parallel x%d (V/N = %d columns per GPU; NCCL: 2 all-reduces + 1 all-gather per call)" % (world, V // world)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

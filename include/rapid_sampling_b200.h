@@ -163,11 +163,13 @@ int rs_sample_static_scratch(const float* logits_device, int64_t B, int64_t T, i
 #define RS_VP_ROUNDS 8
 enum { RS_VP_MAX = 0, RS_VP_SUM = 1, RS_VP_ROUND = 2, RS_VP_TALLY = 3, RS_VP_WEIGHT = 4, RS_VP_PICK = 5, RS_VP_PENALTY = 6,
        /* fast protocol (3 collectives): every shard extracts a short candidate list, the lists are all-gathered and every
-        * rank finishes the row on the union.  Regions from rs_vp_fast_layout (floats): [0] stat1 B*S*2 (all-reduce MAX),
-        * [1] stat2 B*S*4 (all-reduce SUM), [2] send list B*Lmax*2 + [3] send counts B (all-gather into [4] and [5]),
+        * rank finishes the row on the union.  Order: VPF_MAX, VPF_SUM (denominator + octave histogram of the large
+        * elements), VPF_EXTRACT (bound chosen from the reduced histogram), VPF_COMPACT, all-gather, VPF_FINISH.
+        * Regions from rs_vp_fast_layout (floats): [0] stat1 B*S (all-reduce MAX),
+        * [1] stat2 B*S*[10] (all-reduce SUM), [2] send list B*Lmax*2 + [3] send counts B (all-gather into [4] and [5]),
         * [6] ids + 1 (int32 B), [7] valid flags (int32 B; a 0 means: repeat the call with the staged protocol),
         * [8] = S, [9] = Lmax.  RS_VP_PENALTY with round = 1 applies the fast protocol's ids. */
-       RS_VPF_MAX = 10, RS_VPF_SUM = 11, RS_VPF_COMPACT = 12, RS_VPF_FINISH = 13, RS_VPF_ADVANCE = 14 };
+       RS_VPF_MAX = 10, RS_VPF_SUM = 11, RS_VPF_COMPACT = 12, RS_VPF_FINISH = 13, RS_VPF_ADVANCE = 14, RS_VPF_EXTRACT = 15 };
 typedef struct rs_vp_call {
     const float* logits;      /* device, (B, T, V_local) contiguous: this rank's columns; position T-1 is read   */
     float* penalties;         /* device, (B, V_local) or NULL                                                    */
@@ -181,7 +183,7 @@ typedef struct rs_vp_call {
 } rs_vp_call;
 size_t rs_vp_workspace_bytes(int64_t B, int32_t world);
 int rs_vp_layout(int64_t B, int32_t world, int64_t offsets_floats[6]);
-int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets_floats[10]);
+int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets_floats[11]);
 int rs_vp_stage(const rs_vp_call* call, int32_t stage, int32_t round);
 
 /* Reads the device status word of `workspace_device` (synchronises `stream`): RS_OK or RS_ERR_TIMEOUT. */

@@ -39,7 +39,7 @@ class VpCall(C.Structure):
 
 VP_MAX, VP_SUM, VP_ROUND, VP_TALLY, VP_WEIGHT, VP_PICK, VP_PENALTY = range(7)
 VP_ROUNDS = 8
-VPF_MAX, VPF_SUM, VPF_COMPACT, VPF_FINISH, VPF_ADVANCE = 10, 11, 12, 13, 14
+VPF_MAX, VPF_SUM, VPF_COMPACT, VPF_FINISH, VPF_ADVANCE, VPF_EXTRACT = 10, 11, 12, 13, 14, 15
 
 _lib = None
 

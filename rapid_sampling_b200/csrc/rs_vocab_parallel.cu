@@ -318,20 +318,26 @@ static VpLayout vp_layout(long long B, int world) {
 
 
 // =====================================================================================================
-// Fast protocol: 3 collectives.  Each shard extracts a short candidate list (every element above a bound
-// derived from per-thread maxima, as in the single-GPU kernel), the lists are all-gathered, and every rank
-// finishes the row redundantly on the union -- cutoff search, tie weight, owner-free pick -- from identical
-// data, so the id needs no exchange.  A row whose candidates cannot settle the cutoff (too little mass or too
-// few elements above the bound, or a list overflow) is flagged; the driver then repeats the call with the
-// staged protocol above.
-//   vpf_max     per (row, sub-block): max of x, candidate bound            -> all-reduce MAX  [B][S][2]
-//   vpf_sum     per (row, sub-block): denominator partial, candidates       -> all-reduce SUM  [B][S][4]
-//   vpf_compact per row: ordered list of (e, column)                        -> all-gather      [B][Lmax][2] + counts
-//   vpf_finish  per row, on every rank: threshold, weights, pick; validity flag
+// Fast protocol: 3 collectives.  Each shard extracts a short candidate list (every element whose
+// e = exp2(x - max) reaches a bound), the lists are all-gathered, and every rank finishes the row
+// redundantly on the union -- cutoff search, tie weight, owner-free pick -- from identical data, so the id
+// needs no exchange.  The bound is read off a histogram of e by octave that travels with the denominator:
+// the largest power of two above which the row still holds more than top_k + 1 elements, or more than top_p
+// of the mass; no such octave means "take everything", which only fits short rows.  A row whose candidates
+// cannot settle the cutoff (too little mass or too few elements above the bound, or a list overflow) is
+// flagged; the driver then repeats the call with the staged protocol above.
+//   vpf_max     per (row, sub-block): max of x                                  -> all-reduce MAX  [B][S]
+//   vpf_sum     per (row, sub-block): denominator partial, octave histogram     -> all-reduce SUM  [B][S][2 + 2*32]
+//               (count and mass per octave; exact in the top 10 octaves, a 1-in-16 sample of groups below)
+//   vpf_extract per (row, sub-block): per-thread candidate slots (e >= bound)
+//   vpf_compact per row: ordered list of (e, column)                             -> all-gather  [B][Lmax][2] + counts
+//   vpf_finish  per row, on every rank: probabilities staged in shared memory, threshold, weights, pick; validity
 // =====================================================================================================
-constexpr int kFCap = 8;        // candidates a thread may hold per sub-block
-constexpr int kFLmax = 2048;    // candidates a rank may contribute per row
+constexpr int kFCap = 16;       // candidates a thread may hold per sub-block
 constexpr int kFMaxSub = 8;
+constexpr int kFBins = 32;      // octaves of e = exp2(x - max) below 1 that the mass histogram resolves
+// candidates a rank may contribute per row: the union over ranks stays near 32K entries
+__host__ __device__ constexpr int f_lmax(int world) { return (32768 / world) < 2048 ? 2048 : (32768 / world); }
 
 struct FSub { int g0, g1; };    // float4 groups [g0, g1) of the shard handled by a sub-block
 __device__ __forceinline__ FSub f_sub(int n, int S, int s) {
@@ -354,8 +360,8 @@ __device__ __forceinline__ float4 vp_x4(const VpRow& r, int g, float scale) {
 }
 
 __global__ void __launch_bounds__(kVpThreads) vpf_max_kernel(const float* logits, long long row_stride, float* penalties, int n,
-                                                             float scale, int S, int sel_rank, float* stat1) {
-    __shared__ float sh[64];
+                                                             float scale, int S, float* stat1) {
+    __shared__ float sh[32];
     const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x, lane = t & 31, w = t >> 5;
     const VpRow r = vp_row(logits, row_stride, penalties, n, b);
     const FSub sb = f_sub(n, S, s);
@@ -364,76 +370,130 @@ __global__ void __launch_bounds__(kVpThreads) vpf_max_kernel(const float* logits
         const float4 v = vp_x4(r, g, scale);
         tmax = fmaxf(fmaxf(tmax, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
     }
-    // the warp's sel_rank-th largest thread maximum; the minimum over warps bounds >= 32 * sel_rank elements
-    int rank = 0;
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-        const float o = __shfl_sync(0xffffffffu, tmax, i);
-        rank += (o > tmax || (o == tmax && i < lane)) ? 1 : 0;
-    }
-    const unsigned m = __ballot_sync(0xffffffffu, rank == sel_rank - 1);
-    const float wsel = __shfl_sync(0xffffffffu, tmax, __ffs(m) - 1);
     const float wmax = warp_max(tmax);
-    if (lane == 0) { sh[w] = wmax; sh[32 + w] = wsel; }
+    if (lane == 0) sh[w] = wmax;
     __syncthreads();
     if (t < 32) {
-        const float mx = warp_max(sh[t]), bd = warp_min(sh[32 + t]);
-        if (t == 0) { stat1[(b * S + s) * 2] = mx; stat1[(b * S + s) * 2 + 1] = -bd; }
+        const float mx = warp_max(sh[t]);
+        if (t == 0) stat1[b * S + s] = mx;
     }
 }
 
-__device__ __forceinline__ void f_bounds(const float* stat1, int S, int b, float& gmax, float& beta_x) {
-    float mx = -INFINITY, nb = -INFINITY;
-    for (int s = 0; s < S; s++) { mx = fmaxf(mx, stat1[(b * S + s) * 2]); nb = fmaxf(nb, stat1[(b * S + s) * 2 + 1]); }
-    gmax = mx;
-    beta_x = -nb;
+__device__ __forceinline__ float f_gmax(const float* stat1, int S, int b) {
+    float mx = -INFINITY;
+    for (int s = 0; s < S; s++) mx = fmaxf(mx, stat1[b * S + s]);
+    return mx;
+}
+// stat2 per (row, sub-block): [0] denominator partial, [1] unused, [2..] histogram: for octave k (e in [2^-(k+1), 2^-k),
+// e = 1 counted in octave 0) mass at [2 + 2k] and count at [3 + 2k]
+constexpr int kFStat2 = 2 + 2 * kFBins;
+__device__ __forceinline__ float f_denom(const float* stat2, int S, int b) {
+    float d = 0.f;
+    for (int s = 0; s < S; s++) d += stat2[(size_t)(b * S + s) * kFStat2];
+    return d;
+}
+// The candidate bound: the largest power of two 2^-(K+1) such that the octaves 0..K together hold more than top_k
+// elements or about top_p of the mass (a forecast from unordered sums; the finishing kernel checks exactly).
+// Returns 0 when even all resolved octaves are not enough.
+__device__ __forceinline__ float f_bound_e(const float* stat2, int S, int b, float denom, float top_k, float top_p) {
+    float cm = 0.f, cc = 0.f;
+    for (int k = 0; k < kFBins; k++) {
+        for (int s = 0; s < S; s++) {
+            cm += stat2[(size_t)(b * S + s) * kFStat2 + 2 + 2 * k];
+            cc += stat2[(size_t)(b * S + s) * kFStat2 + 3 + 2 * k];
+        }
+        if (cc > top_k + 1.f || cm > top_p * denom * 1.001f) return exp2f(-(float)(k + 1));
+    }
+    return 0.f;
 }
 
+// pass 2: denominator partial and the octave histogram of the large elements
 __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits, long long row_stride, float* penalties, int n,
-                                                             float scale, int S, const float* stat1, float* stat2,
-                                                             uint32_t* tcnt, uint32_t* tent, long long col0) {
+                                                             float scale, int S, const float* stat1, float* stat2) {
     __shared__ float sh[32];
+    __shared__ float hist[2 * kFBins];
     const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x;
     const VpRow r = vp_row(logits, row_stride, penalties, n, b);
     const FSub sb = f_sub(n, S, s);
-    float gmax, beta_x;
-    f_bounds(stat1, S, b, gmax, beta_x);
-    float acc = 0.f, csum = 0.f;
-    uint32_t nc = 0;
-    uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
+    const float gmax = f_gmax(stat1, S, b);
+    if (t < 2 * kFBins) hist[t] = 0.f;
+    __syncthreads();
+    float acc = 0.f;
     for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
         const float4 v = vp_x4(r, g, scale);
         const float x[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float e = exp2f(x[j] - gmax);
+            const float d = x[j] - gmax;
+            const float e = exp2f(d);
             acc += e;
-            if (x[j] >= beta_x) {
-                if (nc < kFCap) { ent[nc * 2] = __float_as_uint(e); ent[nc * 2 + 1] = (uint32_t)(col0 + 4 * g + j); }
-                nc++;
-                csum += e;
+            // The histogram only steers the choice of the bound (the finishing kernel checks the result exactly), so
+            // below the top ten octaves one group in sixteen stands for its neighbours: few shared-memory atomics.
+            if (d > -(float)kFBins) {
+                const bool top = d > -10.f;
+                if (top || (g & 15) == 0) {
+                    int k = (int)(-d);                 // octave: e in (2^-(k+1), 2^-k]
+                    if (e < exp2f(-(float)k) * 0.5f) k++;      // guard the octave edge against rounding of exp2f
+                    const float wgt = top ? 1.f : 16.f;
+                    if (k < kFBins) { atomicAdd(&hist[2 * k], e * wgt); atomicAdd(&hist[2 * k + 1], wgt); }
+                }
             }
         }
     }
-    tcnt[(size_t)(b * S + s) * kVpThreads + t] = nc;
-    const float d = vp_block_sum(acc, sh), cm = vp_block_sum(csum, sh), cn = vp_block_sum((float)nc, sh),
-                ov = vp_block_sum(nc > kFCap ? 1.f : 0.f, sh);
-    if (t == 0) {
-        float* o = stat2 + (size_t)(b * S + s) * 4;
-        o[0] = d; o[1] = cm; o[2] = cn; o[3] = ov;
+    const float d = vp_block_sum(acc, sh);
+    __syncthreads();
+    float* o = stat2 + (size_t)(b * S + s) * kFStat2;
+    if (t == 0) { o[0] = d; o[1] = 0.f; }
+    if (t < 2 * kFBins) o[2 + t] = hist[t];
+}
+
+// pass 3: every element with e >= bound goes to its thread's list (order: column order within the thread)
+__global__ void __launch_bounds__(kVpThreads) vpf_extract_kernel(const float* logits, long long row_stride, float* penalties,
+                                                                 int n, float scale, int S, const float* stat1,
+                                                                 const float* stat2, float top_k, float top_p,
+                                                                 uint32_t* tcnt, uint32_t* tent, long long col0) {
+    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x;
+    const VpRow r = vp_row(logits, row_stride, penalties, n, b);
+    const FSub sb = f_sub(n, S, s);
+    const float gmax = f_gmax(stat1, S, b);
+    const float denom = f_denom(stat2, S, b);
+    const float bound = f_bound_e(stat2, S, b, denom, top_k, top_p);
+    uint32_t nc = 0;
+    uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
+    if (bound > 0.f) {
+        const float bx = log2f(bound) - 1.f;       // cheap pre-test in the x domain, one octave of slack
+        for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
+            const float4 v = vp_x4(r, g, scale);
+            const float x[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (x[j] - gmax >= bx) {
+                    const float e = exp2f(x[j] - gmax);
+                    if (e >= bound) {
+                        if (nc < kFCap) { ent[nc * 2] = __float_as_uint(e); ent[nc * 2 + 1] = (uint32_t)(col0 + 4 * g + j); }
+                        nc++;
+                    }
+                }
+            }
+        }
+    } else {
+        nc = kFCap + 1;     // no usable bound: flag the row through the overflow path
     }
+    tcnt[(size_t)(b * S + s) * kVpThreads + t] = nc;
 }
 
 // Ordered compaction of a row's per-thread lists (sub-block, thread, entry) into one list for the all-gather.
-__global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, const uint32_t* tcnt, const uint32_t* tent,
+__global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, int lmax, const uint32_t* tcnt, const uint32_t* tent,
                                                                  uint32_t* send /* [B][Lmax][2] */, uint32_t* send_cnt) {
+    __shared__ int s_over;
     __shared__ uint32_t sh[32];
     __shared__ uint32_t s_base;
     const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
-    if (t == 0) s_base = 0;
+    if (t == 0) { s_base = 0; s_over = 0; }
     __syncthreads();
     for (int s = 0; s < S; s++) {
         const uint32_t raw = tcnt[(size_t)(b * S + s) * kVpThreads + t];
+        if (raw > (uint32_t)kFCap) s_over = 1;
         const uint32_t c = min(raw, (uint32_t)kFCap);
         uint32_t incl = c;
 #pragma unroll
@@ -448,9 +508,9 @@ __global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, const ui
         const uint32_t off = pre + incl - c;
         const uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
         for (uint32_t i = 0; i < c; i++) {
-            if (off + i < (uint32_t)kFLmax) {
-                send[((size_t)b * kFLmax + off + i) * 2] = ent[i * 2];
-                send[((size_t)b * kFLmax + off + i) * 2 + 1] = ent[i * 2 + 1];
+            if (off + i < (uint32_t)lmax) {
+                send[((size_t)b * lmax + off + i) * 2] = ent[i * 2];
+                send[((size_t)b * lmax + off + i) * 2 + 1] = ent[i * 2 + 1];
             }
         }
         __syncthreads();
@@ -461,7 +521,8 @@ __global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, const ui
         }
         __syncthreads();
     }
-    if (t == 0) send_cnt[b] = s_base;   // may exceed Lmax: the finishing kernel treats that as an overflow
+    __syncthreads();
+    if (t == 0) send_cnt[b] = s_over ? 0xffffffffu : s_base;   // beyond Lmax / flagged: the finishing kernel rejects the row
 }
 
 // block-wide fixed-order sums of NV per-thread values at once: warp trees, then threads 0..NV-1 add the 32 warp values
@@ -486,7 +547,7 @@ __device__ __forceinline__ void f_block_sums(float (&v)[NV], float* sh /* [32][N
     for (int i = 0; i < NV; i++) v[i] = sh[32 * NV + i];
 }
 
-__global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, const float* stat1, const float* stat2,
+__global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, int lmax, const float* stat1, const float* stat2,
                                                                 const uint32_t* gath /* [world][B][Lmax][2] */,
                                                                 const uint32_t* gath_cnt /* [world][B] */, float top_k,
                                                                 float top_p, int use_p, const unsigned char* states,
@@ -494,17 +555,16 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     __shared__ float sh[32 * 30 + 32];
     __shared__ float s_scan[32];
     __shared__ int s_hit;
+    extern __shared__ float s_pr[];   // the probabilities of the row's candidates, list order (up to 32768)
     const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
-    float gmax, beta_x;
-    f_bounds(stat1, S, b, gmax, beta_x);
-    float denom = 0.f, ovf = 0.f;
-    for (int s = 0; s < S; s++) { denom += stat2[(size_t)(b * S + s) * 4]; ovf += stat2[(size_t)(b * S + s) * 4 + 3]; }
-    bool ok_row = (ovf == 0.f);
+    const float denom = f_denom(stat2, S, b);
+    const float bound = f_bound_e(stat2, S, b, denom, top_k, top_p);
+    bool ok_row = bound > 0.f;
     uint32_t M = 0;
     for (int r = 0; r < world; r++) {
         const uint32_t c = gath_cnt[r * B + b];
-        if (c > (uint32_t)kFLmax) ok_row = false;
-        M += min(c, (uint32_t)kFLmax);
+        if (c > (uint32_t)lmax) ok_row = false;
+        M += min(c, (uint32_t)lmax);
     }
     // flat position -> (rank, entry); each thread owns a contiguous block of q positions (keeps list order)
     const uint32_t q = (M + kVpThreads - 1) / kVpThreads;
@@ -512,23 +572,29 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     auto entry = [&](uint32_t pos, float& pr, uint32_t& col) {
         uint32_t r = 0, rem = pos;
         for (;;) {
-            const uint32_t c = min(gath_cnt[r * B + b], (uint32_t)kFLmax);
+            const uint32_t c = min(gath_cnt[r * B + b], (uint32_t)lmax);
             if (rem < c) break;
             rem -= c;
             r++;
         }
-        const uint32_t* e = gath + (((size_t)r * B + b) * kFLmax + rem) * 2;
+        const uint32_t* e = gath + (((size_t)r * B + b) * lmax + rem) * 2;
         pr = __uint_as_float(e[0]) / denom;
         col = e[1];
     };
-    const uint32_t beta_p = __float_as_uint(exp2f(beta_x - gmax) / denom);
-    // 16-ary search over (beta_p, 1.0]; the set at beta_p + 1 must already fail the test, else the list is too thin
+    // every probability > bound / denom is on the list (division is monotone; an element just below the bound may
+    // round to the same quotient, hence strictly); 16-ary search over that range; the set at its lower end must
+    // already fail the test, else the list is too thin
+    const uint32_t beta_p = __float_as_uint(bound / denom);
     uint32_t left = beta_p + 1u, right = 0x3f800001u;
+    for (uint32_t pos = p0; pos < p1; pos++) {      // one look-up and division per candidate; the rounds read shared memory
+        float pr; uint32_t col;
+        entry(pos, pr, col);
+        s_pr[pos] = pr;
+    }
     {
         float v[2] = {0.f, 0.f};
         for (uint32_t pos = p0; pos < p1; pos++) {
-            float pr; uint32_t col;
-            entry(pos, pr, col);
+            const float pr = s_pr[pos];
             if (__float_as_uint(pr) >= left) { v[0] += 1.f; v[1] += pr; }
         }
         f_block_sums<2>(v, sh);
@@ -542,8 +608,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
 #pragma unroll
         for (int j = 0; j < 30; j++) v[j] = 0.f;
         for (uint32_t pos = p0; pos < p1; pos++) {
-            float pr; uint32_t col;
-            entry(pos, pr, col);
+            const float pr = s_pr[pos];
             const uint32_t pb = __float_as_uint(pr);
 #pragma unroll
             for (int j = 0; j < kVpPivots; j++)
@@ -564,8 +629,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     const float thr = __uint_as_float(left);
     float tl[3] = {0.f, 0.f, 0.f};
     for (uint32_t pos = p0; pos < p1; pos++) {
-        float pr; uint32_t col;
-        entry(pos, pr, col);
+        const float pr = s_pr[pos];
         if (pr > thr) { tl[0] += 1.f; tl[1] += pr; }
         if (pr == thr) tl[2] += 1.f;
     }
@@ -574,11 +638,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     const float comp = vp_comp(gt4, thr, top_k, use_p ? top_p : 0.f, use_p != 0);
     // weights in list order; block scan; the first position whose running weight reaches u * total
     float wsum = 0.f;
-    for (uint32_t pos = p0; pos < p1; pos++) {
-        float pr; uint32_t col;
-        entry(pos, pr, col);
-        wsum += vp_weight_of(pr, thr, comp);
-    }
+    for (uint32_t pos = p0; pos < p1; pos++) wsum += vp_weight_of(s_pr[pos], thr, comp);
     const float incl = warp_scan_desc(wsum, lane);
     if (lane == 31) s_scan[w] = incl;
     if (t == 0) s_hit = 0x7fffffff;
@@ -596,9 +656,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     float run = pre + incl - wsum;   // weight before this thread's block
     int last_kept = -1;
     for (uint32_t pos = p0; pos < p1; pos++) {
-        float pr; uint32_t col;
-        entry(pos, pr, col);
-        const float wv = vp_weight_of(pr, thr, comp);
+        const float wv = vp_weight_of(s_pr[pos], thr, comp);
         if (wv > 0.f) {
             run += wv;
             last_kept = (int)pos;
@@ -640,16 +698,17 @@ __global__ void vpf_advance_kernel(unsigned char* states, int B) {
 
 struct VpfLayout { size_t stat1, stat2, tcnt, tent, send, send_cnt, gath, gath_cnt, ids, valid, total; };
 static VpfLayout vpf_layout(long long B, int world, int S) {
+    const int lmax = f_lmax(world);
     VpfLayout l;
     size_t o = 0;
     auto take = [&](size_t n) { size_t at = o; o += (n + 63) & ~(size_t)63; return at; };
-    l.stat1 = take((size_t)B * S * 2);
-    l.stat2 = take((size_t)B * S * 4);
+    l.stat1 = take((size_t)B * S);
+    l.stat2 = take((size_t)B * S * kFStat2);
     l.tcnt = take((size_t)B * S * kVpThreads);
     l.tent = take((size_t)B * S * kVpThreads * kFCap * 2);
-    l.send = take((size_t)B * kFLmax * 2);
+    l.send = take((size_t)B * lmax * 2);
     l.send_cnt = take(B);
-    l.gath = take((size_t)world * B * kFLmax * 2);
+    l.gath = take((size_t)world * B * lmax * 2);
     l.gath_cnt = take((size_t)world * B);
     l.ids = take(B);
     l.valid = take(B);
@@ -674,15 +733,16 @@ size_t rs_vp_workspace_bytes(int64_t B, int32_t world) {
     return (rs::vp_layout(B, world).total + rs::vpf_layout(B, world, rs::kFMaxSub).total) * sizeof(float);
 }
 
-int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets_floats[10]) {
+int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets_floats[11]) {
     if (B <= 0 || world <= 0 || !offsets_floats) return RS_ERR_BATCH;
     const size_t base = rs::vp_layout(B, world).total;
     const int S = rs::vpf_subblocks(B, V_local);
     const rs::VpfLayout l = rs::vpf_layout(B, world, S);
-    const size_t o[10] = {l.stat1, l.stat2, l.send, l.send_cnt, l.gath, l.gath_cnt, l.ids, l.valid, (size_t)S, (size_t)rs::kFLmax};
+    const size_t o[10] = {l.stat1, l.stat2, l.send, l.send_cnt, l.gath, l.gath_cnt, l.ids, l.valid, (size_t)S, (size_t)rs::f_lmax(world)};
     for (int i = 0; i < 8; i++) offsets_floats[i] = (int64_t)(base + o[i]);
     offsets_floats[8] = (int64_t)o[8];
     offsets_floats[9] = (int64_t)o[9];
+    offsets_floats[10] = (int64_t)rs::kFStat2;
     return RS_OK;
 }
 
@@ -755,26 +815,33 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
                     (float)c->repetition_penalty, (float)c->penalty_decay);
             }
             break;
-        case RS_VPF_MAX: case RS_VPF_SUM: case RS_VPF_COMPACT: case RS_VPF_FINISH: case RS_VPF_ADVANCE: {
+        case RS_VPF_MAX: case RS_VPF_SUM: case RS_VPF_EXTRACT: case RS_VPF_COMPACT: case RS_VPF_FINISH: case RS_VPF_ADVANCE: {
             const int S = vpf_subblocks(B, n);
             const VpfLayout f = vpf_layout(B, c->world, S);
+            const int lmax = f_lmax(c->world);
             float* fw = ws + l.total;
             uint32_t* uw = reinterpret_cast<uint32_t*>(fw);
-            int sel_rank = 2;                                   // top-p only: try the ~64 largest of every sub-block
-            if (top_k < V) sel_rank = (int)((top_k + 2 + 31) / 32);
-            if (sel_rank > 32) sel_rank = 32;
             if (stage == RS_VPF_MAX)
-                vpf_max_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, sel_rank, fw + f.stat1);
+                vpf_max_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1);
             else if (stage == RS_VPF_SUM)
                 vpf_sum_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
-                                                                fw + f.stat2, uw + f.tcnt, uw + f.tent, (long long)c->col0);
+                                                                fw + f.stat2);
+            else if (stage == RS_VPF_EXTRACT)
+                vpf_extract_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
+                                                                    fw + f.stat2, fk, fp, uw + f.tcnt, uw + f.tent,
+                                                                    (long long)c->col0);
             else if (stage == RS_VPF_COMPACT)
-                vpf_compact_kernel<<<grid, kVpThreads, 0, st>>>(S, uw + f.tcnt, uw + f.tent, uw + f.send, uw + f.send_cnt);
-            else if (stage == RS_VPF_FINISH)
-                vpf_finish_kernel<<<grid, kVpThreads, 0, st>>>((int)B, S, c->world, fw + f.stat1, fw + f.stat2, uw + f.gath,
+                vpf_compact_kernel<<<grid, kVpThreads, 0, st>>>(S, lmax, uw + f.tcnt, uw + f.tent, uw + f.send, uw + f.send_cnt);
+            else if (stage == RS_VPF_FINISH) {
+                static bool attr_done = false;
+                if (!attr_done) {
+                    cudaFuncSetAttribute(vpf_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+                    attr_done = true;
+                }
+                vpf_finish_kernel<<<grid, kVpThreads, (size_t)lmax * c->world * sizeof(float), st>>>((int)B, S, c->world, lmax, fw + f.stat1, fw + f.stat2, uw + f.gath,
                                                                uw + f.gath_cnt, fk, fp, use_p, (const unsigned char*)c->states,
                                                                (int*)(uw + f.ids), (int*)(uw + f.valid));
-            else
+            } else
                 vpf_advance_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((unsigned char*)c->states, (int)B);
             break;
         }

@@ -25,7 +25,7 @@ import torch.distributed as dist
 from . import abi
 
 STAGES = {"max": 0, "sum": 1, "round": 2, "tally": 3, "weight": 4, "pick": 5, "penalty": 6,
-          "f_max": 10, "f_sum": 11, "f_compact": 12, "f_finish": 13, "f_advance": 14}
+          "f_max": 10, "f_sum": 11, "f_compact": 12, "f_finish": 13, "f_advance": 14, "f_extract": 15}
 
 
 class CudaCompute:
@@ -76,12 +76,12 @@ class VocabParallelSampler:
         self.compute = compute or CudaCompute()
         # fast protocol (3 collectives): regions behind the staged protocol's
         self.fast = fast
-        fo = (C.c_int64 * 10)()
+        fo = (C.c_int64 * 11)()
         L.rs_vp_fast_layout(B, self.V_local, world, fo)
         f = [int(x) for x in fo]
         S, Lmax = f[8], f[9]
-        self.f_stat1 = self.ws[f[0]:f[0] + B * S * 2]
-        self.f_stat2 = self.ws[f[1]:f[1] + B * S * 4]
+        self.f_stat1 = self.ws[f[0]:f[0] + B * S]
+        self.f_stat2 = self.ws[f[1]:f[1] + B * S * f[10]]
         self.f_send = self.ws[f[2]:f[2] + B * Lmax * 2]
         self.f_send_cnt = self.ws[f[3]:f[3] + B]
         self.f_gath = self.ws[f[4]:f[4] + world * B * Lmax * 2]
@@ -107,6 +107,7 @@ class VocabParallelSampler:
         self._reduce(self.f_stat1, dist.ReduceOp.MAX)
         c.stage("f_sum")
         self._reduce(self.f_stat2, dist.ReduceOp.SUM)
+        c.stage("f_extract")
         c.stage("f_compact")
         self._gather(self.f_gath, self.f_send)
         self._gather(self.f_gath_cnt, self.f_send_cnt)

@@ -29,6 +29,7 @@ def emulated_sample(samplers, shards, states, temp, k, p, pens=None, fast=True):
                     region(s).copy_(red)
         fstep("f_max", lambda s: s.f_stat1, "max")
         fstep("f_sum", lambda s: s.f_stat2, "sum")
+        fstep("f_extract")
         fstep("f_compact")
         for s in samplers:          # the all-gather
             s.f_gath.copy_(torch.cat([x.f_send for x in samplers]))
