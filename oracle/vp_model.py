@@ -164,3 +164,135 @@ class NumpyCompute:
             self.pen[:] = new
         else:
             raise ValueError(name)
+
+
+class NumpyFastCompute(NumpyCompute):
+    """Adds the stages of the 3-collective protocol (candidate lists, one all-gather, redundant finish on every rank).
+
+    Same regions and same meaning of every reduced number as the CUDA kernels; the per-shard arithmetic is the plain
+    numpy statement (whole shard in sub-block 0, exact octave histogram)."""
+    BINS = 32
+
+    def _e(self):
+        gmax = self.s.f_stat1.numpy().reshape(self.s.B, -1).max(axis=1)
+        return np.exp2(self._x() - gmax[:, None]).astype(np.float32)
+
+    def _stat2(self):
+        s = self.s
+        return s.f_stat2.numpy().reshape(s.B, -1, 2 + 2 * self.BINS)
+
+    def _denom_bound(self):
+        st = self._stat2()
+        denom = st[:, :, 0].sum(axis=1, dtype=np.float32)
+        bound = np.zeros(self.s.B, dtype=np.float32)
+        for b in range(self.s.B):
+            cm = cc = np.float32(0)
+            for k in range(self.BINS):
+                cm = np.float32(cm + st[b, :, 2 + 2 * k].sum(dtype=np.float32))
+                cc = np.float32(cc + st[b, :, 3 + 2 * k].sum(dtype=np.float32))
+                if cc > self.fk + 1 or cm > np.float32(self.top_p * denom[b]) * np.float32(1.001):
+                    bound[b] = np.float32(2.0 ** -(k + 1))
+                    break
+        return denom, bound
+
+    def stage(self, name, rnd=0):
+        s = self.s
+        B = s.B
+        if name == "f_max":
+            s.f_stat1.numpy().reshape(B, -1)[:] = self._x().max(axis=1)[:, None]
+        elif name == "f_sum":
+            e = self._e()
+            st = self._stat2()
+            st[:] = 0
+            st[:, 0, 0] = e.sum(axis=1, dtype=np.float32)
+            with np.errstate(divide="ignore"):
+                k = np.floor(-np.log2(e.astype(np.float64)))          # e in (2^-(k+1), 2^-k]
+            k = np.where(e >= 1, 0, np.where(np.exp2(-k) == e, k - 1, k))
+            for b in range(B):
+                for kk in range(self.BINS):
+                    m = k[b] == kk
+                    st[b, 0, 2 + 2 * kk] = e[b][m].sum(dtype=np.float32)
+                    st[b, 0, 3 + 2 * kk] = np.float32(m.sum())
+        elif name == "f_extract":
+            e = self._e()
+            _, bound = self._denom_bound()
+            self._lists = [np.nonzero(e[b] >= bound[b])[0] if bound[b] > 0 else None for b in range(B)]
+            self._evals = e
+        elif name == "f_compact":
+            lmax = s.f_send.numel() // (2 * B)
+            send = s.f_send.numpy().view(np.uint32).reshape(B, lmax, 2)
+            cnt = s.f_send_cnt.numpy().view(np.uint32)
+            for b in range(B):
+                idx = self._lists[b]
+                if idx is None or len(idx) > lmax:
+                    cnt[b] = 0xffffffff
+                    continue
+                cnt[b] = len(idx)
+                send[b, :len(idx), 0] = self._evals[b][idx].view(np.uint32)
+                send[b, :len(idx), 1] = (idx + s.col0).astype(np.uint32)
+        elif name == "f_finish":
+            lmax = s.f_send.numel() // (2 * B)
+            gath = s.f_gath.numpy().view(np.uint32).reshape(s.world, B, lmax, 2)
+            gcnt = s.f_gath_cnt.numpy().view(np.uint32).reshape(s.world, B)
+            denom, bound = self._denom_bound()
+            ids, valid = s.f_ids.numpy(), s.f_valid.numpy()
+            for b in range(B):
+                ok = bool(bound[b] > 0) and bool((gcnt[:, b] <= lmax).all())
+                parts = [gath[r, b, :min(int(gcnt[r, b]), lmax)] for r in range(s.world)]
+                ent = np.concatenate(parts, axis=0)
+                p = (ent[:, 0].copy().view(np.float32) / denom[b]).astype(np.float32)
+                pb = p.view(np.uint32).astype(np.uint64)
+                left = np.uint64(np.float32(bound[b] / denom[b]).view(np.uint32)) + np.uint64(1)
+                right = np.uint64(0x3f800001)
+
+                def passes(piv):
+                    m = pb >= piv
+                    return (np.float32(m.sum()) < self.fk) and (p[m].sum(dtype=np.float32) < self.fp)
+                if passes(left):
+                    ok = False
+                for _ in range(8):
+                    w = right - left
+                    if w <= 1:
+                        break
+                    nl, nr, found = left, right, False
+                    for j in range(P):
+                        piv = left + ((w * np.uint64(j + 1)) >> np.uint64(4))
+                        if not passes(piv):
+                            nl = piv
+                        elif not found:
+                            nr, found = piv, True
+                    left, right = nl, nr
+                thr = np.uint32(left).view(np.float32)
+                gt, eq = p > thr, p == thr
+                sgtk, sgtp, seqk = np.float32(gt.sum()), p[gt].sum(dtype=np.float32), np.float32(eq.sum())
+                comp = np.float32(1)
+                if seqk > 0:
+                    if self.use_p:
+                        with np.errstate(all="ignore"):
+                            comp = min(_sf(np.float32((self.top_p - sgtp) / (thr * seqk))), comp)
+                    comp = max(min(_sf(np.float32((self.fk - sgtk) / seqk)), comp), np.float32(0))
+                wgt = np.where(p < thr, np.float32(0), np.where(eq, p * comp, p)).astype(np.float32)
+                tmp = self.states.copy()
+                u = np.float32(co.uniform(co.draw4(tmp, b)[0]))
+                cum = np.cumsum(wgt, dtype=np.float32)
+                target = np.float32(cum[-1] * u) if len(cum) else np.float32(0)
+                hit = np.nonzero((wgt > 0) & (target <= cum))[0]
+                kept = np.nonzero(wgt > 0)[0]
+                if len(kept) == 0:
+                    ids[b], valid[b] = 1, 0
+                    continue
+                pos = hit[0] if len(hit) else kept[-1]
+                ids[b] = int(ent[pos, 1]) + 1
+                valid[b] = 1 if ok else 0
+                self._thr = getattr(self, "_thr", dict())
+                self._thr[b] = thr
+        elif name == "f_advance":
+            for b in range(B):
+                co.draw4(self.states, b)
+        elif name == "penalty" and rnd == 1:
+            keep = s.ids.numpy().copy()
+            s.ids.numpy()[:] = s.f_ids.numpy()
+            super().stage("penalty")
+            s.ids.numpy()[:] = keep
+        else:
+            super().stage(name, rnd)

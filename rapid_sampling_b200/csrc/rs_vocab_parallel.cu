@@ -715,8 +715,8 @@ static VpfLayout vpf_layout(long long B, int world, int S) {
     l.total = o;
     return l;
 }
-// sub-blocks per row: enough CTAs to fill the GPU, but every thread keeps >= 16 float4 groups so that its maximum
-// is a meaningful sample (the candidate bound comes from thread maxima)
+// sub-blocks per row: enough CTAs to fill the GPU, but every thread keeps >= 16 float4 groups (a thread's
+// candidate slots are sized for a sparse sample of a long stripe)
 static int vpf_subblocks(long long B, long long n) {
     long long S = 296 / (B > 0 ? B : 1);
     const long long by_work = (n / 4) / (1024 * 16);

@@ -6,7 +6,7 @@ The driver below owns the SEQUENCE of stages and collectives; the per-shard arit
 model in and runs the driver over gloo).
 
 Fast protocol (default): 2 all-reduces + 1 all-gather.  Every shard extracts a short candidate list (elements above
-a bound derived from per-thread maxima), the lists are all-gathered and every rank finishes the row on the union
+a bound read off an all-reduced octave histogram of the row), the lists are all-gathered and every rank finishes the row on the union
 from identical data -- no id exchange.  If some row's list cannot settle its cutoff (flagged on the device, read by
 the host) the call is repeated with the staged protocol: 13 small collectives:
 
@@ -128,10 +128,11 @@ class VocabParallelSampler:
         c = self.compute
         c.bind(self, logits, states, penalties, float(temperature), int(top_k), float(top_p), float(presence_penalty),
                float(repetition_penalty), float(penalty_decay))
+        self.last_protocol = "staged"
         if self.fast:
             ids = self._sample_fast(penalties)
-            self.last_protocol = "fast" if ids is not None else "staged"
             if ids is not None:
+                self.last_protocol = "fast"
                 return ids
         c.stage("max")
         self._reduce(self.gmax, dist.ReduceOp.MAX)
