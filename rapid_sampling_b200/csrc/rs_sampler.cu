@@ -51,8 +51,9 @@ struct Params {
 
 // shared-memory map (bytes)
 constexpr int kXWords = 10;                      // words each warp contributes to an exchange
-constexpr int kMboxOff = 0;                      // 2 buffers of [kXWords][32 warps] words
-constexpr int kMboxBuf = kXWords * 32 * 4;
+constexpr int kXStride = 12;                     // words between two warps' records in a mailbox (16-byte aligned records)
+constexpr int kMboxOff = 0;                      // 2 buffers of [32 warps][kXStride] words
+constexpr int kMboxBuf = kXStride * 32 * 4;
 constexpr int kMiscOff = 2 * kMboxBuf;           // mbarriers, small scalars, 32 warp totals
 constexpr int kSlabOff = kMiscOff + 256;
 constexpr uint32_t kWaitPolls = 1u << 22;
@@ -152,7 +153,7 @@ __device__ __forceinline__ void append_candidates(float4 v, float beta_e, float*
 }
 
 template <int C, bool SMEM, bool LOWP>
-__global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler_kernel(const Params p) {
+__global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler_kernel(const Params p) {
     constexpr int L = kLanes / C;
     constexpr int WPC = L / 32;  // warps per CTA
     constexpr unsigned FULL = 0xffffffffu;
@@ -222,37 +223,42 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
         return v;
     };
     // ---- exchange of warp values across the cluster ----------------------------------------------------
-    // Every warp contributes kXWords words; word k of (virtual) warp w lands at box[k * 32 + w] in EVERY CTA's
-    // mailbox.  Lane l supplies word l >> 3 (a), word 4 + (l >> 3) (b) and, for l < 16, word 8 + (l >> 3) (c).
-    // The words travel as remote stores that count their bytes on an mbarrier of the destination CTA, so a
-    // CTA only waits for its own mailbox to fill (bounded poll) -- no cluster-wide barrier.  Two mailboxes
-    // alternate: a CTA can post exchange n+2 only after it has received everybody's n+1, which each CTA
-    // sends after it has finished reading n.
+    // Every warp contributes kXWords words; word k of (virtual) warp w lands at box[w * kXStride + k] in EVERY
+    // CTA's mailbox.  Lane l supplies word l >> 3 (a), word 4 + (l >> 3) (b) and, for l < 16, word 8 + (l >> 3)
+    // (c); the words are first collected in the lanes that send (lane r serves CTA r), so that a warp's record
+    // travels as three vector stores per destination instead of ten scalar ones.  The stores count their bytes
+    // on an mbarrier of the destination CTA, so a CTA only waits for its own mailbox to fill (bounded poll) --
+    // no cluster-wide barrier.  Two mailboxes alternate: a CTA can post exchange n+2 only after it has received
+    // everybody's n+1, which each CTA sends after it has finished reading n.
     int phase = 0;
     uint32_t xpar = 0;
     auto exchange = [&](uint32_t a, uint32_t bq, uint32_t c2) -> const uint32_t* {
         uint32_t* box = reinterpret_cast<uint32_t*>(smem + kMboxOff + phase * kMboxBuf);
-        const int k = lane >> 3, r = lane & 7;
+        uint32_t wa[4], wb[4], wc[2];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            wa[k] = __shfl_sync(FULL, a, k * 8);
+            wb[k] = __shfl_sync(FULL, bq, k * 8);
+        }
+        wc[0] = __shfl_sync(FULL, c2, 0);
+        wc[1] = __shfl_sync(FULL, c2, 8);
         if (C == 1) {
-            if (r == 0) {
-                box[k * 32 + wg] = a;
-                box[(4 + k) * 32 + wg] = bq;
-                if (lane < 16) box[(8 + k) * 32 + wg] = c2;
+            if (lane == 0) {
+                uint4* rec = reinterpret_cast<uint4*>(box + wg * kXStride);
+                rec[0] = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+                rec[1] = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+                *reinterpret_cast<uint2*>(rec + 2) = make_uint2(wc[0], wc[1]);
             }
             __syncthreads();
         } else {
             const uint32_t bar = smem_addr(xbar + phase);
-            if (t == 0) mbar_expect_tx(bar, (uint32_t)kMboxBuf);
-#pragma unroll
-            for (int rr = 0; rr < (C > 8 ? 2 : 1); rr++) {
-                const uint32_t dst_cta = (uint32_t)(r + 8 * rr);
-                if (dst_cta < (uint32_t)C) {
-                    const uint32_t base = map_to_cta(smem_addr(box), dst_cta);
-                    const uint32_t rbar = map_to_cta(bar, dst_cta);
-                    st_async_u32(base + (k * 32 + wg) * 4, a, rbar);
-                    st_async_u32(base + ((4 + k) * 32 + wg) * 4, bq, rbar);
-                    if (lane < 16) st_async_u32(base + ((8 + k) * 32 + wg) * 4, c2, rbar);
-                }
+            if (t == 0) mbar_expect_tx(bar, (uint32_t)(kXWords * 32 * 4));
+            if (lane < C) {
+                const uint32_t dst = map_to_cta(smem_addr(box + wg * kXStride), (uint32_t)lane);
+                const uint32_t rbar = map_to_cta(bar, (uint32_t)lane);
+                st_async_v4(dst, wa[0], wa[1], wa[2], wa[3], rbar);
+                st_async_v4(dst + 16, wb[0], wb[1], wb[2], wb[3], rbar);
+                st_async_v2(dst + 32, wc[0], wc[1], rbar);
             }
             if (!mbar_wait_bounded(bar, (xpar >> phase) & 1u, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
         }
@@ -260,6 +266,8 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
         phase ^= 1;
         return box;
     };
+    // word k of virtual warp w in a mailbox
+    auto bx = [&](const uint32_t* box, int k, int w) -> uint32_t { return box[w * kXStride + k]; };
     const int xk = lane >> 3;   // which of four values this lane forwards
     auto pick4 = [&](uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3) -> uint32_t {
         return xk == 0 ? v0 : xk == 1 ? v1 : xk == 2 ? v2 : v3;
@@ -306,18 +314,13 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
         mxv = __reduce_max_sync(FULL, mxv);
         const float cf = __uint2float_rn(pick4(c01 & 0xffffu, c01 >> 16, c23 & 0xffffu, c23 >> 16));
         const uint32_t* box = exchange(__float_as_uint(x), __float_as_uint(cf), xk == 0 ? mn : mxv);
-        vmin = __reduce_min_sync(FULL, box[8 * 32 + lane]);
-        vmax = __reduce_max_sync(FULL, box[9 * 32 + lane]);
+        vmin = __reduce_min_sync(FULL, bx(box, 8, lane));
+        vmax = __reduce_max_sync(FULL, bx(box, 9, lane));
         float sacc = 0.f;
         if (lane < 8) {
-            const float4* col = reinterpret_cast<const float4*>(box + lane * 32);
-            float4 q = col[0];
-            sacc = q.x; sacc += q.y; sacc += q.z; sacc += q.w;
+            sacc = __uint_as_float(bx(box, lane, 0));
 #pragma unroll
-            for (int w4 = 1; w4 < 8; w4++) {
-                q = col[w4];
-                sacc += q.x; sacc += q.y; sacc += q.z; sacc += q.w;
-            }
+            for (int w = 1; w < kWarps; w++) sacc += __uint_as_float(bx(box, lane, w));
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -417,8 +420,8 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     float beta_x;
     {
         const uint32_t* box = exchange(pick4(__float_as_uint(mx), __float_as_uint(wsel), 0u, 0u), 0u, 0u);
-        mx = warp_max(__uint_as_float(box[lane]));
-        beta_x = warp_min(__uint_as_float(box[32 + lane]));   // every warp holds >= sel_rank elements >= beta_x
+        mx = warp_max(__uint_as_float(bx(box, 0, lane)));
+        beta_x = warp_min(__uint_as_float(bx(box, 1, lane)));   // every warp holds >= sel_rank elements >= beta_x
     }
     stamp(3);   // first exchange done
     const bool try_cand = (sel_rank > 0);
@@ -505,13 +508,13 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
         csum = warp_tree_sum(csum);
         const uint32_t* box = exchange(pick4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow),
                                        pick4(wnc, wns, __float_as_uint(csum), 0u), 0u);
-        denom = warp_tree_sum(__uint_as_float(box[lane]));  // tree over the 32 warp partials (sampling.cu:29-33)
-        emin = warp_min(__uint_as_float(box[32 + lane]));
-        emax = warp_max(__uint_as_float(box[64 + lane]));
-        cand_ok = try_cand && (__reduce_add_sync(FULL, box[96 + lane]) == 0u);
-        ncand = __reduce_add_sync(FULL, box[128 + lane]);
-        nstrict = __reduce_add_sync(FULL, box[160 + lane]);
-        const float cmass = warp_tree_sum(__uint_as_float(box[192 + lane])) / denom;   // any order: a forecast only
+        denom = warp_tree_sum(__uint_as_float(bx(box, 0, lane)));  // tree over the 32 warp partials (sampling.cu:29-33)
+        emin = warp_min(__uint_as_float(bx(box, 1, lane)));
+        emax = warp_max(__uint_as_float(bx(box, 2, lane)));
+        cand_ok = try_cand && (__reduce_add_sync(FULL, bx(box, 3, lane)) == 0u);
+        ncand = __reduce_add_sync(FULL, bx(box, 4, lane));
+        nstrict = __reduce_add_sync(FULL, bx(box, 5, lane));
+        const float cmass = warp_tree_sum(__uint_as_float(bx(box, 6, lane))) / denom;   // any order: a forecast only
         const bool enough = (use_cnt && nstrict > (uint32_t)p.top_k) || cmass > p.top_p * 1.001f;
         return !cand_ok || enough || last || !(beta_e > 0.f);
     };
@@ -742,16 +745,13 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 7 : 1) sampler
     float randp;
     {
         // sequential prefix over the warp totals (sampling.cu:85-92)
-        const float4* wt4 = reinterpret_cast<const float4*>(lbox);
         float pre[kWarps];
         float s0 = 0.f;
 #pragma unroll
-        for (int w4 = 0; w4 < 8; w4++) {
-            const float4 q = wt4[w4];
-            s0 = (w4 == 0) ? q.x : s0 + q.x; pre[4 * w4] = s0;
-            s0 += q.y; pre[4 * w4 + 1] = s0;
-            s0 += q.z; pre[4 * w4 + 2] = s0;
-            s0 += q.w; pre[4 * w4 + 3] = s0;
+        for (int w = 0; w < kWarps; w++) {
+            const float q = __uint_as_float(bx(lbox, 0, w));
+            s0 = (w == 0) ? q : s0 + q;
+            pre[w] = s0;
         }
         sum_p = s0;
         randp = sum_p * ux;
