@@ -51,6 +51,7 @@ struct Params {
 
 // shared-memory map (bytes)
 constexpr int kXWords = 10;                      // words each warp contributes to an exchange
+template <int N> struct Packets { static constexpr int value = N; };   // 16-byte packets of an exchange record
 constexpr int kXStride = 12;                     // words between two warps' records in a mailbox (16-byte aligned records)
 constexpr int kMboxOff = 0;                      // 2 buffers of [32 warps][kXStride] words
 constexpr int kMboxBuf = kXStride * 32 * 4;
@@ -139,6 +140,17 @@ __device__ __forceinline__ float4 scaled4(float4 l, float scale) {
     if (probe != probe) v = sanitize4(v);
     return v;
 }
+// Four penalised scaled logits, sanitize((sanitize(l) - pen) * scale).  If the plain product is finite, the logit
+// was finite too (an Inf / NaN logit keeps the product non-finite for any finite or non-finite penalty), both
+// sanitisers were identities and the product is the result; anything else takes the exact formula.
+__device__ __forceinline__ float4 scaled4_rep(float4 l, float4 q, float scale) {
+    float4 v = make_float4((l.x - q.x) * scale, (l.y - q.y) * scale, (l.z - q.z) * scale, (l.w - q.w) * scale);
+    const float probe = fmaf(v.w, 0.f, fmaf(v.z, 0.f, fmaf(v.y, 0.f, v.x * 0.f)));
+    if (probe != probe)
+        v = make_float4(scaled_logit(l.x, q.x, true, scale), scaled_logit(l.y, q.y, true, scale),
+                        scaled_logit(l.z, q.z, true, scale), scaled_logit(l.w, q.w, true, scale));
+    return v;
+}
 // Appends the candidates of one float4 group to the lane's list (rare; out of line).
 __device__ __forceinline__ void append_candidates(float4 v, float beta_e, float* list, int stride4, int cap, int& nc, int& ns) {
     const float e[4] = {v.x, v.y, v.z, v.w};
@@ -213,10 +225,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         float4 v = ldrow4(s * kLanes + tg);
         if (rep) {
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
-            v.x = scaled_logit(v.x, q4.x, true, p.scale);
-            v.y = scaled_logit(v.y, q4.y, true, p.scale);
-            v.z = scaled_logit(v.z, q4.z, true, p.scale);
-            v.w = scaled_logit(v.w, q4.w, true, p.scale);
+            v = scaled4_rep(v, q4, p.scale);
         } else {
             v = scaled4(v, p.scale);
         }
@@ -232,33 +241,36 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     // everybody's n+1, which each CTA sends after it has finished reading n.
     int phase = 0;
     uint32_t xpar = 0;
-    auto exchange = [&](uint32_t a, uint32_t bq, uint32_t c2) -> const uint32_t* {
+    auto exchange = [&](auto packets, uint32_t a, uint32_t bq, uint32_t c2) -> const uint32_t* {
+        constexpr int NP = decltype(packets)::value;   // 1: words 0-3 (a); 2: + words 4-7 (b); 3: + words 8-9 (c)
         uint32_t* box = reinterpret_cast<uint32_t*>(smem + kMboxOff + phase * kMboxBuf);
-        uint32_t wa[4], wb[4], wc[2];
+        uint32_t wa[4], wb[4] = {0u, 0u, 0u, 0u}, wc[2] = {0u, 0u};
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             wa[k] = __shfl_sync(FULL, a, k * 8);
-            wb[k] = __shfl_sync(FULL, bq, k * 8);
+            if (NP >= 2) wb[k] = __shfl_sync(FULL, bq, k * 8);
         }
-        wc[0] = __shfl_sync(FULL, c2, 0);
-        wc[1] = __shfl_sync(FULL, c2, 8);
+        if (NP >= 3) {
+            wc[0] = __shfl_sync(FULL, c2, 0);
+            wc[1] = __shfl_sync(FULL, c2, 8);
+        }
         if (C == 1) {
             if (lane == 0) {
                 uint4* rec = reinterpret_cast<uint4*>(box + wg * kXStride);
                 rec[0] = make_uint4(wa[0], wa[1], wa[2], wa[3]);
-                rec[1] = make_uint4(wb[0], wb[1], wb[2], wb[3]);
-                *reinterpret_cast<uint2*>(rec + 2) = make_uint2(wc[0], wc[1]);
+                if (NP >= 2) rec[1] = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+                if (NP >= 3) *reinterpret_cast<uint2*>(rec + 2) = make_uint2(wc[0], wc[1]);
             }
             __syncthreads();
         } else {
             const uint32_t bar = smem_addr(xbar + phase);
-            if (t == 0) mbar_expect_tx(bar, (uint32_t)(kXWords * 32 * 4));
+            if (t == 0) mbar_expect_tx(bar, (uint32_t)((NP == 1 ? 4 : NP == 2 ? 8 : kXWords) * 32 * 4));
             if (lane < C) {
                 const uint32_t dst = map_to_cta(smem_addr(box + wg * kXStride), (uint32_t)lane);
                 const uint32_t rbar = map_to_cta(bar, (uint32_t)lane);
                 st_async_v4(dst, wa[0], wa[1], wa[2], wa[3], rbar);
-                st_async_v4(dst + 16, wb[0], wb[1], wb[2], wb[3], rbar);
-                st_async_v2(dst + 32, wc[0], wc[1], rbar);
+                if (NP >= 2) st_async_v4(dst + 16, wb[0], wb[1], wb[2], wb[3], rbar);
+                if (NP >= 3) st_async_v2(dst + 32, wc[0], wc[1], rbar);
             }
             if (!mbar_wait_bounded(bar, (xpar >> phase) & 1u, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
         }
@@ -313,7 +325,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         mn = __reduce_min_sync(FULL, mn);
         mxv = __reduce_max_sync(FULL, mxv);
         const float cf = __uint2float_rn(pick4(c01 & 0xffffu, c01 >> 16, c23 & 0xffffu, c23 >> 16));
-        const uint32_t* box = exchange(__float_as_uint(x), __float_as_uint(cf), xk == 0 ? mn : mxv);
+        const uint32_t* box = exchange(Packets<3>(), __float_as_uint(x), __float_as_uint(cf), xk == 0 ? mn : mxv);
         vmin = __reduce_min_sync(FULL, bx(box, 8, lane));
         vmax = __reduce_max_sync(FULL, bx(box, 9, lane));
         float sacc = 0.f;
@@ -385,10 +397,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         for (int s = 0; s < Kt; s++) {
             float4 v = bulk_load ? row.ld(s) : ldrow4(s * kLanes + tg);
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
-            v.x = scaled_logit(v.x, q4.x, true, p.scale);
-            v.y = scaled_logit(v.y, q4.y, true, p.scale);
-            v.z = scaled_logit(v.z, q4.z, true, p.scale);
-            v.w = scaled_logit(v.w, q4.w, true, p.scale);
+            v = scaled4_rep(v, q4, p.scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
             if (SMEM) row.st(s, v);
         }
@@ -419,7 +428,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     if (C > 1) cluster_wait();
     float beta_x;
     {
-        const uint32_t* box = exchange(pick4(__float_as_uint(mx), __float_as_uint(wsel), 0u, 0u), 0u, 0u);
+        const uint32_t* box = exchange(Packets<1>(), pick4(__float_as_uint(mx), __float_as_uint(wsel), 0u, 0u), 0u, 0u);
         mx = warp_max(__uint_as_float(bx(box, 0, lane)));
         beta_x = warp_min(__uint_as_float(bx(box, 1, lane)));   // every warp holds >= sel_rank elements >= beta_x
     }
@@ -477,12 +486,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     #pragma unroll
                     for (int j = 0; j < G; j++) {
                         if (s0 + j < Kt) {
-                            float4 v = lb[j];
-                            v.x = scaled_logit(v.x, qb[j].x, true, p.scale);
-                            v.y = scaled_logit(v.y, qb[j].y, true, p.scale);
-                            v.z = scaled_logit(v.z, qb[j].z, true, p.scale);
-                            v.w = scaled_logit(v.w, qb[j].w, true, p.scale);
-                            pass2_slot(v);
+                            pass2_slot(scaled4_rep(lb[j], qb[j], p.scale));
                         }
                     }
                 }
@@ -506,7 +510,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         const unsigned overflow = __any_sync(FULL, nc > cap) ? 1u : 0u;
         const uint32_t wnc = __reduce_add_sync(FULL, (uint32_t)nc), wns = __reduce_add_sync(FULL, (uint32_t)ns);
         csum = warp_tree_sum(csum);
-        const uint32_t* box = exchange(pick4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow),
+        const uint32_t* box = exchange(Packets<2>(), pick4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow),
                                        pick4(wnc, wns, __float_as_uint(csum), 0u), 0u);
         denom = warp_tree_sum(__uint_as_float(bx(box, 0, lane)));  // tree over the 32 warp partials (sampling.cu:29-33)
         emin = warp_min(__uint_as_float(bx(box, 1, lane)));
@@ -739,7 +743,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     // ---- lane pick (sampling.cu:699-723) -----------------------------------------------------
     const float actual_p = gtp + (thr * eqk) * comp;
     const float incl = warp_scan_desc(actual_p, lane);
-    const uint32_t* lbox = exchange(__float_as_uint(__shfl_sync(FULL, incl, 31)), 0u, 0u);   // word 0: warp total
+    const uint32_t* lbox = exchange(Packets<1>(), __float_as_uint(__shfl_sync(FULL, incl, 31)), 0u, 0u);   // word 0: warp total
     float pre_prev = 0.f, sum_p;   // prefix of the warps before mine; total
     int own_w = -1;                // first warp whose inclusive prefix reaches randp
     float randp;
@@ -854,10 +858,15 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
             const int i4 = s * kLanes + tg;
             float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + i4);
             float e[4] = {q4.x, q4.y, q4.z, q4.w};
+            if (i4 != (token >> 2)) {   // token is -1 outside the owner CTA: no group matches
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float old = e[j];
-                e[j] = fmaf(old, p.decay, (i4 * 4 + j != token) ? 0.f : (old == 0.f ? p.presence : p.repetition));
+                for (int j = 0; j < 4; j++) e[j] = fmaf(e[j], p.decay, 0.f);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float old = e[j];
+                    e[j] = fmaf(old, p.decay, (i4 * 4 + j != token) ? 0.f : (old == 0.f ? p.presence : p.repetition));
+                }
             }
             reinterpret_cast<float4*>(prow)[i4] = make_float4(e[0], e[1], e[2], e[3]);
         }
