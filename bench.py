@@ -15,7 +15,8 @@ Under torchrun each rank takes the same per-GPU batch (weak scaling); rows are i
 is no collective on the data path -- only the barrier and the max-over-ranks of the timings.
 `--impl reference` times the CPU restatement of the reference (the reference has no CPU code of its
 own) on rank 0; `--impl reference-cuda` times the reference's own CUDA extension (oracle/_ref) on the
-same workload, for the latency comparison against the original kernel.
+same workload, for the latency comparison against the original kernel.  `--sweep small|full` runs a parameter
+sweep in the shape of the reference's own (B x V x top_p x top_k x five distributions) and writes a table.
 """
 import argparse
 import json
@@ -24,6 +25,8 @@ import statistics
 import sys
 import threading
 import time
+
+import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -224,6 +227,81 @@ def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch,
         dist.destroy_process_group()
 
 
+SWEEP_GRIDS = {
+    # the reference's own grid (bench.py:32-35): 12000 combinations
+    "full": dict(B=[512, 256, 128, 64, 32, 16, 8, 4, 2, 1], V=[262144, 151936, 131072, 100256, 65536, 50304, 32768, 256],
+                 p=[0.1, 0.3, 0.7, 0.9, 1], k=[-1, 1, 10, 100, 1000, 10000]),
+    # a cut through it that finishes in about a minute
+    "small": dict(B=[128, 16, 1], V=[262144, 151936, 32768, 256], p=[0.1, 0.9, 1], k=[-1, 1, 100, 10000]),
+}
+
+
+def sweep_logits(kind, B, V, dev, torch):
+    """The five synthetic distributions of the reference's sweep (bench.py:66-72)."""
+    if kind == 0:
+        return torch.zeros(B, V, dtype=torch.float32, device=dev)
+    if kind == 1:
+        return torch.rand(B, V, dtype=torch.float32, device=dev)
+    if kind == 2:
+        return torch.randn(B, V, dtype=torch.float32, device=dev) / 2
+    if kind == 3:
+        return torch.randn(B, V, dtype=torch.float32, device=dev) * 3
+    return torch.rand(B, V, dtype=torch.float32, device=dev) * 4
+
+
+def run_sweep(a):
+    """Breadth run in the shape of the reference's sweep: B x V x top_p x top_k x 5 distributions, 5 repetitions each,
+    per-call wall time with a synchronise on both sides (the reference's method, bench.py:73-92), median.  Where the
+    reference's CUDA kernel is available it is timed on the same logits and its ids are compared with ours."""
+    import torch
+    import rapid_sampling_b200 as rs
+    from oracle import build_ref
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    ext = rs._load_ext()
+    ref = build_ref.load_ref()
+    g = SWEEP_GRIDS[a.sweep]
+    torch.manual_seed(0)
+    rows, mismatched = [], 0
+
+    def timed(f):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = f()
+        torch.cuda.synchronize()
+        return out, (time.perf_counter() - t0) * 1e6
+    for V in g["V"]:
+        for B in g["B"]:
+            for p in g["p"]:
+                for k in g["k"]:
+                    for kind in range(5):
+                        st_o = ext.setup_rand(0, B)
+                        st_r = ref.setup_rand(0, B) if ref is not None else None
+                        t_o, t_r, bad = [], [], 0
+                        for _ in range(5):
+                            lg = sweep_logits(kind, B, V, dev, torch)
+                            out_o, dt = timed(lambda: ext.batch_sampling_temperature_topk_topp(lg, st_o, 1.0, k, float(p)))
+                            t_o.append(dt)
+                            if ref is not None:
+                                out_r, dt = timed(lambda: ref.batch_sampling_temperature_topk_topp(lg, st_r, 1.0, k, float(p)))
+                                t_r.append(dt)
+                                bad += int((out_o != out_r).sum().item())
+                        mismatched += bad
+                        rows.append({"B": B, "V": V, "top_p": p, "top_k": k, "logit_type": kind,
+                                     "ours_us": float(np.median(t_o)),
+                                     "reference_cuda_us": float(np.median(t_r)) if t_r else None, "ids_differ": bad})
+    with open(a.sweep_out, "w") as f:
+        json.dump(rows, f)
+    line = {"sweep": a.sweep, "combinations": len(rows), "repetitions": 5, "ours_median_us": float(np.median([r["ours_us"] for r in rows])),
+            "results_file": a.sweep_out}
+    if ref is not None:
+        ratio = np.array([r["reference_cuda_us"] / r["ours_us"] for r in rows])
+        line.update(reference_cuda_median_us=float(np.median([r["reference_cuda_us"] for r in rows])),
+                    speedup_geomean=float(np.exp(np.log(ratio).mean())), speedup_min=float(ratio.min()),
+                    speedup_max=float(ratio.max()), ids_differ=mismatched)
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -234,7 +312,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"], help="storage type of the logits (ours only)")
     ap.add_argument("--vp", action="store_true", help="vocab-parallel: every rank holds V/N columns of every row")
+    ap.add_argument("--sweep", choices=sorted(SWEEP_GRIDS), help="run the reference-shaped parameter sweep instead (one GPU)")
+    ap.add_argument("--sweep-out", default="sweep_results.json")
     a = ap.parse_args()
+    if a.sweep:
+        return run_sweep(a)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -107,6 +107,27 @@ int rs_sample_typed(const void* logits_device, int32_t logits_dtype, int64_t B, 
                     rs_trace* trace_device);
 
 /*
+ * Per-row parameters.  No counterpart in the reference, whose host functions take one scalar temperature / top_k /
+ * top_p per call (sampling.cpp:2-3); a serving batch mixes requests with different settings.
+ * temperature_device / top_k_device / top_p_device are device arrays of B values (float32 / int32 / float32);
+ * a NULL array stands for the neutral value in every row (temperature 1, top_k -1, top_p 1).  Each row is
+ * sampled exactly as a one-row call of rs_sample_typed with that row's values would sample it (same checks and
+ * remaps, sampling.cu:458-486, applied on the device; same ids, states and penalties), except that a temperature
+ * outside [0.001, 1000] cannot be refused by a call that does not read the array: such a row is sampled at
+ * temperature 1 and the device status word is set to RS_ERR_TEMPERATURE (rs_device_status).
+ * out_prob_device (optional, B floats): the sampled id's probability under the full softmax of the scaled /
+ * penalised row.  out_kept_mass_device (optional, B floats): the probability mass of the kept set the id was
+ * drawn from (boundary ties counted with their fractional weight, sampling.cu:690-696).
+ * The workspace needs rs_rows_workspace_bytes(B, V) bytes, zero-initialised once, 256-byte aligned.
+ */
+size_t rs_rows_workspace_bytes(int64_t B, int64_t V);
+int rs_sample_rows(const void* logits_device, int32_t logits_dtype, int64_t B, int64_t T, int64_t V,
+                   float* penalties_device, void* states_device, int32_t* out_device, const float* temperature_device,
+                   const int32_t* top_k_device, const float* top_p_device, double presence_penalty,
+                   double repetition_penalty, double penalty_decay, float* out_prob_device, float* out_kept_mass_device,
+                   void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
  * Host-buffer convenience around rs_sample for callers that hold logits in (pinned) host memory:
  * copies logits[:, T-1, :] to `staging_device` (B*V floats), samples, copies the ids back to
  * out_host and synchronises `stream`.  Penalties and states stay on the device.

@@ -57,10 +57,20 @@ def batch_sampling_repetition_temperature_topk_topp_any(logits, penalties, state
         logits, penalties, states, presence_penalty, repetition_penalty, penalty_decay, temperature, top_k, top_p)
 
 
+def batch_sampling_rows(logits, states, temperature=None, top_k=None, top_p=None, penalties=None, presence_penalty=0.0,
+                        repetition_penalty=0.0, penalty_decay=0.0, return_prob=False):
+    """Per-row parameters: `temperature` (float32), `top_k` (int32) and `top_p` (float32) are CUDA tensors of B values, or
+    None for the neutral value in every row.  Row b is sampled exactly as a one-row call of the functions above with its
+    values would sample it.  With `return_prob` the result is (ids, probability of each id under the full softmax, kept
+    probability mass).  The reference takes scalars only (sampling.cpp:2-3)."""
+    return _load_ext().batch_sampling_rows(logits, states, temperature, top_k, top_p, penalties, presence_penalty,
+                                           repetition_penalty, penalty_decay, return_prob)
+
+
 def kernel_launch_count():
     return _load_ext().kernel_launch_count()
 
 
 __all__ = ["setup_rand", "batch_sampling_temperature_topk_topp", "batch_sampling_repetition_temperature_topk_topp",
-           "batch_sampling_temperature_topk_topp_any", "batch_sampling_repetition_temperature_topk_topp_any",
+           "batch_sampling_temperature_topk_topp_any", "batch_sampling_repetition_temperature_topk_topp_any", "batch_sampling_rows",
            "kernel_launch_count"]

@@ -17,7 +17,7 @@ RS_STATE_BYTES = 64
 RS_DTYPE_F32, RS_DTYPE_F16, RS_DTYPE_BF16 = 0, 1, 2
 RS_STATIC_SCRATCH_FLOATS = 4194304
 
-SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_typed", "rs_sample_static_scratch",
+SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_typed", "rs_sample_static_scratch", "rs_rows_workspace_bytes", "rs_sample_rows",
            "rs_device_status", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_fast_layout", "rs_vp_stage", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
@@ -62,6 +62,10 @@ def load():
     L.rs_sample_host.argtypes = common + [vp, vp, vp, C.c_size_t, vp]
     L.rs_sample_typed.argtypes = [vp, C.c_int32] + common[1:] + [vp, C.c_size_t, vp, vp, vp]
     L.rs_sample_static_scratch.argtypes = common + [vp]
+    L.rs_rows_workspace_bytes.argtypes = [i64, i64]
+    L.rs_rows_workspace_bytes.restype = C.c_size_t
+    L.rs_sample_rows.argtypes = [vp, C.c_int32, i64, i64, i64, vp, vp, vp, vp, vp, vp, C.c_double, C.c_double, C.c_double,
+                                 vp, vp, vp, C.c_size_t, vp]
     L.rs_vp_workspace_bytes.argtypes = [i64, C.c_int32]
     L.rs_vp_workspace_bytes.restype = C.c_size_t
     L.rs_vp_layout.argtypes = [i64, C.c_int32, C.POINTER(C.c_int64)]

@@ -47,6 +47,15 @@ struct Params {
     int sel_rank;            // 0 = no candidate shortcut; else rank of the per-warp thread maximum used as bound
     int cand_slots;          // float4 slots per lane of the candidate buffer (shared-memory variant)
     float scale, top_p, presence, repetition, decay;
+    const struct RowArgs* rows;   // per-row parameters (ROWP kernels only), else null
+    float* out_prob;         // optional B: probability of the sampled id (ROWP kernels only)
+    float* out_kept;         // optional B: kept probability mass the id was drawn from (ROWP kernels only)
+};
+
+// Normalised parameters of one row, made on the device from the caller's per-row tensors.
+struct __align__(32) RowArgs {
+    int kind, top_k, sel_rank, pad0;
+    float scale, top_p, pad1, pad2;
 };
 
 // shared-memory map (bytes)
@@ -164,7 +173,7 @@ __device__ __forceinline__ void append_candidates(float4 v, float beta_e, float*
     }
 }
 
-template <int C, bool SMEM, bool LOWP>
+template <int C, bool SMEM, bool LOWP, bool ROWP>
 __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler_kernel(const Params p) {
     constexpr int L = kLanes / C;
     constexpr int WPC = L / 32;  // warps per CTA
@@ -177,8 +186,15 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     const int wg = tg >> 5;             // virtual warp
     const int V = p.V, V4 = V >> 2;
     const int Kt = (tg < V4) ? ((V4 - tg + kLanes - 1) >> 10) : 0;
-    const bool rep = (p.kind == kRepetition);
-    const bool use_cnt = (p.kind != kTopP);
+    // per-call parameters, or (ROWP) this row's own
+    int a_kind = p.kind, a_top_k = p.top_k, a_sel_rank = p.sel_rank;
+    float a_scale = p.scale, a_top_p = p.top_p;
+    if (ROWP) {
+        const RowArgs ra = p.rows[b];
+        a_kind = ra.kind; a_top_k = ra.top_k; a_sel_rank = ra.sel_rank; a_scale = ra.scale; a_top_p = ra.top_p;
+    }
+    const bool rep = (a_kind == kRepetition);
+    const bool use_cnt = (a_kind != kTopP);
     const int dtype = LOWP ? p.dtype : RS_DTYPE_F32;   // fp32 rows keep a kernel of their own: no type tests in its loops
     const char* lrow_b = reinterpret_cast<const char*>(p.logits) + (long long)b * p.row_stride * (dtype == RS_DTYPE_F32 ? 4 : 2);
     const float* lrow = reinterpret_cast<const float*>(lrow_b);   // valid as such for fp32 logits only
@@ -225,9 +241,9 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         float4 v = ldrow4(s * kLanes + tg);
         if (rep) {
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
-            v = scaled4_rep(v, q4, p.scale);
+            v = scaled4_rep(v, q4, a_scale);
         } else {
-            v = scaled4(v, p.scale);
+            v = scaled4(v, a_scale);
         }
         return v;
     };
@@ -397,7 +413,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         for (int s = 0; s < Kt; s++) {
             float4 v = bulk_load ? row.ld(s) : ldrow4(s * kLanes + tg);
             const float4 q4 = __ldcg(reinterpret_cast<const float4*>(prow) + s * kLanes + tg);
-            v = scaled4_rep(v, q4, p.scale);
+            v = scaled4_rep(v, q4, a_scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
             if (SMEM) row.st(s, v);
         }
@@ -405,7 +421,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
 #pragma unroll 8
         for (int s = 0; s < Kt; s++) {
             float4 v = bulk_load ? row.ld(s) : ldrow4(s * kLanes + tg);
-            v = scaled4(v, p.scale);
+            v = scaled4(v, a_scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
             if (SMEM) row.st(s, v);
         }
@@ -414,7 +430,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     float mx = warp_max(tmax);
     // The warp's sel_rank-th largest thread maximum: at least sel_rank elements of this warp are >= it.
     float wsel = INFINITY;
-    const int sel_rank = p.sel_rank;
+    const int sel_rank = a_sel_rank;
     if (sel_rank > 0) {
         int rank = 0;
 #pragma unroll
@@ -486,7 +502,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     #pragma unroll
                     for (int j = 0; j < G; j++) {
                         if (s0 + j < Kt) {
-                            pass2_slot(scaled4_rep(lb[j], qb[j], p.scale));
+                            pass2_slot(scaled4_rep(lb[j], qb[j], a_scale));
                         }
                     }
                 }
@@ -499,7 +515,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
                         if (s0 + j < Kt) lb[j] = ldrow4((s0 + j) * kLanes + tg);
     #pragma unroll
                     for (int j = 0; j < G; j++)
-                        if (s0 + j < Kt) pass2_slot(scaled4(lb[j], p.scale));
+                        if (s0 + j < Kt) pass2_slot(scaled4(lb[j], a_scale));
                 }
             }
         }
@@ -519,7 +535,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         ncand = __reduce_add_sync(FULL, bx(box, 4, lane));
         nstrict = __reduce_add_sync(FULL, bx(box, 5, lane));
         const float cmass = warp_tree_sum(__uint_as_float(bx(box, 6, lane))) / denom;   // any order: a forecast only
-        const bool enough = (use_cnt && nstrict > (uint32_t)p.top_k) || cmass > p.top_p * 1.001f;
+        const bool enough = (use_cnt && nstrict > (uint32_t)a_top_k) || cmass > a_top_p * 1.001f;
         return !cand_ok || enough || last || !(beta_e > 0.f);
     };
     if (!pass2(false)) {
@@ -545,8 +561,8 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
 
     stamp(5);   // second exchange done
     // ---- cutoff search (sampling.cu:593-654, :829-878) ---------------------------------------
-    const uint32_t top_k = (uint32_t)p.top_k;
-    const float top_p = p.top_p;
+    const uint32_t top_k = (uint32_t)a_top_k;
+    const float top_p = a_top_p;
     uint32_t left = 0, right = 0, rounds = 0, n_eval = 0;
     uint32_t path = 1;
     uint32_t conv_cnt = 0, conv_left_cnt = 0;   // counts at `right` / `left` and ordered mass at `right` on return
@@ -796,7 +812,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
             const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
             float o0 = 0.f;
             if (idn < V) {
-                const float x = scaled_logit(ldrow1(idn), rep ? prow[idn] : 0.f, rep, p.scale);
+                const float x = scaled_logit(ldrow1(idn), rep ? prow[idn] : 0.f, rep, a_scale);
                 o0 = exp2f(x - mx) / denom;
             }
             const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
@@ -832,6 +848,13 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         stamp(8);   // element pick done
         if (t == 0) {
             p.out[b] = token;
+            if (ROWP) {
+                if (p.out_prob) {   // the sampled id's probability under the full softmax, as the passes computed it
+                    const float x = scaled_logit(ldrow1(token), rep ? prow[token] : 0.f, rep, a_scale);
+                    p.out_prob[b] = exp2f(x - mx) / denom;
+                }
+                if (p.out_kept) p.out_kept[b] = sum_p;
+            }
             if (p.dbg_trace) {
                 rs_trace tr;
                 tr.maxu = mx; tr.denom = denom; tr.pmin = pmin; tr.pmax = pmax; tr.threshold = thr; tr.comp = comp;
@@ -886,11 +909,44 @@ __global__ void setup_rand_kernel(unsigned char* states, unsigned long long seed
     st[3] = make_uint4(0u, 0u, 0u, 0u);
 }
 
+// Per-row parameters: the host functions' checks and remaps (sampling.cu:458-486, :982-1011) applied to every row
+// on the device.  A temperature outside [0.001, 1000] cannot raise here; the row is sampled at temperature 1 and
+// the status word reports RS_ERR_TEMPERATURE.
+__global__ void row_args_kernel(int B, int V, const float* temperature, const int* top_k, const float* top_p, int rep,
+                                int allow_candidates, RowArgs* out, int* status) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= B) return;
+    float tmp = temperature ? temperature[b] : 1.0f;
+    long long k = top_k ? top_k[b] : -1;
+    float pp = top_p ? top_p[b] : 1.0f;
+    if (!(tmp >= 0.001f && tmp <= 1000.f)) {
+        atomicExch(status, RS_ERR_TEMPERATURE);
+        tmp = 1.0f;
+    }
+    if (k <= 0 || k > V) k = V;
+    if (pp < 0.f || pp > 1.f || pp != pp) pp = 1.f;
+    if (pp == 0.f) { k = 1; pp = 1.f; }
+    RowArgs r;
+    r.kind = rep ? kRepetition : ((tmp == 1.0f && k == V) ? kTopP : kGeneral);
+    r.top_k = (int)k;
+    r.top_p = pp;
+    r.scale = (r.kind == kTopP) ? (float)1.4426950408889634074 : (float)(1.4426950408889634074 / (double)tmp);
+    // rank of the thread maximum that bounds the candidate list: same rule as for per-call parameters
+    int sel = 0;
+    if (allow_candidates && !(k >= V && pp >= 1.0f)) {
+        if (k < V) sel = (k + 2 > 256) ? 0 : (int)((k + 2 + 31) / 32);
+        else sel = 2;
+    }
+    r.sel_rank = sel;
+    r.pad0 = 0; r.pad1 = r.pad2 = 0.f;
+    out[b] = r;
+}
+
 // ------------------------------------------------------------------ host side -------------
 struct DeviceInfo {
     bool ready = false;
     int sms = 0, smem_optin = 0, smem_sm = 0;
-    bool attr_set[10][2] = {};
+    bool attr_set[20][2] = {};
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_mu;
@@ -906,19 +962,19 @@ static int cuda_fail(cudaError_t e, const char* what) {
 
 static int cidx(int C) { return C == 1 ? 0 : C == 2 ? 1 : C == 4 ? 2 : C == 8 ? 3 : 4; }
 
-template <int C, bool SMEM, bool LOWP>
+template <int C, bool SMEM, bool LOWP, bool ROWP = false>
 static int launch_typed(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
-    auto kern = sampler_kernel<C, SMEM, LOWP>;
+    auto kern = sampler_kernel<C, SMEM, LOWP, ROWP>;
     {
         std::lock_guard<std::mutex> lk(g_mu);
-        if (!di.attr_set[cidx(C) + (LOWP ? 5 : 0)][SMEM ? 1 : 0]) {
+        if (!di.attr_set[cidx(C) + (LOWP ? 5 : 0) + (ROWP ? 10 : 0)][SMEM ? 1 : 0]) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, di.smem_optin);
             if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(smem)");
             if (C > 8) {
                 e = cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
                 if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(cluster)");
             }
-            di.attr_set[cidx(C) + (LOWP ? 5 : 0)][SMEM ? 1 : 0] = true;
+            di.attr_set[cidx(C) + (LOWP ? 5 : 0) + (ROWP ? 10 : 0)][SMEM ? 1 : 0] = true;
         }
     }
     cudaLaunchConfig_t cfg;
@@ -944,6 +1000,12 @@ template <int C, bool SMEM>
 static int launch_one(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
     return p.dtype == RS_DTYPE_F32 ? launch_typed<C, SMEM, false>(p, smem, stream, di)
                                    : launch_typed<C, SMEM, true>(p, smem, stream, di);
+}
+// per-row parameters: the widths the planner picks by itself (8 or 16 CTAs on chip, 8 streaming)
+template <int C, bool SMEM>
+static int launch_rows(const Params& p, int smem, cudaStream_t stream, DeviceInfo& di) {
+    return p.dtype == RS_DTYPE_F32 ? launch_typed<C, SMEM, false, true>(p, smem, stream, di)
+                                   : launch_typed<C, SMEM, true, true>(p, smem, stream, di);
 }
 
 static int get_device(DeviceInfo** out) {
@@ -1063,6 +1125,9 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     p.scratch = (float*)((char*)workspace + 256);
     p.dbg_probs = dbg_probs;
     p.dbg_trace = dbg_trace;
+    p.rows = nullptr;
+    p.out_prob = nullptr;
+    p.out_kept = nullptr;
     p.B = (int)B;
     p.V = (int)V;
     p.kind = penalties ? kRepetition : ((temperature == 1 && top_k == V) ? kTopP : kGeneral);
@@ -1086,6 +1151,73 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
         case 16: return launch_one<16, true>(p, smem, st, *di);
     }
     return RS_ERR_LIMIT;
+}
+
+
+// Per-row temperature / top_k / top_p (device arrays of B values; a null array means the neutral value for every
+// row: temperature 1, top_k -1, top_p 1).  Workspace: 256 B status, the rows' normalised parameters, then the
+// scratch rows of the streaming variant.
+static size_t row_args_bytes(long long B) { return ((size_t)B * sizeof(RowArgs) + 255) & ~(size_t)255; }
+
+static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T, int64_t V, float* penalties, void* states,
+                            int32_t* out, const float* temperature, const int32_t* top_k, const float* top_p, double presence,
+                            double repetition, double decay, float* out_prob, float* out_kept, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+    if (!(V > 0 && V <= 1048576 && V % 4 == 0)) return RS_ERR_VOCAB;
+    if (!(B > 0 && T > 0)) return RS_ERR_BATCH;
+    if (B > (1ll << 24)) return RS_ERR_LIMIT;
+    if (dtype != RS_DTYPE_F32 && dtype != RS_DTYPE_F16 && dtype != RS_DTYPE_BF16) return RS_ERR_DTYPE;
+    if (!logits || !states || !out || !workspace) return RS_ERR_POINTER;
+    if (((uintptr_t)logits & (dtype == RS_DTYPE_F32 ? 15 : 7)) || ((uintptr_t)states & 15) || ((uintptr_t)penalties & 15) ||
+        ((uintptr_t)workspace & 255) || ((uintptr_t)temperature & 3) || ((uintptr_t)top_k & 3) || ((uintptr_t)top_p & 3))
+        return RS_ERR_POINTER;
+    DeviceInfo* di = nullptr;
+    int rc = get_device(&di);
+    if (rc) return rc;
+    const size_t rab = row_args_bytes(B);
+    if (workspace_bytes < 256 + rab) return RS_ERR_WORKSPACE;
+    // rows differ in top_k: the candidate buffer takes the widest size
+    const bool allow_cand = g_path_override.load() != 1;
+    const Plan pl = make_plan(*di, B, (int)V, allow_cand ? 8 : 0, allow_cand ? 4 : 0, workspace_bytes - rab);
+    if (workspace_bytes < pl.ws + rab) return RS_ERR_WORKSPACE;
+    if (pl.smem && pl.C != 8 && pl.C != 16) return RS_ERR_LIMIT;   // forced widths exist for the per-call entry only
+
+    cudaStream_t st = (cudaStream_t)stream;
+    RowArgs* rows = (RowArgs*)((char*)workspace + 256);
+    row_args_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((int)B, (int)V, temperature, top_k, top_p, penalties ? 1 : 0,
+                                                               allow_cand ? 1 : 0, rows, (int*)workspace);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "launch(row_args)");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+
+    Params p;
+    p.logits = (const char*)logits + (T - 1) * V * (dtype == RS_DTYPE_F32 ? 4 : 2);
+    p.dtype = dtype;
+    p.row_stride = (long long)T * V;
+    p.penalties = penalties;
+    p.states = (unsigned char*)states;
+    p.out = out;
+    p.status = (int*)workspace;
+    p.scratch = (float*)((char*)workspace + 256 + rab);
+    p.dbg_probs = nullptr;
+    p.dbg_trace = nullptr;
+    p.rows = rows;
+    p.out_prob = out_prob;
+    p.out_kept = out_kept;
+    p.B = (int)B;
+    p.V = (int)V;
+    p.kind = penalties ? kRepetition : kGeneral;   // the kernel takes kind, top_k, top_p, scale and the rank from `rows`
+    p.top_k = (int)V;
+    p.scale = 1.f;
+    p.top_p = 1.f;
+    p.presence = (float)presence;
+    p.repetition = (float)repetition;
+    p.decay = (float)decay;
+    p.sel_rank = 0;
+    p.cand_slots = pl.cand_slots;
+    if (!pl.smem) return launch_rows<8, false>(p, kSlabOff + pl.cand_slots * (kLanes / 8) * 16, st, *di);
+    const int smem = smem_need((int)V, pl.C, pl.cand_slots);
+    return pl.C == 8 ? launch_rows<8, true>(p, smem, st, *di) : launch_rows<16, true>(p, smem, st, *di);
 }
 
 
@@ -1150,6 +1282,9 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     p.scratch = base + 64;
     p.dbg_probs = nullptr;
     p.dbg_trace = nullptr;
+    p.rows = nullptr;
+    p.out_prob = nullptr;
+    p.out_kept = nullptr;
     p.B = (int)B;
     p.V = (int)V;
     p.kind = penalties ? kRepetition : ((temperature == 1 && top_k == V) ? kTopP : kGeneral);
@@ -1243,6 +1378,21 @@ int rs_sample_typed(const void* logits_device, int32_t logits_dtype, int64_t B, 
     return rs::sample_impl(logits_device, logits_dtype, B, T, V, penalties_device, states_device, out_device, temperature,
                            top_k, top_p, presence_penalty, repetition_penalty, penalty_decay, workspace_device,
                            workspace_bytes, stream, probs_device, trace_device);
+}
+
+size_t rs_rows_workspace_bytes(int64_t B, int64_t V) {
+    if (B <= 0) return 256;
+    return rs_workspace_bytes(B, V) + rs::row_args_bytes(B);
+}
+
+int rs_sample_rows(const void* logits_device, int32_t logits_dtype, int64_t B, int64_t T, int64_t V, float* penalties_device,
+                   void* states_device, int32_t* out_device, const float* temperature_device, const int32_t* top_k_device,
+                   const float* top_p_device, double presence_penalty, double repetition_penalty, double penalty_decay,
+                   float* out_prob_device, float* out_kept_mass_device, void* workspace_device, size_t workspace_bytes,
+                   void* stream) {
+    return rs::sample_rows_impl(logits_device, logits_dtype, B, T, V, penalties_device, states_device, out_device,
+                                temperature_device, top_k_device, top_p_device, presence_penalty, repetition_penalty,
+                                penalty_decay, out_prob_device, out_kept_mass_device, workspace_device, workspace_bytes, stream);
 }
 
 int rs_device_status(void* workspace_device, void* stream) {

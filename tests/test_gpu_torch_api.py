@@ -81,3 +81,33 @@ def test_error_conditions_raise_value_error():
     # out-of-range top_k / top_p are remapped, not errors (sampling.cu:1005-1010)
     out = rs.batch_sampling_temperature_topk_topp(ok, st, 1.0, 10 ** 9, 7.0)
     assert out.shape == (2,)
+
+
+def test_call_is_capturable_in_a_cuda_graph():
+    """A decode loop may record the call once and replay it: no allocation, synchronisation or host read-back
+    happens inside the call once its workspace for the stream exists (the reference allocates per call,
+    sampling.cu:488, :498).  Replays advance states and penalties exactly like eager calls."""
+    import rapid_sampling_b200 as rs
+    for B, V, rep in [(8, 32768, True), (160, 32768, False), (2, 262144, False)]:
+        lg = make_logits("normal3", B, V, 21, torch).cuda()
+        st_e, st_g = rs.setup_rand(9, B), rs.setup_rand(9, B)
+        pen_e, pen_g = torch.zeros(B, V, device="cuda"), torch.zeros(B, V, device="cuda")
+
+        def call(st, pen):
+            if rep:
+                return rs.batch_sampling_repetition_temperature_topk_topp(lg, pen, st, 0.1, 0.2, 0.9, 0.8, 40, 0.9)
+            return rs.batch_sampling_temperature_topk_topp(lg, st, 0.8, 40, 0.9)
+        eager = [call(st_e, pen_e).clone() for _ in range(3)]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):      # first call on the capture stream: creates its workspace
+            call(rs.setup_rand(1, B), torch.zeros(B, V, device="cuda"))
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = call(st_g, pen_g)
+        for want in eager:
+            graph.replay()
+            torch.cuda.synchronize()
+            assert torch.equal(out, want)
+        assert torch.equal(st_g, st_e) and torch.equal(pen_g, pen_e)
