@@ -173,8 +173,14 @@ __device__ __forceinline__ void append_candidates(float4 v, float beta_e, float*
     }
 }
 
+// CTAs of one variant that the register file of an SM holds (64K registers): the streaming variant is compiled
+// for 64 registers per thread, the on-chip variants for up to 128.  The launch planner counts resident rows with it.
+__host__ __device__ constexpr int ctas_per_sm_by_registers(int C, bool smem_variant) {
+    return smem_variant ? (C >= 4 ? C / 2 : 1) : (C == 8 ? 8 : 1);
+}
+
 template <int C, bool SMEM, bool LOWP, bool ROWP>
-__global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler_kernel(const Params p) {
+__global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM)) sampler_kernel(const Params p) {
     constexpr int L = kLanes / C;
     constexpr int WPC = L / 32;  // warps per CTA
     constexpr unsigned FULL = 0xffffffffu;
@@ -224,6 +230,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     int* s_idxt = reinterpret_cast<int*>(smem + kMiscOff + 8);
     int* s_token = reinterpret_cast<int*>(smem + kMiscOff + 12);
     float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
+    volatile uint32_t* s_res = reinterpret_cast<volatile uint32_t*>(smem + kMiscOff + 192);   // ten combined words of an exchange
     Row<C, SMEM> row;
     row.slab = SMEM ? reinterpret_cast<float4*>(smem + kSlabOff + p.cand_slots * L * 16)
                     : reinterpret_cast<float4*>(p.scratch + (long long)b * V);
@@ -257,7 +264,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
     // everybody's n+1, which each CTA sends after it has finished reading n.
     int phase = 0;
     uint32_t xpar = 0;
-    auto exchange = [&](auto packets, uint32_t a, uint32_t bq, uint32_t c2) -> const uint32_t* {
+    auto exchange = [&](auto packets, uint32_t a, uint32_t bq, uint32_t c2, const bool wait_here = true) -> const uint32_t* {
         constexpr int NP = decltype(packets)::value;   // 1: words 0-3 (a); 2: + words 4-7 (b); 3: + words 8-9 (c)
         uint32_t* box = reinterpret_cast<uint32_t*>(smem + kMboxOff + phase * kMboxBuf);
         uint32_t wa[4], wb[4] = {0u, 0u, 0u, 0u}, wc[2] = {0u, 0u};
@@ -288,7 +295,7 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
                 if (NP >= 2) st_async_v4(dst + 16, wb[0], wb[1], wb[2], wb[3], rbar);
                 if (NP >= 3) st_async_v2(dst + 32, wc[0], wc[1], rbar);
             }
-            if (!mbar_wait_bounded(bar, (xpar >> phase) & 1u, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
+            if (wait_here && !mbar_wait_bounded(bar, (xpar >> phase) & 1u, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
         }
         xpar ^= (1u << phase);
         phase ^= 1;
@@ -341,20 +348,30 @@ __global__ void __launch_bounds__(kLanes / C, (!SMEM && C == 8) ? 8 : 1) sampler
         mn = __reduce_min_sync(FULL, mn);
         mxv = __reduce_max_sync(FULL, mxv);
         const float cf = __uint2float_rn(pick4(c01 & 0xffffu, c01 >> 16, c23 & 0xffffu, c23 >> 16));
-        const uint32_t* box = exchange(Packets<3>(), __float_as_uint(x), __float_as_uint(cf), xk == 0 ? mn : mxv);
-        vmin = __reduce_min_sync(FULL, bx(box, 8, lane));
-        vmax = __reduce_max_sync(FULL, bx(box, 9, lane));
-        float sacc = 0.f;
-        if (lane < 8) {
-            sacc = __uint_as_float(bx(box, lane, 0));
+        // Only the first warp of a CTA waits for the mailbox and combines it; the others pick the ten results up
+        // from shared memory after a CTA barrier instead of repeating the 32-step chains.
+        const uint32_t* box = exchange(Packets<3>(), __float_as_uint(x), __float_as_uint(cf), xk == 0 ? mn : mxv, wl == 0);
+        if (wl == 0) {
+            const uint32_t bmin = __reduce_min_sync(FULL, bx(box, 8, lane));
+            const uint32_t bmax = __reduce_max_sync(FULL, bx(box, 9, lane));
+            float sacc = 0.f;
+            if (lane < 8) {
+                sacc = __uint_as_float(bx(box, lane, 0));
 #pragma unroll
-            for (int w = 1; w < kWarps; w++) sacc += __uint_as_float(bx(box, lane, w));
+                for (int w = 1; w < kWarps; w++) sacc += __uint_as_float(bx(box, lane, w));
+                s_res[lane] = __float_as_uint(sacc);
+            }
+            if (lane == 8) s_res[8] = bmin;
+            if (lane == 9) s_res[9] = bmax;
         }
+        __syncthreads();
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            mass[i] = __shfl_sync(FULL, sacc, i);
-            cnt[i] = __float2uint_rn(__shfl_sync(FULL, sacc, 4 + i));
+            mass[i] = __uint_as_float(s_res[i]);
+            cnt[i] = __float2uint_rn(__uint_as_float(s_res[4 + i]));
         }
+        vmin = s_res[8];
+        vmax = s_res[9];
     };
 
     // ---- load: bulk async copies of this CTA's stripes; RNG state read meanwhile -------------
@@ -1069,6 +1086,7 @@ static Plan make_plan(const DeviceInfo& di, long long B, int V, int sel_rank, in
         const int need = smem_need(V, C, cand_slots) + 1024;
         int per_sm = di.smem_sm / need;
         per_sm = per_sm < 2048 / (kLanes / C) ? per_sm : 2048 / (kLanes / C);
+        per_sm = per_sm < ctas_per_sm_by_registers(C, true) ? per_sm : ctas_per_sm_by_registers(C, true);
         if (per_sm > 32) per_sm = 32;
         return (long long)di.sms * per_sm / C;
     };
