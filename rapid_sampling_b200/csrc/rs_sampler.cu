@@ -556,10 +556,17 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
         return !cand_ok || enough || last || !(beta_e > 0.f);
     };
     if (!pass2(false)) {
-        beta_e *= 0.0625f;
-        if (!pass2(false)) {
-            beta_e *= 0.0625f;
-            pass2(true);
+        // A flat row: the lowered bound would already admit every element.  Either the whole row fits the
+        // candidate buffer (one more pass with no bound at all), or there is no point in trying.
+        const bool all_in = beta_e * 0.0625f <= emin;
+        if (all_in && V > cap * kLanes) {
+            cand_ok = false;
+        } else {
+            beta_e = all_in ? 0.f : beta_e * 0.0625f;
+            if (!pass2(false)) {
+                beta_e *= 0.0625f;
+                pass2(true);
+            }
         }
     }
     // division is monotone, so the row's min/max probability are the quotients of min/max e
@@ -687,14 +694,50 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
                 if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
             }
         };
-        done = run_search(cand_eval, true, beta_p, use_cnt && nstrict > top_k, nstrict);
-        if (done) {
-            path = 0;
-            const float thr = __uint_as_float(left);
-            for (int i = 0; i < m_own; i++) {
-                const float q = cand_at(i);
-                if (q == thr) eqk++;
-                if (q > thr) { gtk++; gtp += q; }
+        if (ncand <= 4096u) {
+            done = run_search(cand_eval, true, beta_p, use_cnt && nstrict > top_k, nstrict);
+            if (done) {
+                path = 0;
+                const float thr = __uint_as_float(left);
+                for (int i = 0; i < m_own; i++) {
+                    const float q = cand_at(i);
+                    if (q == thr) eqk++;
+                    if (q > thr) { gtk++; gtp += q; }
+                }
+            }
+        } else {
+            // Long lists (flat rows whose lowered bound took in much of the row): the buffer has the slab's
+            // [slot][lane] float4 layout, so it is searched like a slab -- vector loads, and elements below
+            // `left` dropped in place once the bracket has risen above the bound.
+            for (int i = m_own; i < ((m_own + 3) & ~3); i++) cand_at(i) = -1.f;
+            Row<C, true> crow;
+            crow.slab = reinterpret_cast<float4*>(cand);
+            crow.t = t;
+            crow.tg = tg;
+            int n = m_own;
+            uint32_t list_total = ncand, list_left = 0u;
+            auto cand_slab_eval = [&](const float (&f)[4], uint32_t lo, uint32_t, uint32_t cnt_lo, float (&m)[4], uint32_t& c01,
+                                      uint32_t& c23, uint32_t& mn, uint32_t& mxv) {
+                mn = 0u;
+                mxv = 1u;   // bounds are not tracked for long lists
+                const bool compact = (lo != list_left) && (lo > beta_p) && (cnt_lo * 2u <= list_total);
+                if (compact) {
+                    slab_pass<C, true, true>(crow, n, f, __uint_as_float(lo), m, c01, c23);
+                    list_total = cnt_lo;
+                    list_left = lo;
+                } else {
+                    slab_pass<C, true, false>(crow, n, f, 0.f, m, c01, c23);
+                }
+            };
+            done = run_search(cand_slab_eval, true, beta_p, use_cnt && nstrict > top_k, nstrict);
+            if (done) {
+                path = 0;
+                const float thr = __uint_as_float(left);
+                for (int i = 0; i < n; i++) {
+                    const float q = cand_at(i);
+                    if (q == thr) eqk++;
+                    if (q > thr) { gtk++; gtp += q; }
+                }
             }
         }
     }

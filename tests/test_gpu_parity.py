@@ -39,6 +39,9 @@ MATRIX = [
     ("normal3", 8, 32768, 1.0, -1, 0.999999, 17),
     ("peaked", 300, 8192, 0.8, 50, 0.9, 18),       # more rows than fit at once
     ("normal3", 2, 524288, 0.9, 200, 0.95, 19),    # needs the 16-CTA cluster to stay on chip
+    ("uniform", 100, 32768, 1.0, -1, 0.9, 20),     # flat rows, streaming variant: the lowered bound takes in the whole row
+    ("uniform4", 90, 16384, 1.0, -1, 0.1, 21),     # long candidate lists that shrink as the bracket rises
+    ("coarse", 80, 32768, 1.0, -1, 0.7, 22),       # the same with heavy ties
 ]
 
 
@@ -183,6 +186,24 @@ def test_penalties_with_masks_and_existing_values(abi, ref):
         got = abi.sample(lg, s_our, 0.9, 40, 0.95, penalties=pen_our, presence=0.1, repetition=0.1, decay=0.95)
         assert torch.equal(got, want)
     assert torch.equal(pen_our.view(torch.int32), pen_ref.view(torch.int32))
+
+
+def test_long_candidate_lists_are_searched_in_place(abi):
+    """Flat rows in the streaming variant: the lowered bound admits (nearly) the whole row to the candidate buffer, which is
+    then searched like a slab, shrinking as the bracket rises.  Same trace as the whole-row search."""
+    B, V = 100, 32768
+    lg = make_logits("uniform", B, V, 3, torch).cuda()
+    out_a, _, tr = abi.sample(lg, abi.setup_rand(3, B), 1.0, -1, 0.9, debug=True)
+    assert all(t.path == 0 and t.ncand > 4096 for t in tr), [(t.path, t.ncand) for t in tr][:4]
+    try:
+        abi.set_path(1)
+        out_b, _, tr_b = abi.sample(lg, abi.setup_rand(3, B), 1.0, -1, 0.9, debug=True)
+    finally:
+        abi.set_path(0)
+    assert torch.equal(out_a, out_b)
+    for x, y in zip(tr, tr_b):
+        assert y.path == 1 and x.left == y.left and x.rounds == y.rounds and x.idxt == y.idxt
+        assert x.sum_p == y.sum_p and x.comp == y.comp and x.seqk == y.seqk and x.sgtk == y.sgtk
 
 
 @pytest.mark.parametrize("kind,B,V,temp,k,p,seed", [m for m in MATRIX if m[2] <= 262144 and m[1] <= 64])
