@@ -34,7 +34,7 @@ sys.path.insert(0, ROOT)
 L2_BYTES = 126 * 1000 * 1000
 # per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of sampler_kernel from the ncu
 # captures summarised under profiles/, keyed by workload; None where no capture exists.
-NCU_TRAFFIC = {"C2": 1.114e6, "C3": 38.99e6, "C4": 160.8e6}
+NCU_TRAFFIC = {"C2": 1.157e6, "C3": 39.02e6, "C4": 160.66e6}
 
 
 def workload(name):
