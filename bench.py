@@ -172,7 +172,7 @@ def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch,
     from rapid_sampling_b200.sharding import setup_rand_rows
     from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
     B, T, V = w["B"], w["T"], w["V"]
-    s = VocabParallelSampler(B, V, rank, world, T=T)
+    s = VocabParallelSampler(B, V, rank, world, T=T, graph=a.vp_graph)
     pool_n = 2 if V * B * T * 4 // world > 256 * 2 ** 20 else 4
     pool = []
     for i in range(pool_n):   # the same full tensor on every rank (same seed), sliced: shards of one logical row set
@@ -186,7 +186,7 @@ def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch,
     def call(lg):
         return s.sample(lg, states, w["temperature"], w["top_k"], w["top_p"], penalties=pen, presence_penalty=0.1,
                         repetition_penalty=0.1, penalty_decay=0.95)
-    for i in range(Wm):
+    for i in range(max(Wm, 2 * pool_n + 1) if a.vp_graph else Wm):   # a graph per buffer: one eager call, one recording
         call(pool[i % pool_n])
     torch.cuda.synchronize()
     if world > 1:
@@ -216,14 +216,16 @@ def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch,
             pass
         ach = alg / (ms * 1e-3) / 1e9
         line = dict(base, impl="ours", scaling="strong", value=B * K / (total_ms * 1e-3), ms_per_step=ms, median_us=ms * 1e3,
-                    clocks=clk, gpu_launches=K * (6 if s.last_protocol == "fast" else 19), protocol=s.last_protocol,
+                    clocks=clk, gpu_launches=K * (6 if s.last_protocol == "fast" else 19), protocol=s.last_protocol + ("+graph" if a.vp_graph else ""),
                     roofline={"bound": "hbm", "kernel": "vpf_* stage kernels (fast protocol: 3 passes over the shard, 3 collectives)", "achieved": ach,
                               "peak": peak * world, "unit": "GB/s", "frac": ach / (peak * world),
                               "algorithmic_bytes_per_launch": alg, "traffic": None,
                               "note": "latency-bound: collectives and one host check per call"})
         line["config"]["parallelism"] = "vocab-parallel x%d (V/N = %d columns per GPU; NCCL: 2 all-reduces + 1 all-gather per call)" % (world, V // world)
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    s.release_graphs()      # recorded graphs must be gone before NCCL shuts its communicator down
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -312,6 +314,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"], help="storage type of the logits (ours only)")
     ap.add_argument("--vp", action="store_true", help="vocab-parallel: every rank holds V/N columns of every row")
+    ap.add_argument("--vp-graph", action="store_true", help="vocab-parallel: replay the stages from a CUDA graph per input buffer")
     ap.add_argument("--sweep", choices=sorted(SWEEP_GRIDS), help="run the reference-shaped parameter sweep instead (one GPU)")
     ap.add_argument("--sweep-out", default="sweep_results.json")
     a = ap.parse_args()

@@ -200,6 +200,7 @@ class NumpyFastCompute(NumpyCompute):
         B = s.B
         if name == "f_max":
             s.f_stat1.numpy().reshape(B, -1)[:] = self._x().max(axis=1)[:, None]
+            s.f_all_valid.numpy()[0] = 1
         elif name == "f_sum":
             e = self._e()
             st = self._stat2()
@@ -280,16 +281,23 @@ class NumpyFastCompute(NumpyCompute):
                 kept = np.nonzero(wgt > 0)[0]
                 if len(kept) == 0:
                     ids[b], valid[b] = 1, 0
+                    s.f_all_valid.numpy()[0] = 0
                     continue
                 pos = hit[0] if len(hit) else kept[-1]
                 ids[b] = int(ent[pos, 1]) + 1
                 valid[b] = 1 if ok else 0
+                if not ok:
+                    s.f_all_valid.numpy()[0] = 0
                 self._thr = getattr(self, "_thr", dict())
                 self._thr[b] = thr
         elif name == "f_advance":
+            if s.f_all_valid.numpy()[0] == 0:
+                return
             for b in range(B):
                 co.draw4(self.states, b)
         elif name == "penalty" and rnd == 1:
+            if s.f_all_valid.numpy()[0] == 0:
+                return
             keep = s.ids.numpy().copy()
             s.ids.numpy()[:] = s.f_ids.numpy()
             super().stage("penalty")

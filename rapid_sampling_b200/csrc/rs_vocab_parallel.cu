@@ -291,9 +291,10 @@ __global__ void __launch_bounds__(kVpThreads) vp_pick_kernel(const float* logits
 
 // Penalty update of this shard's columns (sampling.cu:427-437): decay everything, add the hit on the sampled id.
 __global__ void vp_penalty_kernel(float* penalties, int n, int B, const int* ids_plus1 /* reduced */, long long col0,
-                                  float presence, float repetition, float decay) {
+                                  float presence, float repetition, float decay, const int* gate) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)B * n) return;
+    if (gate && *gate == 0) return;   // fast protocol: some row could not be settled, the call is repeated as a whole
     const int b = (int)(i / n), c = (int)(i - (long long)b * n);
     const float old = penalties[i];
     const bool hit = (col0 + c) == (long long)(ids_plus1[b] - 1);
@@ -360,9 +361,10 @@ __device__ __forceinline__ float4 vp_x4(const VpRow& r, int g, float scale) {
 }
 
 __global__ void __launch_bounds__(kVpThreads) vpf_max_kernel(const float* logits, long long row_stride, float* penalties, int n,
-                                                             float scale, int S, float* stat1) {
+                                                             float scale, int S, float* stat1, int* all_valid) {
     __shared__ float sh[32];
     const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x, lane = t & 31, w = t >> 5;
+    if (blockIdx.x == 0 && t == 0) *all_valid = 1;   // cleared by the finishing kernel of any row that cannot be settled
     const VpRow r = vp_row(logits, row_stride, penalties, n, b);
     const FSub sb = f_sub(n, S, s);
     float tmax = -INFINITY;
@@ -682,13 +684,14 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
         }
         ids[b] = id + 1;
         valid[b] = ok_row ? 1 : 0;
+        if (!ok_row) atomicAnd(valid + B, 0);
     }
 }
 
 // every rank advances its replica of the RNG states by one block (after a fast-protocol call that was valid)
-__global__ void vpf_advance_kernel(unsigned char* states, int B) {
+__global__ void vpf_advance_kernel(unsigned char* states, int B, const int* gate) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= B) return;
+    if (b >= B || *gate == 0) return;
     uint4* st = reinterpret_cast<uint4*>(states + (long long)b * RS_STATE_BYTES);
     const uint4 nctr = ctr_next(st[0]);
     const uint4 key = st[2];
@@ -711,7 +714,7 @@ static VpfLayout vpf_layout(long long B, int world, int S) {
     l.gath = take((size_t)world * B * lmax * 2);
     l.gath_cnt = take((size_t)world * B);
     l.ids = take(B);
-    l.valid = take(B);
+    l.valid = take(B + 1);   // per-row flags, then one flag for the whole call
     l.total = o;
     return l;
 }
@@ -812,7 +815,8 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
                                                 : (const int*)(ws + l.ids);   // round 1: ids of the fast protocol
                 vp_penalty_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(
                     c->penalties, (int)n, (int)B, idsrc, (long long)c->col0, (float)c->presence_penalty,
-                    (float)c->repetition_penalty, (float)c->penalty_decay);
+                    (float)c->repetition_penalty, (float)c->penalty_decay,
+                    (round == 1) ? (const int*)(ws + l.total + vpf_layout(B, c->world, vpf_subblocks(B, n)).valid) + B : nullptr);
             }
             break;
         case RS_VPF_MAX: case RS_VPF_SUM: case RS_VPF_EXTRACT: case RS_VPF_COMPACT: case RS_VPF_FINISH: case RS_VPF_ADVANCE: {
@@ -822,7 +826,8 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
             float* fw = ws + l.total;
             uint32_t* uw = reinterpret_cast<uint32_t*>(fw);
             if (stage == RS_VPF_MAX)
-                vpf_max_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1);
+                vpf_max_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
+                                                                (int*)(uw + f.valid) + B);
             else if (stage == RS_VPF_SUM)
                 vpf_sum_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
                                                                 fw + f.stat2);
@@ -842,7 +847,8 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
                                                                uw + f.gath_cnt, fk, fp, use_p, (const unsigned char*)c->states,
                                                                (int*)(uw + f.ids), (int*)(uw + f.valid));
             } else
-                vpf_advance_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((unsigned char*)c->states, (int)B);
+                vpf_advance_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((unsigned char*)c->states, (int)B,
+                                                                                (const int*)(uw + f.valid) + B);
             break;
         }
         default:

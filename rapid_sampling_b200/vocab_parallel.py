@@ -54,7 +54,7 @@ class CudaCompute:
 
 
 class VocabParallelSampler:
-    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1, fast=True):
+    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1, fast=True, graph=False):
         if V_global % world or (V_global // world) % 4:
             raise ValueError("V=%d cannot be split into %d shards of a multiple of 4 columns" % (V_global, world))
         self.B, self.T, self.V_global, self.rank, self.world, self.group = B, T, V_global, rank, world, group
@@ -88,7 +88,17 @@ class VocabParallelSampler:
         self.f_gath_cnt = self.ws[f[5]:f[5] + world * B]
         self.f_ids = self.ws[f[6]:f[6] + B].view(torch.int32)
         self.f_valid = self.ws[f[7]:f[7] + B].view(torch.int32)
+        self.f_all_valid = self.ws[f[7] + B:f[7] + B + 1].view(torch.int32)   # cleared if any row could not be settled
+        self.use_graph = graph and fast
+        self._graphs = {}
         self.last_protocol = None
+
+    def release_graphs(self):
+        """Drops the recorded CUDA graphs.  Call it before the process group is destroyed (and before the process
+        exits): NCCL waits for every graph that captured its collectives to be gone before a communicator shuts down."""
+        self._graphs.clear()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
 
     def _reduce(self, t, op):
         if self.world > 1:
@@ -100,8 +110,9 @@ class VocabParallelSampler:
         else:
             out.copy_(inp)
 
-    def _sample_fast(self, penalties):
-        """Three collectives; returns ids, or None when some row's candidate list could not settle its cutoff."""
+    def _fast_stages(self, penalties):
+        """The device side of the fast protocol: five kernels, three collectives, then the state advance and the penalty
+        update, which the device applies only if every row was settled."""
         c = self.compute
         c.stage("f_max")
         self._reduce(self.f_stat1, dist.ReduceOp.MAX)
@@ -112,11 +123,35 @@ class VocabParallelSampler:
         self._gather(self.f_gath, self.f_send)
         self._gather(self.f_gath_cnt, self.f_send_cnt)
         c.stage("f_finish")
-        if int(self.f_valid.min().item()) == 0:      # the one host synchronisation of the fast protocol
-            return None
         c.stage("f_advance")
         if penalties is not None:
             c.stage("penalty", 1)
+
+    def _sample_fast(self, bind_args, penalties):
+        """Returns ids, or None when some row's candidate list could not settle its cutoff.  With `graph=True` the
+        second call with the same buffers and parameters records the stages into a CUDA graph, later ones replay it."""
+        if self.use_graph:
+            key = (bind_args[0].data_ptr(), bind_args[1].data_ptr(), penalties.data_ptr() if penalties is not None else 0) + \
+                tuple(bind_args[3:])
+            g = self._graphs.get(key)
+            if g is None:
+                self.compute.bind(self, *bind_args)
+                self._fast_stages(penalties)            # eager the first time (communicators, kernel attributes)
+                self._graphs[key] = False
+            elif g is False:
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.compute.bind(self, *bind_args)  # picks up the capture stream
+                    self._fast_stages(penalties)
+                self._graphs[key] = g
+                g.replay()
+            else:
+                g.replay()
+        else:
+            self._fast_stages(penalties)
+        if int(self.f_all_valid.item()) == 0:            # the one host synchronisation of the fast protocol
+            return None
         return self.f_ids - 1
 
     def sample(self, logits, states, temperature, top_k, top_p, penalties=None, presence_penalty=0.0,
@@ -126,11 +161,12 @@ class VocabParallelSampler:
         assert logits.shape[-1] == self.V_local and logits.dtype == torch.float32
         assert (logits.shape[1] if logits.dim() == 3 else 1) == self.T
         c = self.compute
-        c.bind(self, logits, states, penalties, float(temperature), int(top_k), float(top_p), float(presence_penalty),
-               float(repetition_penalty), float(penalty_decay))
+        bind_args = (logits, states, penalties, float(temperature), int(top_k), float(top_p), float(presence_penalty),
+                     float(repetition_penalty), float(penalty_decay))
+        c.bind(self, *bind_args)
         self.last_protocol = "staged"
         if self.fast:
-            ids = self._sample_fast(penalties)
+            ids = self._sample_fast(bind_args, penalties)
             if ids is not None:
                 self.last_protocol = "fast"
                 return ids

@@ -35,14 +35,17 @@ def emulated_sample(samplers, shards, states, temp, k, p, pens=None, fast=True):
             s.f_gath.copy_(torch.cat([x.f_send for x in samplers]))
             s.f_gath_cnt.copy_(torch.cat([x.f_send_cnt for x in samplers]))
         fstep("f_finish")
+        before = [st.clone() for st in states]
+        fstep("f_advance")            # applied by the device only if every row was settled
+        if pens is not None:
+            fstep("penalty", rnd=1)
         torch.cuda.synchronize()
-        if all(int(s.f_valid.min()) == 1 for s in samplers):
-            fstep("f_advance")
-            if pens is not None:
-                fstep("penalty", rnd=1)
+        if all(int(s.f_all_valid.item()) == 1 for s in samplers):
+            assert all(int(s.f_valid.min()) == 1 for s in samplers)
             emulated_sample.last = "fast"
             return [s.f_ids - 1 for s in samplers]
-        assert all(int(s.f_valid.min()) == 0 for s in samplers)      # every rank reaches the same verdict
+        assert all(int(s.f_all_valid.item()) == 0 and int(s.f_valid.min()) == 0 for s in samplers)   # same verdict on every rank
+        assert all(torch.equal(a, b) for a, b in zip(before, states))   # nothing was advanced
     emulated_sample.last = "staged"
 
     def step(name, rnd, region, op):
@@ -168,7 +171,12 @@ def _nccl_worker(rank, world, port, q):
     shard = full[:, s.col0:s.col0 + s.V_local].contiguous().cuda()
     st = Abi().setup_rand(9, B)
     out = [s.sample(shard, st, 0.8, 50, 0.9).cpu().numpy() for _ in range(3)]
-    q.put((rank, out))
+    # the same three calls with the stages recorded into a CUDA graph (first call eager, second records, third replays)
+    sg = VocabParallelSampler(B, V, rank, world, graph=True)
+    stg = Abi().setup_rand(9, B)
+    outg = [sg.sample(shard, stg, 0.8, 50, 0.9).cpu().numpy() for _ in range(3)]
+    q.put((rank, (out, outg, sg.last_protocol, bool(torch.equal(st, stg)))))
+    sg.release_graphs()       # before the communicator goes away
     dist.barrier()
     dist.destroy_process_group()
 
@@ -196,4 +204,26 @@ def test_nccl_two_gpus_match_emulation(abi):
     states = [abi.setup_rand(9, B) for _ in range(2)]
     for call in range(3):
         want = emulated_sample(samplers, shards, states, 0.8, 50, 0.9)[0].cpu().numpy()
-        assert np.array_equal(res[0][call], want) and np.array_equal(res[1][call], want)
+        assert np.array_equal(res[0][0][call], want) and np.array_equal(res[1][0][call], want)
+        assert np.array_equal(res[0][1][call], want) and np.array_equal(res[1][1][call], want)   # graph replays
+    assert res[0][2] == res[1][2] == "fast" and res[0][3] and res[1][3]
+
+
+def test_graph_replay_matches_eager_single_rank(abi):
+    """The stages of the fast protocol recorded into a CUDA graph (first call eager, second records, later ones replay):
+    same ids, states and penalties as eager calls, including the device-side gate on the state advance."""
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    B, V = 8, 65536
+    shard = make_logits("peaked", B, V, 4, torch).cuda()
+    eager, graph = VocabParallelSampler(B, V, 0, 1), VocabParallelSampler(B, V, 0, 1, graph=True)
+    st_e, st_g = abi.setup_rand(9, B), abi.setup_rand(9, B)
+    pen_e, pen_g = torch.zeros(B, V, device="cuda"), torch.zeros(B, V, device="cuda")
+    for call in range(4):
+        a = eager.sample(shard, st_e, 0.8, 50, 0.9, penalties=pen_e, presence_penalty=0.1, repetition_penalty=0.2,
+                         penalty_decay=0.5).clone()
+        b = graph.sample(shard, st_g, 0.8, 50, 0.9, penalties=pen_g, presence_penalty=0.1, repetition_penalty=0.2,
+                         penalty_decay=0.5).clone()
+        assert eager.last_protocol == graph.last_protocol == "fast"
+        assert torch.equal(a, b), call
+        assert torch.equal(st_e, st_g) and torch.equal(pen_e, pen_g)
+    graph.release_graphs()
