@@ -5,14 +5,18 @@
 //   * a row is handled by a thread-block CLUSTER of C CTAs (C = 1..16).  The reference's 1024
 //     threads become 1024 "virtual lanes"; CTA c plays lanes [c*1024/C, (c+1)*1024/C).  Lane t
 //     still owns float4 groups t, t+1024, ... so every fp32 sum keeps the reference's order.
-//   * the row is read from HBM ONCE, by 1-D bulk async copies (one per 16 KiB stripe) into the
-//     cluster's shared memory, and all later passes (exp, normalise, search rounds, recount)
-//     run on chip.  The reference re-reads a global scratch copy ~18 times from one SM.
-//   * search rounds drop, in place and order-preserving, every element below the current
-//     lower bound, so later rounds touch only the surviving candidates.
-//   * warp partials cross CTAs through small distributed-shared-memory mailboxes (remote
-//     stores + one cluster barrier per exchange); every CTA combines the 32 partials itself
-//     in the reference's order, so all CTAs take identical decisions without a broadcast.
+//   * on-chip variant (small batches): the row is read from HBM ONCE, by 1-D bulk async copies (one per
+//     stripe) into the cluster's shared memory, and all later passes run on chip.  Streaming variant
+//     (batches beyond what is resident at once): the row is read twice (HBM, then L2) and only a short
+//     candidate list stays on chip.  The reference re-reads a global scratch copy ~18 times from one SM.
+//   * candidate list: a bound derived from the threads' own maxima selects the ~200 largest elements of
+//     the row; the cutoff search replays the reference's pivots on that list and proves for each pivot
+//     that the decision equals the one taken on the whole row.  Rows whose list cannot settle the cutoff
+//     fall back to the search over the whole row, which drops, in place and order-preserving, every element
+//     below the current lower bound as the bracket rises.
+//   * warp partials cross CTAs through small distributed-shared-memory mailboxes (remote vector stores that
+//     count their bytes on an mbarrier of the destination, no cluster barrier); every CTA combines the 32
+//     partials itself in the reference's order, so all CTAs take identical decisions without a broadcast.
 //   * rows too large for the cluster's shared memory use the same code on a global scratch row.
 //
 // No tensor cores: nothing here is a contraction.  The bound is HBM bandwidth (4 bytes per
