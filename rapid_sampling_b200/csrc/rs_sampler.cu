@@ -745,7 +745,13 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             }
         }
     }
-    if (!done) {
+    if (!done && emin == emax) {
+        // Every element has the same probability: the reference's loop never starts (left = pmin, right = left + 1),
+        // the threshold is that probability and the whole row ties with it.  No pass is needed.
+        left = __float_as_uint(pmin);
+        right = left + 1u;
+        eqk = (uint32_t)(Kt * 4);
+    } else if (!done) {
         // ===== whole row: pass 3, p = exp2f(x - max) / denom (sampling.cu:573-590), in place; then the search
         // over every lane's full list, dropping elements below `left` as the bracket rises =====
 #pragma unroll (SMEM ? 2 : 4)
