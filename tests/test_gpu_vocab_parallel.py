@@ -171,7 +171,13 @@ def _nccl_worker(rank, world, port, q):
     shard = full[:, s.col0:s.col0 + s.V_local].contiguous().cuda()
     st = Abi().setup_rand(9, B)
     out = [s.sample(shard, st, 0.8, 50, 0.9).cpu().numpy() for _ in range(3)]
-    q.put((rank, (out, s.last_protocol)))
+    # the same three calls with the stages recorded into a CUDA graph (first call eager, second records, third replays)
+    sg = VocabParallelSampler(B, V, rank, world, graph=True)
+    stg = Abi().setup_rand(9, B)
+    outg = [sg.sample(shard, stg, 0.8, 50, 0.9).cpu().numpy() for _ in range(3)]
+    ok = bool(torch.equal(st, stg)) and sg.last_protocol == "fast"
+    sg.release_graphs()       # NCCL cannot shut the communicator down while a graph that captured its collectives lives
+    q.put((rank, (out, s.last_protocol, outg, ok)))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -200,7 +206,8 @@ def test_nccl_two_gpus_match_emulation(abi):
     for call in range(3):
         want = emulated_sample(samplers, shards, states, 0.8, 50, 0.9)[0].cpu().numpy()
         assert np.array_equal(res[0][0][call], want) and np.array_equal(res[1][0][call], want)
-    assert res[0][1] == res[1][1] == "fast"
+        assert np.array_equal(res[0][2][call], want) and np.array_equal(res[1][2][call], want)   # graph replays
+    assert res[0][1] == res[1][1] == "fast" and res[0][3] and res[1][3]
 
 
 def test_graph_replay_matches_eager_single_rank(abi):
