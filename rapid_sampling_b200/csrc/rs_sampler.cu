@@ -369,13 +369,17 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             if (lane == 9) s_res[9] = bmax;
         }
         __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            mass[i] = __uint_as_float(s_res[i]);
-            cnt[i] = __float2uint_rn(__uint_as_float(s_res[4 + i]));
+        {
+            const uint32_t* rp = const_cast<const uint32_t*>(s_res);   // ordered by the barrier above
+            const uint4 r0 = *reinterpret_cast<const uint4*>(rp), r1 = *reinterpret_cast<const uint4*>(rp + 4);
+            const uint2 r2 = *reinterpret_cast<const uint2*>(rp + 8);
+            mass[0] = __uint_as_float(r0.x); mass[1] = __uint_as_float(r0.y); mass[2] = __uint_as_float(r0.z);
+            mass[3] = __uint_as_float(r0.w);
+            cnt[0] = __float2uint_rn(__uint_as_float(r1.x)); cnt[1] = __float2uint_rn(__uint_as_float(r1.y));
+            cnt[2] = __float2uint_rn(__uint_as_float(r1.z)); cnt[3] = __float2uint_rn(__uint_as_float(r1.w));
+            vmin = r2.x;
+            vmax = r2.y;
         }
-        vmin = s_res[8];
-        vmax = s_res[9];
     };
 
     // ---- load: bulk async copies of this CTA's stripes; RNG state read meanwhile -------------
@@ -652,21 +656,25 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
                     mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
                 }
             }
-            bool ok[3];
+            // the three tests and the bracket update, written with selects: this is the critical path of every round
+            bool ok[3], bad = false;
 #pragma unroll
             for (int i = 0; i < 3; i++) {
-                if (clamp && pv[i] <= beta_p) {
-                    ok[i] = false;
-                    if (!((use_cnt && cnt[i] > top_k) || mass[i] > top_p)) valid = false;
-                } else {
-                    ok[i] = (use_cnt ? cnt[i] < top_k : true) && mass[i] < top_p;
-                }
+                const bool below = clamp && pv[i] <= beta_p;
+                const bool exceeds = (use_cnt && cnt[i] > top_k) || mass[i] > top_p;
+                const bool pass = (!use_cnt || cnt[i] < top_k) && mass[i] < top_p;
+                ok[i] = !below && pass;
+                bad = bad || (below && !exceeds);
             }
-            if (!valid) break;
-            if (ok[0]) { right = py; cnt_r = cnt[0]; mass_r = mass[0]; }
-            else if (ok[1]) { left = py; right = pz; cnt_x = cnt[0]; mass_x = mass[0]; cnt_r = cnt[1]; mass_r = mass[1]; }
-            else if (ok[2]) { left = pz; right = pw; cnt_x = cnt[1]; mass_x = mass[1]; cnt_r = cnt[2]; mass_r = mass[2]; }
-            else { left = pw; cnt_x = cnt[2]; mass_x = mass[2]; }
+            if (bad) { valid = false; break; }
+            const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];   // none: the bracket's upper part
+            const uint32_t nl = s0 ? left : s1 ? py : s2 ? pz : pw;
+            const uint32_t nr = s0 ? py : s1 ? pz : s2 ? pw : right;
+            const uint32_t ncx = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
+            const float nmx = s0 ? mass_x : s1 ? mass[0] : s2 ? mass[1] : mass[2];
+            const uint32_t ncr = s0 ? cnt[0] : s1 ? cnt[1] : s2 ? cnt[2] : cnt_r;
+            const float nmr = s0 ? mass[0] : s1 ? mass[1] : s2 ? mass[2] : mass_r;
+            left = nl; right = nr; cnt_x = ncx; mass_x = nmx; cnt_r = ncr; mass_r = nmr;
         }
         conv_cnt = cnt_r;
         conv_mass = mass_r;
