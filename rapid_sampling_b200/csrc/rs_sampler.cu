@@ -631,10 +631,13 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             float mass[4];
             if (clamp && sure_cnt && pw <= beta_p) {
                 // All three pivots lie at or below the bound, and more than top_k elements are known to lie
-                // strictly above it: every test fails, the loop moves on, no data is needed.
-                cnt[0] = cnt[1] = cnt[2] = n_above;
-                mass[0] = mass[1] = mass[2] = 0.f;
-            } else if (!frozen) {
+                // strictly above it: every test fails, the lower end moves to the last pivot, no data is needed.
+                left = pw;
+                cnt_x = n_above;
+                mass_x = 0.f;
+                continue;
+            }
+            if (!frozen) {
                 n_eval++;
                 const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
                                     __uint_as_float(max(pw, ustar)), __uint_as_float(max(left + 1u, ustar))};
