@@ -838,10 +838,17 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
             else if (stage == RS_VPF_COMPACT)
                 vpf_compact_kernel<<<grid, kVpThreads, 0, st>>>(S, lmax, uw + f.tcnt, uw + f.tent, uw + f.send, uw + f.send_cnt);
             else if (stage == RS_VPF_FINISH) {
-                static bool attr_done = false;
-                if (!attr_done) {
-                    cudaFuncSetAttribute(vpf_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-                    attr_done = true;
+                // the union of the ranks' lists is staged in shared memory: 4 bytes per candidate
+                constexpr size_t kFinishSmem = 160 * 1024;
+                if ((size_t)lmax * c->world * sizeof(float) > kFinishSmem) return RS_ERR_LIMIT;
+                static bool attr_done[64] = {};     // per device
+                int dev = 0;
+                if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RS_ERR_CUDA;
+                if (!attr_done[dev]) {
+                    if (cudaFuncSetAttribute(vpf_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFinishSmem) !=
+                        cudaSuccess)
+                        return RS_ERR_CUDA;
+                    attr_done[dev] = true;
                 }
                 vpf_finish_kernel<<<grid, kVpThreads, (size_t)lmax * c->world * sizeof(float), st>>>((int)B, S, c->world, lmax, fw + f.stat1, fw + f.stat2, uw + f.gath,
                                                                uw + f.gath_cnt, fk, fp, use_p, (const unsigned char*)c->states,
