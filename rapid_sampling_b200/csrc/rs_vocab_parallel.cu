@@ -329,7 +329,7 @@ static VpLayout vp_layout(long long B, int world) {
 // flagged; the driver then repeats the call with the staged protocol above.
 //   vpf_max     per (row, sub-block): max of x                                  -> all-reduce MAX  [B][S]
 //   vpf_sum     per (row, sub-block): denominator partial, octave histogram     -> all-reduce SUM  [B][S][2 + 2*32]
-//               (count and mass per octave; exact in the top 10 octaves, a 1-in-16 sample of groups below)
+//               (count and mass per octave; exact in the top 10 octaves, a 1-in-64 sample of groups below)
 //   vpf_extract per (row, sub-block): per-thread candidate slots (e >= bound)
 //   vpf_compact per row: ordered list of (e, column)                             -> all-gather  [B][Lmax][2] + counts
 //   vpf_finish  per row, on every rank: probabilities staged in shared memory, threshold, weights, pick; validity
@@ -413,12 +413,12 @@ __device__ __forceinline__ float f_bound_e(const float* stat2, int S, int b, flo
 __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits, long long row_stride, float* penalties, int n,
                                                              float scale, int S, const float* stat1, float* stat2) {
     __shared__ float sh[32];
-    __shared__ float hist[2 * kFBins];
-    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x;
+    __shared__ float hist[32][2 * kFBins];     // one histogram per warp: atomics only collide inside a warp
+    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x, w = t >> 5;
     const VpRow r = vp_row(logits, row_stride, penalties, n, b);
     const FSub sb = f_sub(n, S, s);
     const float gmax = f_gmax(stat1, S, b);
-    if (t < 2 * kFBins) hist[t] = 0.f;
+    for (int i = t; i < 32 * 2 * kFBins; i += kVpThreads) (&hist[0][0])[i] = 0.f;
     __syncthreads();
     float acc = 0.f;
     for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
@@ -430,14 +430,14 @@ __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits
             const float e = exp2f(d);
             acc += e;
             // The histogram only steers the choice of the bound (the finishing kernel checks the result exactly), so
-            // below the top ten octaves one group in sixteen stands for its neighbours: few shared-memory atomics.
+            // below the top ten octaves one group in 64 stands for its neighbours: few shared-memory atomics.
             if (d > -(float)kFBins) {
                 const bool top = d > -10.f;
-                if (top || (g & 15) == 0) {
+                if (top || (g & 63) == 0) {
                     int k = (int)(-d);                 // octave: e in (2^-(k+1), 2^-k]
                     if (e < exp2f(-(float)k) * 0.5f) k++;      // guard the octave edge against rounding of exp2f
-                    const float wgt = top ? 1.f : 16.f;
-                    if (k < kFBins) { atomicAdd(&hist[2 * k], e * wgt); atomicAdd(&hist[2 * k + 1], wgt); }
+                    const float wgt = top ? 1.f : 64.f;
+                    if (k < kFBins) { atomicAdd(&hist[w][2 * k], e * wgt); atomicAdd(&hist[w][2 * k + 1], wgt); }
                 }
             }
         }
@@ -446,7 +446,11 @@ __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits
     __syncthreads();
     float* o = stat2 + (size_t)(b * S + s) * kFStat2;
     if (t == 0) { o[0] = d; o[1] = 0.f; }
-    if (t < 2 * kFBins) o[2 + t] = hist[t];
+    if (t < 2 * kFBins) {
+        float a = hist[0][t];
+        for (int k = 1; k < 32; k++) a += hist[k][t];
+        o[2 + t] = a;
+    }
 }
 
 // pass 3: every element with e >= bound goes to its thread's list (order: column order within the thread)
