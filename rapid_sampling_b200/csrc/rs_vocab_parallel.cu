@@ -553,12 +553,43 @@ __device__ __forceinline__ void f_block_sums(float (&v)[NV], float* sh /* [32][N
     for (int i = 0; i < NV; i++) v[i] = sh[32 * NV + i];
 }
 
+// The same for 30 values at once (the 15 pivots of a round): the warp stage is a transposing butterfly -- at offset 16 a
+// lane keeps 16 of the 32 partial sums and hands the other 16 to its partner, at offset 8 it keeps 8, ... -- 31 shuffles
+// instead of 150, after which lane l holds the warp's total of value l.  Fixed order, identical on every rank.
+__device__ __forceinline__ void f_block_sums30(float (&v)[30], float* sh /* [32][32] + [32] */) {
+    const int t = threadIdx.x, lane = t & 31, w = t >> 5;
+    float a[32];
+#pragma unroll
+    for (int i = 0; i < 30; i++) a[i] = v[i];
+    a[30] = a[31] = 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const bool up = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < o; i++) {
+            const float keep = up ? a[i + o] : a[i], give = up ? a[i] : a[i + o];
+            a[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+        }
+    }
+    __syncthreads();
+    sh[w * 32 + lane] = a[0];
+    __syncthreads();
+    if (t < 32) {
+        float x = sh[t];
+        for (int k = 1; k < 32; k++) x += sh[k * 32 + t];
+        sh[32 * 32 + t] = x;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 30; i++) v[i] = sh[32 * 32 + i];
+}
+
 __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, int lmax, const float* stat1, const float* stat2,
                                                                 const uint32_t* gath /* [world][B][Lmax][2] */,
                                                                 const uint32_t* gath_cnt /* [world][B] */, float top_k,
                                                                 float top_p, int use_p, const unsigned char* states,
                                                                 int* ids, int* valid) {
-    __shared__ float sh[32 * 30 + 32];
+    __shared__ float sh[32 * 32 + 32];
     __shared__ float s_scan[32];
     __shared__ int s_hit;
     extern __shared__ float s_pr[];   // the probabilities of the row's candidates, list order (up to 32768)
@@ -620,7 +651,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
             for (int j = 0; j < kVpPivots; j++)
                 if (pb >= piv[j]) { v[2 * j] += 1.f; v[2 * j + 1] += pr; }
         }
-        f_block_sums<30>(v, sh);
+        f_block_sums30(v, sh);
         uint32_t nl = left, nr = right;
         bool found = false;
 #pragma unroll
