@@ -492,11 +492,11 @@ __global__ void __launch_bounds__(kVpThreads) vpf_extract_kernel(const float* lo
 __global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, int lmax, const uint32_t* tcnt, const uint32_t* tent,
                                                                  uint32_t* send /* [B][Lmax][2] */, uint32_t* send_cnt) {
     __shared__ int s_over;
-    __shared__ uint32_t sh[32];
-    __shared__ uint32_t s_base;
+    __shared__ uint32_t sh[2][32];     // warp totals, double-buffered over the sub-blocks
     const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
-    if (t == 0) { s_base = 0; s_over = 0; }
+    if (t == 0) s_over = 0;
     __syncthreads();
+    uint32_t base = 0;                  // entries of the sub-blocks before this one (every thread keeps its own copy)
     for (int s = 0; s < S; s++) {
         const uint32_t raw = tcnt[(size_t)(b * S + s) * kVpThreads + t];
         if (raw > (uint32_t)kFCap) s_over = 1;
@@ -507,28 +507,23 @@ __global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, int lmax
             const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
             if (lane >= o) incl += v;
         }
-        if (lane == 31) sh[w] = incl;
+        if (lane == 31) sh[s & 1][w] = incl;
         __syncthreads();
-        uint32_t pre = s_base;
-        for (int k = 0; k < w; k++) pre += sh[k];
-        const uint32_t off = pre + incl - c;
-        const uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
-        for (uint32_t i = 0; i < c; i++) {
-            if (off + i < (uint32_t)lmax) {
-                send[((size_t)b * lmax + off + i) * 2] = ent[i * 2];
-                send[((size_t)b * lmax + off + i) * 2 + 1] = ent[i * 2 + 1];
-            }
+        uint32_t pre = 0, tot = 0;
+        for (int k = 0; k < 32; k++) {
+            const uint32_t x = sh[s & 1][k];
+            pre += (k < w) ? x : 0u;
+            tot += x;
         }
-        __syncthreads();
-        if (t == 0) {
-            uint32_t tot = s_base;
-            for (int k = 0; k < 32; k++) tot += sh[k];
-            s_base = tot;
-        }
-        __syncthreads();
+        const uint32_t off = base + pre + incl - c;
+        const uint2* ent = reinterpret_cast<const uint2*>(tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2);
+        uint2* dst = reinterpret_cast<uint2*>(send) + (size_t)b * lmax;
+        for (uint32_t i = 0; i < c; i++)
+            if (off + i < (uint32_t)lmax) dst[off + i] = ent[i];
+        base += tot;
     }
     __syncthreads();
-    if (t == 0) send_cnt[b] = s_over ? 0xffffffffu : s_base;   // beyond Lmax / flagged: the finishing kernel rejects the row
+    if (t == 0) send_cnt[b] = s_over ? 0xffffffffu : base;   // beyond Lmax / flagged: the finishing kernel rejects the row
 }
 
 // block-wide fixed-order sums of NV per-thread values at once: warp trees, then threads 0..NV-1 add the 32 warp values
