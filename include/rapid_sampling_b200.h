@@ -150,8 +150,9 @@ int rs_sample_host(const float* logits_host, int64_t B, int64_t T, int64_t V, fl
  *
  * Limits and rules:
  *  - B * V must not exceed RS_STATIC_SCRATCH_FLOATS, otherwise RS_ERR_LIMIT is returned and nothing runs.
- *  - The first call on each device looks up the array's device address (and clears its status word); make
- *    that first call before any stream capture begins.
+ *  - The first call on each device looks up the array's device address (and clears its status word, on the
+ *    call's stream); make that first call before any stream capture begins.  rs_device_status(NULL, stream)
+ *    reads that status word.
  *  - All calls on a device share the one array, which keeps whatever the previous call left in it (the kernel
  *    overwrites what it reads, only the status word relies on the initial clearing).  Two calls that overlap
  *    on the GPU (different streams) race on it: keep calls to this entry point on one stream, or order them.
@@ -207,8 +208,39 @@ int rs_vp_layout(int64_t B, int32_t world, int64_t offsets_floats[6]);
 int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets_floats[11]);
 int rs_vp_stage(const rs_vp_call* call, int32_t stage, int32_t round);
 
-/* Reads the device status word of `workspace_device` (synchronises `stream`): RS_OK or RS_ERR_TIMEOUT. */
+/*
+ * Device status word.  The kernels never trap: a condition they cannot report through a return code is written to
+ * the first int32 of the workspace, which stays set until it is cleared.  Values: RS_OK; RS_ERR_TIMEOUT (a bounded
+ * on-chip wait gave up: the rows of the CTAs that saw it report id -1 and leave their RNG state and penalties
+ * untouched; other rows of the call are unaffected); RS_ERR_TEMPERATURE (rs_sample_rows: some row's temperature
+ * lay outside [0.001, 1000] and was sampled at 1).  No reference counterpart: the reference checks nothing after
+ * a launch (sampling.cu:500-515).
+ *
+ * rs_device_status reads the word (synchronises `stream`); rs_clear_status zeroes it on `stream`.  For both,
+ * workspace_device == NULL names the status word of rs_sample_static_scratch's built-in array on the current device.
+ */
 int rs_device_status(void* workspace_device, void* stream);
+int rs_clear_status(void* workspace_device, void* stream);
+
+/*
+ * Optional host mirror of the status word for the current device: `host_word` must be a 4-byte word of pinned,
+ * device-accessible host memory (cudaHostAlloc / cudaHostRegister; NULL removes the mirror).  Kernels launched
+ * afterwards store a non-zero status there as well, so a host can notice a failure by reading its own memory,
+ * without a copy or a synchronisation.  The caller owns the word and clears it.
+ */
+int rs_set_status_mirror(int* host_word);
+
+/* Poll limit of the kernels' bounded waits (each poll blocks for a short hardware-defined time).  0 only queries.
+ * Returns the previous limit.  The default (about four million polls) is far beyond any legitimate wait. */
+uint32_t rs_set_wait_polls(uint32_t polls);
+
+/*
+ * Test instrumentation for the failure path, no reference counterpart: launches one CTA that waits with the given
+ * poll limit (1..4096) on a barrier nothing will ever complete -- no copy or remote store is in flight -- and
+ * reports the expiry as the sampler does: RS_ERR_TIMEOUT in the status word of `workspace_device` (and the
+ * mirror).  The GPU context stays usable.
+ */
+int rs_selftest_bounded_wait(void* workspace_device, uint32_t polls, void* stream);
 
 /* Forces the thread-block-cluster width (1, 2, 4, 8 or 16) used per row; 0 restores the automatic
  * choice.  Benchmarking aid; returns the previous value. */

@@ -71,6 +71,18 @@ def kernel_launch_count():
     return _load_ext().kernel_launch_count()
 
 
+def device_status():
+    """Synchronises the current stream and returns the device status word of this device (0 = ok, else a negative
+    RS_ERR_* code such as "a bounded on-chip wait gave up"), clearing it.  Sampling calls check a host mirror of the
+    word by themselves and raise on the NEXT call; this is the explicit, synchronising form."""
+    return _load_ext().device_status()
+
+
+def release_workspaces():
+    """Drops the per-(device, stream) scratch buffers the sampling calls keep between calls."""
+    return _load_ext().release_workspaces()
+
+
 __all__ = ["setup_rand", "batch_sampling_temperature_topk_topp", "batch_sampling_repetition_temperature_topk_topp",
            "batch_sampling_temperature_topk_topp_any", "batch_sampling_repetition_temperature_topk_topp_any", "batch_sampling_rows",
-           "kernel_launch_count"]
+           "kernel_launch_count", "device_status", "release_workspaces"]

@@ -47,6 +47,8 @@ struct Params {
     float* dbg_probs;        // optional (B,V)
     rs_trace* dbg_trace;     // optional B
     int* status;             // device status word
+    int* status_mirror;      // optional: a word of pinned host memory the device can write (zero-copy), or null
+    uint32_t wait_polls;     // polls after which a bounded wait gives up
     int B, V, kind, top_k;
     int sel_rank;            // 0 = no candidate shortcut; else rank of the per-warp thread maximum used as bound
     int cand_slots;          // float4 slots per lane of the candidate buffer (shared-memory variant)
@@ -70,7 +72,7 @@ constexpr int kMboxOff = 0;                      // 2 buffers of [32 warps][kXSt
 constexpr int kMboxBuf = kXStride * 32 * 4;
 constexpr int kMiscOff = 2 * kMboxBuf;           // mbarriers, small scalars, 32 warp totals
 constexpr int kSlabOff = kMiscOff + 256;
-constexpr uint32_t kWaitPolls = 1u << 22;
+constexpr uint32_t kDefaultWaitPolls = 1u << 22;
 
 __host__ __device__ constexpr int slab_bytes(int V, int C) { return ((V / 4 + 1023) / 1024) * (1024 / C) * 16; }
 
@@ -235,6 +237,14 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     int* s_token = reinterpret_cast<int*>(smem + kMiscOff + 12);
     float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
     volatile uint32_t* s_res = reinterpret_cast<volatile uint32_t*>(smem + kMiscOff + 192);   // ten combined words of an exchange
+    volatile int* s_fail = reinterpret_cast<volatile int*>(smem + kMiscOff + 32);             // set when a bounded wait of this CTA gave up
+    // A wait that ran out: the status word (and its host mirror) say so, and this CTA stops producing results --
+    // its row reports id -1 and leaves the RNG state and the penalties as they were.
+    auto wait_failed = [&]() {
+        atomicExch(p.status, RS_ERR_TIMEOUT);
+        if (p.status_mirror) *reinterpret_cast<volatile int*>(p.status_mirror) = RS_ERR_TIMEOUT;
+        *s_fail = 1;
+    };
     Row<C, SMEM> row;
     row.slab = SMEM ? reinterpret_cast<float4*>(smem + kSlabOff + p.cand_slots * L * 16)
                     : reinterpret_cast<float4*>(p.scratch + (long long)b * V);
@@ -299,7 +309,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
                 if (NP >= 2) st_async_v4(dst + 16, wb[0], wb[1], wb[2], wb[3], rbar);
                 if (NP >= 3) st_async_v2(dst + 32, wc[0], wc[1], rbar);
             }
-            if (wait_here && !mbar_wait_bounded(bar, (xpar >> phase) & 1u, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
+            if (wait_here && !mbar_wait_bounded(bar, (xpar >> phase) & 1u, p.wait_polls)) wait_failed();
         }
         xpar ^= (1u << phase);
         phase ^= 1;
@@ -391,6 +401,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             fence_mbar_init();
             *s_idxt = 0;
             *s_token = 0;
+            *s_fail = 0;
         }
         __syncthreads();
         if (wl == 0 && bulk_load) {
@@ -411,6 +422,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             fence_mbar_init();
             *s_idxt = 0;
             *s_token = 0;
+            *s_fail = 0;
         }
         __syncthreads();
     }
@@ -426,7 +438,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     const float ux = u01(r0), uy = u01(r1);
 
     if (bulk_load) {
-        if (!mbar_wait_bounded(smem_addr(mbar), 0, kWaitPolls)) atomicExch(p.status, RS_ERR_TIMEOUT);
+        if (!mbar_wait_bounded(smem_addr(mbar), 0, p.wait_polls)) wait_failed();
     }
 
     stamp(1);   // row resident
@@ -873,7 +885,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     const bool is_owner = ((int)crank == owner_cta);
     if (u != u_prev) *s_idxt = tg;
 
-    if (crank == 0 && t == 0) {  // advance the stored RNG state by one 4-word block
+    if (crank == 0 && t == 0 && *s_fail == 0) {  // advance the stored RNG state by one 4-word block
         const uint4 nctr = ctr_next(rng.ctr);
         uint4* st = reinterpret_cast<uint4*>(p.states + (long long)b * RS_STATE_BYTES);
         st[0] = nctr;
@@ -925,14 +937,18 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             if (uo != uo_prev) *s_token = (idn_of[it] < V) ? idn_of[it] : 0;
         }
         __syncthreads();
-        token = *s_token;
+        token = (*s_fail == 0) ? *s_token : -1;
         stamp(8);   // element pick done
         if (t == 0) {
             p.out[b] = token;
             if (ROWP) {
                 if (p.out_prob) {   // the sampled id's probability under the full softmax, as the passes computed it
-                    const float x = scaled_logit(ldrow1(token), rep ? prow[token] : 0.f, rep, a_scale);
-                    p.out_prob[b] = exp2f(x - mx) / denom;
+                    float pr = 0.f;
+                    if (token >= 0) {
+                        const float x = scaled_logit(ldrow1(token), rep ? prow[token] : 0.f, rep, a_scale);
+                        pr = exp2f(x - mx) / denom;
+                    }
+                    p.out_prob[b] = pr;
                 }
                 if (p.out_kept) p.out_kept[b] = sum_p;
             }
@@ -952,11 +968,13 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
                 p.dbg_trace[b] = tr;
             }
         }
+        // out_prob reads the sampled id's OLD penalty: every thread of this CTA stays out of the update until it is read
+        if (ROWP && rep && p.out_prob) __syncthreads();
     }
 
     // ---- penalties: decay everything, add the hit on the sampled id (sampling.cu:427-437).
     // The sampled id lies in the owner CTA's own stripes, so no cross-CTA hand-off is needed. ---
-    if (rep) {
+    if (rep && *s_fail == 0) {
 #pragma unroll 4
         for (int s = 0; s < Kt; s++) {
             const int i4 = s * kLanes + tg;
@@ -990,11 +1008,27 @@ __global__ void setup_rand_kernel(unsigned char* states, unsigned long long seed
     st[3] = make_uint4(0u, 0u, 0u, 0u);
 }
 
+// Test instrumentation for the failure path: one CTA waits, with the given poll limit, on an mbarrier that nothing
+// will ever complete, and reports the expiry exactly as the sampler does.  No copy or remote store is in flight,
+// so nothing can land in the shared memory of the CTA after it has returned.
+__global__ void selftest_wait_kernel(int* status, int* status_mirror, uint32_t polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_addr(&bar), 1);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait_bounded(smem_addr(&bar), 0, polls)) {
+        atomicExch(status, RS_ERR_TIMEOUT);
+        if (status_mirror) *reinterpret_cast<volatile int*>(status_mirror) = RS_ERR_TIMEOUT;
+    }
+}
+
 // Per-row parameters: the host functions' checks and remaps (sampling.cu:458-486, :982-1011) applied to every row
 // on the device.  A temperature outside [0.001, 1000] cannot raise here; the row is sampled at temperature 1 and
 // the status word reports RS_ERR_TEMPERATURE.
 __global__ void row_args_kernel(int B, int V, const float* temperature, const int* top_k, const float* top_p, int rep,
-                                int allow_candidates, RowArgs* out, int* status) {
+                                int allow_candidates, RowArgs* out, int* status, int* status_mirror) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= B) return;
     float tmp = temperature ? temperature[b] : 1.0f;
@@ -1002,6 +1036,7 @@ __global__ void row_args_kernel(int B, int V, const float* temperature, const in
     float pp = top_p ? top_p[b] : 1.0f;
     if (!(tmp >= 0.001f && tmp <= 1000.f)) {
         atomicExch(status, RS_ERR_TEMPERATURE);
+        if (status_mirror) *reinterpret_cast<volatile int*>(status_mirror) = RS_ERR_TEMPERATURE;
         tmp = 1.0f;
     }
     if (k <= 0 || k > V) k = V;
@@ -1028,12 +1063,14 @@ struct DeviceInfo {
     bool ready = false;
     int sms = 0, smem_optin = 0, smem_sm = 0;
     bool attr_set[20][2] = {};
+    int* mirror = nullptr;   // host word the kernels copy a non-zero status to (rs_set_status_mirror)
 };
 static DeviceInfo g_dev[64];
 static std::mutex g_mu;
 static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_cluster_override{0};
 static std::atomic<int> g_path_override{0};
+static std::atomic<uint32_t> g_wait_polls{kDefaultWaitPolls};
 static thread_local char g_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -1204,6 +1241,8 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     p.states = (unsigned char*)states;
     p.out = out;
     p.status = (int*)workspace;
+    p.status_mirror = di->mirror;
+    p.wait_polls = g_wait_polls.load();
     p.scratch = (float*)((char*)workspace + 256);
     p.dbg_probs = dbg_probs;
     p.dbg_trace = dbg_trace;
@@ -1267,7 +1306,7 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     cudaStream_t st = (cudaStream_t)stream;
     RowArgs* rows = (RowArgs*)((char*)workspace + 256);
     row_args_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((int)B, (int)V, temperature, top_k, top_p, penalties ? 1 : 0,
-                                                               allow_cand ? 1 : 0, rows, (int*)workspace);
+                                                               allow_cand ? 1 : 0, rows, (int*)workspace, di->mirror);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e, "launch(row_args)");
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -1280,6 +1319,8 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     p.states = (unsigned char*)states;
     p.out = out;
     p.status = (int*)workspace;
+    p.status_mirror = di->mirror;
+    p.wait_polls = g_wait_polls.load();
     p.scratch = (float*)((char*)workspace + 256 + rab);
     p.dbg_probs = nullptr;
     p.dbg_trace = nullptr;
@@ -1317,15 +1358,17 @@ static float* g_static_ptr[64] = {};   // device address of the array, per devic
 
 // Set-up, once per device, with that device current.  In host code the array's NAME is only a
 // host-side handle; the device address has to be asked for.
-static int static_scratch_address(int dev, float** out) {
+static int static_scratch_address(int dev, cudaStream_t stream, float** out) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!g_static_ptr[dev]) {
         float* ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
         if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
         if (!ptr) return RS_ERR_POINTER;
-        e = cudaMemset(ptr, 0, 256);   // the status word starts clear; the rows need no clearing (written before read)
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMemset(static status word)");
+        // the status word starts clear (on the caller's stream, ahead of the first launch); the rows need no
+        // clearing: the kernel writes them before it reads them
+        e = cudaMemsetAsync(ptr, 0, 256, stream);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMemsetAsync(static status word)");
         g_static_ptr[dev] = ptr;
     }
     *out = g_static_ptr[dev];
@@ -1338,7 +1381,7 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     if (!(V > 0 && V <= 1048576 && V % 4 == 0)) return RS_ERR_VOCAB;
     if (!(B > 0 && T > 0)) return RS_ERR_BATCH;
     if (!(temperature >= 0.001 && temperature <= 1000)) return RS_ERR_TEMPERATURE;
-    if (B * V > (int64_t)RS_STATIC_SCRATCH_FLOATS) return RS_ERR_LIMIT;
+    if (B > (int64_t)RS_STATIC_SCRATCH_FLOATS / V) return RS_ERR_LIMIT;   // B * V cannot wrap this way
     if (!logits || !states || !out) return RS_ERR_POINTER;
     if (((uintptr_t)logits & 15) || ((uintptr_t)states & 15) || ((uintptr_t)penalties & 15)) return RS_ERR_POINTER;
     if (top_k <= 0 || top_k > V) top_k = V;
@@ -1351,7 +1394,7 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
     float* base = nullptr;
-    rc = static_scratch_address(dev, &base);
+    rc = static_scratch_address(dev, (cudaStream_t)stream, &base);
     if (rc) return rc;
     Params p;
     p.logits = logits + (T - 1) * V;
@@ -1361,6 +1404,8 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     p.states = (unsigned char*)states;
     p.out = out;
     p.status = (int*)base;
+    p.status_mirror = di->mirror;
+    p.wait_polls = g_wait_polls.load();
     p.scratch = base + 64;
     p.dbg_probs = nullptr;
     p.dbg_trace = nullptr;
@@ -1479,10 +1524,63 @@ int rs_sample_rows(const void* logits_device, int32_t logits_dtype, int64_t B, i
 
 int rs_device_status(void* workspace_device, void* stream) {
     int v = 0;
+    if (!workspace_device) {   // the status word of rs_sample_static_scratch's built-in array on the current device
+        int dev = 0;
+        cudaError_t e0 = cudaGetDevice(&dev);
+        if (e0 != cudaSuccess) return rs::cuda_fail(e0, "cudaGetDevice");
+        if (dev < 0 || dev >= 64) return RS_ERR_LIMIT;
+        float* base = nullptr;
+        const int rc = rs::static_scratch_address(dev, (cudaStream_t)stream, &base);
+        if (rc) return rc;
+        workspace_device = base;
+    }
     cudaError_t e = cudaMemcpyAsync(&v, workspace_device, sizeof v, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
     if (e != cudaSuccess) return rs::cuda_fail(e, "status read");
     return v;
+}
+
+int rs_clear_status(void* workspace_device, void* stream) {
+    if (!workspace_device) {
+        int dev = 0;
+        cudaError_t e0 = cudaGetDevice(&dev);
+        if (e0 != cudaSuccess) return rs::cuda_fail(e0, "cudaGetDevice");
+        if (dev < 0 || dev >= 64) return RS_ERR_LIMIT;
+        float* base = nullptr;
+        const int rc = rs::static_scratch_address(dev, (cudaStream_t)stream, &base);
+        if (rc) return rc;
+        workspace_device = base;
+    }
+    cudaError_t e = cudaMemsetAsync(workspace_device, 0, sizeof(int), (cudaStream_t)stream);
+    if (e != cudaSuccess) return rs::cuda_fail(e, "status clear");
+    return RS_OK;
+}
+
+int rs_set_status_mirror(int* host_word) {
+    rs::DeviceInfo* di = nullptr;
+    const int rc = rs::get_device(&di);
+    if (rc) return rc;
+    if ((uintptr_t)host_word & 3) return RS_ERR_POINTER;
+    std::lock_guard<std::mutex> lk(rs::g_mu);
+    di->mirror = host_word;
+    return RS_OK;
+}
+
+uint32_t rs_set_wait_polls(uint32_t polls) {
+    return polls ? rs::g_wait_polls.exchange(polls) : rs::g_wait_polls.load();
+}
+
+int rs_selftest_bounded_wait(void* workspace_device, uint32_t polls, void* stream) {
+    if (!workspace_device || ((uintptr_t)workspace_device & 3)) return RS_ERR_POINTER;
+    if (polls == 0 || polls > 4096) return RS_ERR_LIMIT;   // a self-test, not a delay loop
+    rs::DeviceInfo* di = nullptr;
+    const int rc = rs::get_device(&di);
+    if (rc) return rc;
+    rs::selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((int*)workspace_device, di->mirror, polls);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return rs::cuda_fail(e, "launch(selftest)");
+    rs::g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RS_OK;
 }
 
 int rs_set_cluster_override(int cluster_ctas) {

@@ -20,15 +20,47 @@ namespace {
     throw std::invalid_argument(msg);  // pybind11 maps this to ValueError, as in the reference
 }
 
-// One zero-initialised workspace per (device, stream); grows, never shrinks.
-at::Tensor& workspace_for(int device, cudaStream_t stream, size_t bytes) {
-    static std::mutex mu;
-    static std::map<std::pair<int, cudaStream_t>, at::Tensor> cache;
-    std::lock_guard<std::mutex> lk(mu);
-    at::Tensor& w = cache[{device, stream}];
+// One zero-initialised workspace per (device, stream); grows, never shrinks, and is kept for the life of the
+// process (release_workspaces() drops them).  Returned by value: the reference count is taken under the lock, so a
+// concurrent call that grows the same entry cannot free the buffer under a caller that still uses it.  Growing
+// allocates: the first call with a given shape must come before any stream capture.
+std::mutex g_ws_mu;
+std::map<std::pair<int, cudaStream_t>, at::Tensor> g_ws_cache;
+at::Tensor workspace_for(int device, cudaStream_t stream, size_t bytes) {
+    std::lock_guard<std::mutex> lk(g_ws_mu);
+    at::Tensor& w = g_ws_cache[{device, stream}];
     if (!w.defined() || (size_t)w.numel() < bytes)
         w = at::zeros({(int64_t)bytes}, at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
     return w;
+}
+
+// Host mirror of the device status word, one pinned int per device: the kernels store a non-zero status there as
+// well, so a failure (a bounded wait that gave up, a per-row temperature out of range) is noticed by the NEXT call
+// on that device from host memory alone -- no copy, no synchronisation on the hot path.
+struct Mirror {
+    at::Tensor word;   // pinned int32[1]
+};
+std::mutex g_mirror_mu;
+std::map<int, Mirror> g_mirror;
+volatile int* mirror_for(int device) {
+    std::lock_guard<std::mutex> lk(g_mirror_mu);
+    Mirror& m = g_mirror[device];
+    if (!m.word.defined()) {
+        m.word = at::zeros({1}, at::TensorOptions().dtype(at::kInt)).pin_memory();
+        if (rs_set_status_mirror(m.word.data_ptr<int>()) != RS_OK) throw std::runtime_error("rs_set_status_mirror failed !\n");
+    }
+    return m.word.data_ptr<int>();
+}
+// Raises what an earlier call on this device left in the mirror, once.
+void raise_pending_status(int device, at::Tensor& ws, cudaStream_t stream) {
+    volatile int* w = mirror_for(device);
+    const int v = *w;
+    if (v == 0) return;
+    *w = 0;
+    rs_clear_status(ws.data_ptr(), stream);
+    std::string msg = "an earlier sampling call on cuda:" + std::to_string(device) + " reported: " + rs_status_string(v) + " !\n";
+    if (v == RS_ERR_TEMPERATURE) throw std::invalid_argument(msg);
+    throw std::runtime_error(msg);
 }
 
 struct Shapes {
@@ -79,7 +111,8 @@ at::Tensor sample_common(at::Tensor& logits, at::Tensor* penalties, at::Tensor& 
     const int dev = logits.get_device();
     cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
     const size_t wsb = rs_workspace_bytes(B, V);
-    at::Tensor& ws = workspace_for(dev, stream, wsb);
+    at::Tensor ws = workspace_for(dev, stream, wsb);
+    raise_pending_status(dev, ws, stream);
     at::Tensor out = at::empty({B > 0 ? B : 0}, at::TensorOptions().dtype(at::kInt).device(logits.device()));
     const int dt = sh.dtype;
     const int rc = rs_sample_typed(logits.data_ptr(), dt, B, T, V, pen, states.data_ptr(), out.data_ptr<int32_t>(), temperature,
@@ -118,7 +151,8 @@ pybind11::object batch_sampling_rows(at::Tensor& logits, at::Tensor& states, c10
     c10::cuda::CUDAGuard guard(logits.device());
     const int dev = logits.get_device();
     cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
-    at::Tensor& ws = workspace_for(dev, stream, rs_rows_workspace_bytes(sh.B, sh.V));
+    at::Tensor ws = workspace_for(dev, stream, rs_rows_workspace_bytes(sh.B, sh.V));
+    raise_pending_status(dev, ws, stream);
     const int64_t n = sh.B > 0 ? sh.B : 0;
     at::Tensor out = at::empty({n}, at::TensorOptions().dtype(at::kInt).device(logits.device()));
     at::Tensor prob, kept;
@@ -188,5 +222,30 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("presence_penalty") = 0.0, py::arg("repetition_penalty") = 0.0, py::arg("penalty_decay") = 0.0,
           py::arg("return_prob") = false);
     m.def("kernel_launch_count", []() { return rs_kernel_launch_count(); });
+    m.def("device_status", []() {
+        // Synchronises the current stream and returns the status word of its workspace (0 = ok), clearing word and mirror.
+        const int dev = c10::cuda::current_device();
+        cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
+        at::Tensor ws = workspace_for(dev, stream, 256);
+        int v = rs_device_status(ws.data_ptr(), stream);
+        if (v != 0) rs_clear_status(ws.data_ptr(), stream);
+        volatile int* w = mirror_for(dev);
+        if (v == 0) v = *w;     // a status raised through another workspace of this device
+        *w = 0;
+        return v;
+    });
+    m.def("selftest_bounded_wait", [](int64_t polls) {
+        // Failure-path instrumentation: one CTA waits on a barrier nothing completes; the next sampling call raises.
+        const int dev = c10::cuda::current_device();
+        cudaStream_t stream = at::cuda::getCurrentCUDAStream(dev).stream();
+        at::Tensor ws = workspace_for(dev, stream, 256);
+        mirror_for(dev);
+        const int rc = rs_selftest_bounded_wait(ws.data_ptr(), (uint32_t)polls, stream);
+        if (rc != RS_OK) fail(rc, "");
+    }, py::arg("polls") = 4);
+    m.def("release_workspaces", []() {
+        std::lock_guard<std::mutex> lk(g_ws_mu);
+        g_ws_cache.clear();
+    });
     m.def("version", []() { return std::string(rs_version()); });
 }

@@ -793,8 +793,14 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
     const int64_t B = c->B, T = c->T, n = c->V_local, V = c->V_global;
     if (!(V > 0 && V <= 1048576 && V % 4 == 0) || !(n > 0 && n <= V)) return RS_ERR_VOCAB;
     if (!(B > 0 && T > 0) || c->world <= 0 || c->rank < 0 || c->rank >= c->world) return RS_ERR_BATCH;
+    // The shard kernels read float4 groups at row_base + g: every row of the shard must start on a 16-byte boundary,
+    // and the shards must tile the vocabulary in rank order (the finishing kernel reports GLOBAL column ids).
+    if (n % 4 != 0 || n * (int64_t)c->world != V || c->col0 != (int64_t)c->rank * n) return RS_ERR_VOCAB;
     if (!(c->temperature >= 0.001 && c->temperature <= 1000)) return RS_ERR_TEMPERATURE;
     if (!c->logits || !c->states || !c->workspace) return RS_ERR_POINTER;
+    if (((uintptr_t)c->logits & 15) || ((uintptr_t)c->penalties & 15) || ((uintptr_t)c->workspace & 15) ||
+        ((uintptr_t)c->states & 15))
+        return RS_ERR_POINTER;
     int64_t top_k = c->top_k;
     double top_p = c->top_p;
     if (top_k <= 0 || top_k > V) top_k = V;          // remaps of sampling.cu:1005-1010, on the GLOBAL vocabulary
@@ -827,7 +833,7 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
                                                          ws + l.tallies, (int)B, RS_VP_ROUNDS, fk, fp, ws + l.gtally);
             break;
         case RS_VP_WEIGHT:
-            cudaMemsetAsync(ws + l.weights, 0, (size_t)B * c->world * sizeof(float), st);
+            if (cudaMemsetAsync(ws + l.weights, 0, (size_t)B * c->world * sizeof(float), st) != cudaSuccess) return RS_ERR_CUDA;
             vp_weight_kernel<<<grid, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, ws + l.gmax, ws + l.gsum,
                                                           ws + l.tallies, (int)B, RS_VP_ROUNDS, fk, fp, use_p, ws + l.gtally,
                                                           c->rank, c->world, ws + l.weights);

@@ -60,3 +60,31 @@ def test_python_package_exports_reference_names():
     for arg in ("logits", "penalties", "states", "presence_penalty", "repetition_penalty", "penalty_decay",
                 "temperature", "top_k", "top_p"):
         assert arg in doc
+
+
+def test_vocab_parallel_stage_refuses_bad_shards_without_a_gpu():
+    """rs_vp_stage reads float4 groups at row_base + g, so a shard must be a multiple of 4 columns wide, 16-byte
+    aligned, and the shards must tile the vocabulary in rank order; anything else is an error code, not a launch."""
+    from rapid_sampling_b200 import abi
+    L = abi.load()
+
+    def call(**kw):
+        c = abi.VpCall()
+        c.logits = c.states = c.workspace = 4096
+        c.penalties = None
+        c.B, c.T, c.V_local, c.V_global, c.col0 = 2, 1, 8192, 32768, 8192
+        c.top_k, c.temperature, c.top_p = 50, 0.8, 0.9
+        c.rank, c.world = 1, 4
+        for k, v in kw.items():
+            setattr(c, k, v)
+        return L.rs_vp_stage(C.byref(c), abi.VPF_MAX, 0)
+    assert call(V_local=8190, V_global=32760) == abi.RS_ERR_VOCAB            # not a multiple of 4 columns
+    assert call(V_local=4096) == abi.RS_ERR_VOCAB                            # shards do not tile the vocabulary
+    assert call(col0=0) == abi.RS_ERR_VOCAB                                  # not this rank's columns
+    assert call(logits=4100) == abi.RS_ERR_POINTER
+    assert call(penalties=4104) == abi.RS_ERR_POINTER
+    assert call(workspace=4098) == abi.RS_ERR_POINTER
+    assert call(rank=4) == abi.RS_ERR_BATCH
+    assert call(temperature=0.0) == abi.RS_ERR_TEMPERATURE
+    assert L.rs_selftest_bounded_wait(None, 4, None) == abi.RS_ERR_POINTER
+    assert L.rs_set_wait_polls(0) > 0

@@ -96,6 +96,8 @@ def test_rows_bad_temperature_sets_status_and_spares_other_rows(abi):
                           0.0, 0.0, 0.0, None, None, ws.data_ptr(), ws.numel(), abi.stream())
     assert rc == 0
     assert L.rs_device_status(ws.data_ptr(), abi.stream()) == abi.abi.RS_ERR_TEMPERATURE
+    import rapid_sampling_b200 as rs
+    rs.device_status()       # the torch binding's host mirror (if registered) saw it too: consume it here
     # rows 0 and 3 as one-row calls with their own values; rows 1 and 2 ran at temperature 1
     st2 = abi.setup_rand(6, B)
     for b, temp in enumerate([1.0, 1.0, 1.0, float(np.float32(0.9))]):
@@ -104,3 +106,24 @@ def test_rows_bad_temperature_sets_status_and_spares_other_rows(abi):
     # too small a workspace is refused
     assert L.rs_sample_rows(lg.data_ptr(), 0, B, 1, V, None, st.data_ptr(), out.data_ptr(), t.data_ptr(), None, None, 0.0, 0.0, 0.0,
                             None, None, ws.data_ptr(), 256, abi.stream()) == abi.abi.RS_ERR_WORKSPACE
+
+
+def test_rows_probability_is_taken_before_the_penalty_update():
+    """With penalties, the reported probability of the sampled id must come from the penalties as they were BEFORE
+    the call (the same values the softmax ran on), on every call of a chain."""
+    import rapid_sampling_b200 as rs
+    from oracle import cpu_ref
+    B, V = 12, 32768
+    lg = make_logits("peaked", B, V, 13, torch)
+    t, k, p = row_settings(B)
+    pen = torch.zeros(B, V, device="cuda")
+    st = rs.setup_rand(5, B)
+    for call in range(4):
+        before = pen.cpu().clone()
+        ids, prob, kept = rs.batch_sampling_rows(lg.cuda(), st, t.cuda(), k.cuda(), p.cuda(), penalties=pen, presence_penalty=0.5,
+                                                 repetition_penalty=0.7, penalty_decay=0.9, return_prob=True)
+        ids, prob = ids.cpu(), prob.cpu().double()
+        for b in range(B):
+            d = cpu_ref.distribution(lg[b:b + 1], float(t[b]), int(k[b]), float(p[b]), penalties=before[b:b + 1])
+            want = float(d["probs"][0, ids[b]])
+            assert abs(float(prob[b]) - want) <= 1e-5 * want + 1e-12, (call, b, float(prob[b]), want)

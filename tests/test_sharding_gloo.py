@@ -1,6 +1,7 @@
 """CPU, world_size 2 over gloo: batch sharding is a pure partition -- each rank samples its own rows
 with states seeded by GLOBAL row index, and the gathered ids equal the unsharded run (checked with
-the CPU oracle standing in for the kernel; the GPU version of this test is in test_gpu_multi.py)."""
+the CPU oracle standing in for the kernel; the GPU version of this check is
+test_batch_shards_reproduce_the_unsharded_ids in test_gpu_baseline_configs.py)."""
 import os
 import socket
 
