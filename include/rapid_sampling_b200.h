@@ -247,8 +247,9 @@ int rs_selftest_bounded_wait(void* workspace_device, uint32_t polls, void* strea
 int rs_set_cluster_override(int cluster_ctas);
 
 /* Strategy override: 0 = automatic, 1 = always search the whole row (no candidate shortcut), 2 = always the
- * streaming variant, 3 = always the on-chip variant when the row fits.  Results are identical; testing /
- * benchmarking aid.  Returns the previous value. */
+ * streaming cluster variant, 3 = always the on-chip cluster variant when the row fits, 4 = always one CTA per row
+ * (fp32 logits with a full-size workspace; other calls keep the automatic choice).  Results are identical;
+ * testing / benchmarking aid.  Returns the previous value. */
 int rs_set_path_override(int mode);
 
 /* Number of sampler kernels launched through this library since it was loaded. */

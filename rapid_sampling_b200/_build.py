@@ -17,7 +17,8 @@ EXT_NAME = "_rs_torch"
 EXT = os.path.join(HERE, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--extra-device-vectorization", "-Xptxas", "-O3", "-Xcompiler", "-fPIC"]
+              "--extra-device-vectorization", "-Xptxas", "-O3", "-Xcompiler", "-fPIC"] + \
+    os.environ.get("RS_EXTRA_NVCC_FLAGS", "").split()
 
 
 def _newer(target, sources):
@@ -37,14 +38,28 @@ def _run(cmd, verbose):
         print(r.stdout)
 
 
+CU_SOURCES = ["rs_sampler.cu", "rs_rowcta.cu", "rs_vocab_parallel.cu"]
+HEADERS = [os.path.join(CSRC, h) for h in ("rs_device.cuh", "rs_common.cuh", "rs_rowcta.cuh")] + \
+    [os.path.join(INCLUDE, "rapid_sampling_b200.h")]
+OBJ_DIR = os.path.join(HERE, "build")
+
+
 def build_lib(force=False, verbose=False, ptxas_v=False):
-    srcs = [os.path.join(CSRC, "rs_sampler.cu"), os.path.join(CSRC, "rs_vocab_parallel.cu"),
-            os.path.join(CSRC, "rs_device.cuh"), os.path.join(INCLUDE, "rapid_sampling_b200.h")]
-    if not force and _newer(LIB, srcs):
-        return LIB
+    """Compiles every .cu file to an object of its own (in parallel), then links them into the library."""
+    import concurrent.futures as cf
     nvcc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc")
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_v else []) + ["-shared", "-o", LIB, srcs[0], srcs[1]]
-    _run(cmd, verbose or ptxas_v)
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    jobs = []
+    for name in CU_SOURCES:
+        src = os.path.join(CSRC, name)
+        obj = os.path.join(OBJ_DIR, name[:-3] + ".o")
+        if force or ptxas_v or not _newer(obj, [src] + HEADERS):
+            jobs.append([nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_v else []) + ["-c", src, "-o", obj])
+    with cf.ThreadPoolExecutor(max_workers=max(1, len(jobs))) as ex:
+        list(ex.map(lambda c: _run(c, verbose or ptxas_v), jobs))
+    objs = [os.path.join(OBJ_DIR, n[:-3] + ".o") for n in CU_SOURCES]
+    if jobs or not _newer(LIB, objs):
+        _run([nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"], verbose)
     return LIB
 
 

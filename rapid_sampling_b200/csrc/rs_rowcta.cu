@@ -1,0 +1,897 @@
+// Row-per-CTA variant of the sampler for large batches (sm_100a).
+//
+// The reference runs one 1024-thread CTA per row (sampling.cu:500, :1025) and re-reads a global scratch copy of the
+// row ~18 times.  Here a row is also handled by ONE CTA, so no value ever crosses an SM boundary, but:
+//   * a thread plays LPT of the reference's 1024 "virtual lanes" (lane t still owns float4 groups t, t+1024, ... and
+//     every fp32 sum keeps the reference's association: per-lane chain -> 32-lane xor tree -> warp values in order),
+//     so a row costs 1024/LPT threads and several rows share an SM;
+//   * every thread streams exactly the float4 groups it will read itself through a private pipeline of asynchronous
+//     16-byte copies (cp.async) into shared memory: several stripes in flight per thread, no registers held by loads
+//     in flight, and no barrier of any kind in the streaming passes.  The first stripes stay on chip as scaled logits,
+//     so the second pass re-reads only the rest (from L2);
+//   * the cutoff search runs on the short candidate list (first entries in registers) with one CTA barrier per
+//     evaluated round;
+//   * with penalties, the first stripes of the update pass are already in flight while the search runs.
+// Rows whose candidate list cannot settle the cutoff search the whole row on a global scratch row, dropping, in place
+// and order-preserving, every element below the current lower bound as the bracket rises.
+#include "rs_common.cuh"
+#include "rs_rowcta.cuh"
+
+#include <mutex>
+
+namespace rs {
+
+namespace {
+
+// shared-memory map (bytes)
+constexpr int kOffScal = 0;        // s_idxt, s_token
+constexpr int kOffWtot = 64;       // 32 warp totals of a scan
+constexpr int kOffBoxC = 192;      // 2 x [16 physical warps][8 words]
+constexpr int kOffBox = 1216;      // 2 x [4 values][32 virtual warps] floats, value-major
+constexpr int kBoxBytes = 4 * 32 * 4;
+static_assert(kOffBox + 2 * kBoxBytes <= kRowCtaFixedSmem, "fixed shared-memory area too small");
+constexpr int kStripeBytes = 16384;   // 1024 float4 groups: one group per virtual lane
+
+// order-preserving map float -> u32 (no NaN here: inputs are sanitised), so that integer warp reductions serve floats
+__device__ __forceinline__ uint32_t fkey(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float fromkey(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// The xor trees (offsets 16, 8, 4, 2, 1) of N values per lane at once.  While more than one value is left, a lane
+// keeps half of its partial sums and hands the other half to its partner -- the same additions as N separate
+// butterflies, in N - 1 + log2(32 / N) shuffles -- so that m[0] ends as the total of value index (lane >> log2(32 / N)),
+// identical in the lanes that share those bits.
+template <int N, int O>
+__device__ __forceinline__ void tree_levels(float* m, const int lane) {
+    if constexpr (O > 0) {
+        const bool up = (lane & O) != 0;
+        if constexpr (N > 1) {
+            constexpr int H = N / 2;
+#pragma unroll
+            for (int i = 0; i < H; i++) {
+                const float keepv = up ? m[i + H] : m[i], give = up ? m[i] : m[i + H];
+                m[i] = keepv + __shfl_xor_sync(0xffffffffu, give, O);
+            }
+            tree_levels<H, O / 2>(m, lane);
+        } else {
+            m[0] = m[0] + __shfl_xor_sync(0xffffffffu, m[0], O);
+            tree_levels<1, O / 2>(m, lane);
+        }
+    }
+}
+
+}  // namespace
+
+template <int LPT>
+__global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kernel(const Params p, const RowCtaPlan pl) {
+    constexpr int NT = kLanes / LPT;   // threads; thread t plays virtual lanes j * NT + t
+    constexpr int WPB = NT / 32;       // warps; physical warp pw plays virtual warps j * WPB + pw
+    constexpr int NV = LPT * 4;        // ordered masses a thread holds in a search round
+    constexpr int CR = 2;              // candidates per virtual lane that are kept in registers during the search
+    constexpr unsigned FULL = 0xffffffffu;
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int t = threadIdx.x, lane = t & 31, pw = t >> 5;
+    const int b = blockIdx.x;
+    const int V = p.V, V4 = V >> 2;
+    const int K = (V4 + kLanes - 1) >> 10;   // stripes of 1024 float4 groups
+    const int a_kind = p.kind, a_top_k = p.top_k, a_sel_rank = p.sel_rank;
+    const float a_scale = p.scale, a_top_p = p.top_p;
+    const bool rep = (a_kind == kRepetition);
+    const bool use_cnt = (a_kind != kTopP);
+    const float* lrow = reinterpret_cast<const float*>(p.logits) + (long long)b * p.row_stride;
+    float* prow = rep ? p.penalties + (long long)b * V : nullptr;
+    const int D = pl.depth, NC = pl.cached, cap = pl.cap;
+
+    int* s_idxt = reinterpret_cast<int*>(smem + kOffScal);
+    int* s_token = reinterpret_cast<int*>(smem + kOffScal + 4);
+    float* s_wtot = reinterpret_cast<float*>(smem + kOffWtot);
+    float* cand = reinterpret_cast<float*>(smem + pl.off_cand);          // entry i of virtual lane v at cand[i * 1024 + v]
+    unsigned char* ring = smem + pl.off_ring;                            // D stages of pl.stage_bytes
+    unsigned char* cache = smem + pl.off_cache;                          // NC stripes of scaled logits
+    if (t == 0) {
+        *s_idxt = 0;
+        *s_token = 0;
+    }
+
+    // ---- the thread's private copy pipeline ------------------------------------------------------------------
+    // The n-th stripe requested in a pass lands in ring stage n % D (its logits in the first 16 KiB, its penalties in
+    // the second), except that the logits of the first NC stripes go straight to their place in the on-chip cache.
+    // A thread only ever copies, reads and overwrites its own 16-byte slots, so nothing but its own wait_group orders
+    // anything.  Passes alternate their direction over the stripes (down, up, down): what one pass read last is what
+    // the next one reads first, so a batch larger than L2 still finds the recent part of its rows there.
+    const int Kf = V4 >> 10, rem = V4 & 1023;       // full stripes; float4 groups in the ragged last one
+    bool tail_ok[LPT];
+#pragma unroll
+    for (int j = 0; j < LPT; j++) tail_ok[j] = (j * NT + t) < rem;
+    const uint32_t sm_ring = smem_addr(ring) + (uint32_t)t * 16u, sm_cache = smem_addr(cache) + (uint32_t)t * 16u;
+    const float4* const gl = reinterpret_cast<const float4*>(lrow) + t;
+    const float4* const gp = reinterpret_cast<const float4*>(prow) + t;
+    int ik = 0, islot = 0, idir = 1;   // next stripe to request, its stage, and the direction of the pass
+    auto request = [&](const bool with_logits, const bool with_pen) {
+        if (ik >= 0 && ik < K) {
+            const uint32_t st = sm_ring + (uint32_t)islot * (uint32_t)pl.stage_bytes;
+            const uint32_t ldst = (ik < NC) ? sm_cache + (uint32_t)ik * kStripeBytes : st;
+            const float4* src = gl + (size_t)ik * kLanes;
+            const float4* psrc = gp + (size_t)ik * kLanes;
+            const bool fullk = ik < Kf;
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                if (fullk || tail_ok[j]) {
+                    if (with_logits) cp_async16(ldst + j * NT * 16, src + j * NT);
+                    if (with_pen) cp_async16(st + kStripeBytes + j * NT * 16, psrc + j * NT);
+                }
+            }
+        }
+        cp_commit();
+        ik += idir;
+        islot = (islot + 1 == D) ? 0 : islot + 1;
+    };
+    auto wait_stage = [&]() {   // the oldest requested stage has landed
+        if (D == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else if (D == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+        else asm volatile("cp.async.wait_group 3;" ::: "memory");
+    };
+    auto begin_pass = [&](const int first, const int dir, const bool with_logits, const bool with_pen) {
+        ik = first;
+        idir = dir;
+        islot = 0;
+        for (int i = 0; i < D - 1; i++) request(with_logits, with_pen);
+    };
+    begin_pass(K - 1, -1, true, rep);
+
+    // exchange of warp values inside the CTA: two alternating boxes, one barrier per exchange
+    int phase = 0;
+    auto box_of = [&](int ph) -> float* { return reinterpret_cast<float*>(smem + kOffBox + ph * kBoxBytes); };
+    auto boxc_of = [&](int ph) -> uint32_t* { return reinterpret_cast<uint32_t*>(smem + kOffBoxC + ph * 16 * 8 * 4); };
+
+    uint32_t ts[10];
+    const bool want_ts = (p.dbg_trace != nullptr);
+    unsigned long long t_begin = 0;
+    auto stamp = [&](int i) {
+        if (want_ts) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (i == 0) t_begin = now;
+            ts[i] = (uint32_t)(now - t_begin);
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < 10; i++) ts[i] = 0;
+    stamp(0);
+
+    RngWords rng;
+    {
+        const uint4* st = reinterpret_cast<const uint4*>(p.states + (long long)b * RS_STATE_BYTES);
+        rng.ctr = st[0]; rng.block = st[1]; rng.key_pos = st[2];
+    }
+    uint32_t rnd4[4], r0, r1;
+    rng_peek2(rng, r0, r1, rnd4);
+    const float ux = u01(r0), uy = u01(r1);
+
+    // x of one float4 group as the streaming passes compute it, read from global memory (slow paths only)
+    auto xload_global = [&](int g) -> float4 {
+        float4 v = __ldg(reinterpret_cast<const float4*>(lrow) + g);
+        if (rep) v = scaled4_rep(v, __ldcg(reinterpret_cast<const float4*>(prow) + g), a_scale);
+        else v = scaled4(v, a_scale);
+        return v;
+    };
+
+    // ---- pass 1: x = sanitised scaled logit (sampling.cu:208-227, :547-559); every virtual lane's maximum ----
+    float tmax[LPT];
+#pragma unroll
+    for (int j = 0; j < LPT; j++) tmax[j] = -INFINITY;
+    {
+        int cslot = 0;
+        for (int k = K - 1; k >= 0; k--) {
+            request(true, rep);
+            wait_stage();
+            const unsigned char* st = ring + (size_t)cslot * pl.stage_bytes;
+            const bool keep = (k < NC);
+            unsigned char* own = cache + (size_t)k * kStripeBytes;
+            const unsigned char* src = keep ? own : st;
+            const bool fullk = k < Kf;
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                const int l = j * NT + t;
+                if (fullk || tail_ok[j]) {
+                    float4 v = reinterpret_cast<const float4*>(src)[l];
+                    if (rep) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
+                    else v = scaled4(v, a_scale);
+                    tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
+                    if (keep) reinterpret_cast<float4*>(own)[l] = v;
+                }
+            }
+            cslot = (cslot + 1 == D) ? 0 : cslot + 1;
+        }
+    }
+    begin_pass(NC, 1, true, rep);   // the second pass's first stripes travel while the maxima are reduced
+    stamp(1);
+    stamp(2);
+    // row maximum, and per virtual warp its sel_rank-th largest lane maximum: at least sel_rank elements of that
+    // warp are >= it, so the minimum over the warps bounds 32 * sel_rank elements of the row from below
+    const int sel_rank = a_sel_rank;
+    float mx, beta_x;
+    {
+        uint32_t* box = reinterpret_cast<uint32_t*>(box_of(phase));
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            const uint32_t key = fkey(tmax[j]);
+            uint32_t top = __reduce_max_sync(FULL, key), sel = top, cur = key;
+            for (int r = 1; r < sel_rank; r++) {     // drop one occurrence of the current maximum, take the next
+                const unsigned m = __ballot_sync(FULL, cur == sel);
+                if (lane == __ffs(m) - 1) cur = 0u;
+                sel = __reduce_max_sync(FULL, cur);
+            }
+            if (lane == 0) {
+                box[j * WPB + pw] = top;
+                box[32 + j * WPB + pw] = sel;
+            }
+        }
+        __syncthreads();
+        mx = fromkey(__reduce_max_sync(FULL, box[lane]));
+        beta_x = fromkey(__reduce_min_sync(FULL, box[32 + lane]));
+        phase ^= 1;
+    }
+    stamp(3);
+    const bool try_cand = (sel_rank > 0);
+    float beta_e = try_cand ? exp2f(beta_x - mx) : INFINITY;
+
+    // ---- pass 2: e = exp2f(x - max), ordered denominator (sampling.cu:560-572); min / max of e; elements with
+    // e >= beta_e are appended, in order, to their lane's candidate list.  A list that looks too thin to settle the
+    // cutoff gets its bound lowered 16-fold and the pass repeated (from global memory), at most twice. ------------
+    float acc[LPT], emin, emax, csum, denom;
+    int nc[LPT], ns;
+    bool cand_ok;
+    uint32_t ncand, nstrict;
+    auto pass2_group = [&](const int j, float4 v) {
+        v.x = exp2f(v.x - mx);
+        v.y = exp2f(v.y - mx);
+        v.z = exp2f(v.z - mx);
+        v.w = exp2f(v.w - mx);
+        float em = 0.f;
+        em += v.x; em += v.y; em += v.z; em += v.w;
+        acc[j] += em;
+        const float hi = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+        emin = fminf(fminf(emin, fminf(v.x, v.y)), fminf(v.z, v.w));
+        emax = fmaxf(emax, hi);
+        if (hi >= beta_e) {
+            const float e4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                if (e4[q] >= beta_e) {
+                    if (nc[j] < cap) cand[nc[j] * kLanes + j * NT + t] = e4[q];
+                    nc[j]++;
+                    ns += (e4[q] > beta_e) ? 1 : 0;
+                }
+            }
+            csum += (v.x >= beta_e ? v.x : 0.f) + (v.y >= beta_e ? v.y : 0.f) + (v.z >= beta_e ? v.z : 0.f) +
+                    (v.w >= beta_e ? v.w : 0.f);
+        }
+    };
+    auto pass2 = [&](const bool last) -> bool {
+        emin = INFINITY; emax = -INFINITY; csum = 0.f; ns = 0;
+#pragma unroll
+        for (int j = 0; j < LPT; j++) { acc[j] = 0.f; nc[j] = 0; }
+        int cslot = 0;
+        for (int k = 0; k < K; k++) {
+            const bool kept = (k < NC);
+            const unsigned char* st = ring + (size_t)cslot * pl.stage_bytes;
+            if (!kept) {
+                request(true, rep);
+                wait_stage();
+                cslot = (cslot + 1 == D) ? 0 : cslot + 1;
+            }
+            const unsigned char* src = kept ? cache + (size_t)k * kStripeBytes : st;
+            const bool fullk = k < Kf;
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                const int l = j * NT + t;
+                if (fullk || tail_ok[j]) {
+                    float4 v = reinterpret_cast<const float4*>(src)[l];
+                    if (!kept) {
+                        if (rep) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
+                        else v = scaled4(v, a_scale);
+                    }
+                    pass2_group(j, v);
+                }
+            }
+        }
+        stamp(4);
+        float* box = box_of(phase);
+        uint32_t* boxc = boxc_of(phase);
+        int nct = 0;
+        bool over = false;
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            const float a = warp_tree_sum(acc[j]);
+            if (lane == 0) box[j * WPB + pw] = a;
+            nct += nc[j];
+            over = over || (nc[j] > cap);
+        }
+        const uint32_t kmin = __reduce_min_sync(FULL, fkey(emin)), kmax = __reduce_max_sync(FULL, fkey(emax));
+        const uint32_t wov = __any_sync(FULL, over) ? 1u : 0u;
+        const uint32_t wnc = __reduce_add_sync(FULL, (uint32_t)nct), wns = __reduce_add_sync(FULL, (uint32_t)ns);
+        const float wcs = warp_tree_sum(csum);
+        if (lane == 0) {
+            boxc[pw * 8 + 0] = kmin; boxc[pw * 8 + 1] = kmax; boxc[pw * 8 + 2] = wov;
+            boxc[pw * 8 + 3] = wnc; boxc[pw * 8 + 4] = wns; boxc[pw * 8 + 5] = __float_as_uint(wcs);
+        }
+        __syncthreads();
+        denom = warp_tree_sum(box[lane]);   // tree over the 32 warp partials (sampling.cu:29-33)
+        const bool in = lane < WPB;
+        emin = fromkey(__reduce_min_sync(FULL, in ? boxc[lane * 8 + 0] : 0xffffffffu));
+        emax = fromkey(__reduce_max_sync(FULL, in ? boxc[lane * 8 + 1] : 0u));
+        cand_ok = try_cand && (__reduce_add_sync(FULL, in ? boxc[lane * 8 + 2] : 0u) == 0u);
+        ncand = __reduce_add_sync(FULL, in ? boxc[lane * 8 + 3] : 0u);
+        nstrict = __reduce_add_sync(FULL, in ? boxc[lane * 8 + 4] : 0u);
+        const float cmass = warp_tree_sum(in ? __uint_as_float(boxc[lane * 8 + 5]) : 0.f) / denom;   // a forecast only
+        phase ^= 1;
+        const bool enough = (use_cnt && nstrict > (uint32_t)a_top_k) || cmass > a_top_p * 1.001f;
+        return !cand_ok || enough || last || !(beta_e > 0.f);
+    };
+    for (int attempt = 0; attempt < 3; attempt++) {
+        if (pass2(attempt == 2)) break;
+        if (attempt == 0) {
+            const bool all_in = beta_e * 0.0625f <= emin;      // a flat row: the lowered bound would admit every element
+            if (all_in && V > cap * kLanes) {
+                cand_ok = false;
+                break;
+            }
+            beta_e = all_in ? 0.f : beta_e * 0.0625f;
+        } else {
+            beta_e *= 0.0625f;
+        }
+        begin_pass(NC, 1, true, rep);   // the same pass again with the lowered bound
+    }
+    if (rep) begin_pass(K - 1, -1, false, true);   // the update pass's first penalty stripes, in flight from here on
+    const float pmin = emin / denom, pmax = emax / denom;   // division is monotone
+    if (p.dbg_probs) {   // test instrumentation: the probabilities of the whole row
+        float* dprow = p.dbg_probs + (long long)b * V;
+        for (int k = 0; k < K; k++)
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                const int g = k * kLanes + j * NT + t;
+                if (g < V4) {
+                    float4 v = xload_global(g);
+                    v.x = exp2f(v.x - mx) / denom; v.y = exp2f(v.y - mx) / denom;
+                    v.z = exp2f(v.z - mx) / denom; v.w = exp2f(v.w - mx) / denom;
+                    reinterpret_cast<float4*>(dprow)[g] = v;
+                }
+            }
+    }
+    stamp(5);
+
+    // ---- row totals of NV ordered masses (4 pivots x LPT lanes per thread), 4 counts and min / max of two bit
+    // patterns.  Masses: xor tree over the 32 lanes of each virtual warp -- all trees share shuffles -- then the 32
+    // warp values added in warp order, as thread 0 of the reference does (sampling.cu:34-42): lanes 0..3 of every
+    // warp run the four 32-step chains on vector loads, lanes 4..9 add up the counts and bounds, and the ten results
+    // reach the other lanes by shuffles.
+    auto totals = [&](float (&m)[NV], const uint32_t (&c)[4], uint32_t mn, uint32_t mxv, uint32_t (&cnt)[4], float (&mass)[4],
+                      uint32_t& vmin, uint32_t& vmax) {
+        tree_levels<NV, 16>(m, lane);
+        // value index i = j * 4 + pivot ended in the lanes whose upper bits spell i
+        constexpr int SH = (NV == 32) ? 0 : (NV == 16) ? 1 : (NV == 8) ? 2 : 3;
+        uint32_t cs[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) cs[i] = __reduce_add_sync(FULL, c[i]);
+        mn = __reduce_min_sync(FULL, mn);
+        mxv = __reduce_max_sync(FULL, mxv);
+        float* box = box_of(phase);
+        uint32_t* boxc = boxc_of(phase);
+        if ((lane & ((1 << SH) - 1)) == 0) {
+            const int i = lane >> SH;
+            box[(i & 3) * 32 + (i >> 2) * WPB + pw] = m[0];
+        }
+        if (lane == 0) {
+            *reinterpret_cast<uint4*>(boxc + pw * 8) = make_uint4(cs[0], cs[1], cs[2], cs[3]);
+            *reinterpret_cast<uint2*>(boxc + pw * 8 + 4) = make_uint2(mn, mxv);
+        }
+        __syncthreads();
+        uint32_t r = 0u;
+        if (lane < 4) {
+            const float4* col = reinterpret_cast<const float4*>(box + lane * 32);
+            float4 w[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) w[q] = col[q];
+            float sacc = w[0].x;
+            sacc += w[0].y; sacc += w[0].z; sacc += w[0].w;
+#pragma unroll
+            for (int q = 1; q < 8; q++) { sacc += w[q].x; sacc += w[q].y; sacc += w[q].z; sacc += w[q].w; }
+            r = __float_as_uint(sacc);
+        } else if (lane < 10) {
+            const int f = lane - 4;
+            uint32_t a = boxc[f];
+#pragma unroll
+            for (int w = 1; w < WPB; w++) {
+                const uint32_t x = boxc[w * 8 + f];
+                a = (f < 4) ? a + x : (f == 4) ? min(a, x) : max(a, x);
+            }
+            r = a;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            mass[i] = __uint_as_float(__shfl_sync(FULL, r, i));
+            cnt[i] = __shfl_sync(FULL, r, 4 + i);
+        }
+        vmin = __shfl_sync(FULL, r, 8);
+        vmax = __shfl_sync(FULL, r, 9);
+        phase ^= 1;
+    };
+
+    // ---- cutoff search (sampling.cu:593-654, :829-878): the reference's loop replayed with the same pivots and the
+    // same decisions; see the cluster variant for why the candidate list answers every pivot the same way -----------
+    const uint32_t top_k = (uint32_t)a_top_k;
+    const float top_p = a_top_p;
+    uint32_t left = 0, right = 0, rounds = 0, n_eval = 0;
+    uint32_t path = 1;
+    uint32_t conv_cnt = 0, conv_left_cnt = 0;
+    float conv_mass = 0.f;
+    auto run_search = [&](auto&& lane_eval, const bool clamp, const uint32_t beta_p, const bool sure_cnt,
+                          const uint32_t n_above) -> bool {
+        const uint32_t ustar = clamp ? beta_p + 1u : 0u;
+        left = __float_as_uint(pmin);
+        right = __float_as_uint(pmax) + 1u;
+        rounds = 0;
+        uint32_t cnt_x = (uint32_t)V, cnt_r = 0u;
+        float mass_x = 1.0f, mass_r = 0.f;
+        bool frozen = false, valid = true;
+        uint32_t v_bits = 0, cnt_v = 0;
+        float mass_v = 0.f;
+        while (rounds < 64u) {
+            const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
+            if (!(go && left < right - 1u)) break;
+            rounds++;
+            const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pwv = (pz + right) >> 1;
+            const uint32_t pv[3] = {py, pz, pwv};
+            uint32_t cnt[4];
+            float mass[4];
+            if (clamp && sure_cnt && pwv <= beta_p) {
+                left = pwv;
+                cnt_x = n_above;
+                mass_x = 0.f;
+                continue;
+            }
+            if (!frozen) {
+                n_eval++;
+                const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
+                                    __uint_as_float(max(pwv, ustar)), __uint_as_float(max(left + 1u, ustar))};
+                float m[NV];
+                uint32_t c[4], mn, mxv, vmin, vmax;
+                lane_eval(f, left, right, cnt_x, m, c, mn, mxv);
+                totals(m, c, mn, mxv, cnt, mass, vmin, vmax);
+                if (clamp && left >= beta_p && vmin >= vmax) {
+                    frozen = true;
+                    v_bits = (vmin == vmax) ? vmin : left;
+                    cnt_v = cnt[3];
+                    mass_v = mass[3];
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 3; i++) {
+                    const bool at_left = (pv[i] == left), le_v = (pv[i] <= v_bits);
+                    cnt[i] = at_left ? cnt_x : le_v ? cnt_v : cnt_r;
+                    mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
+                }
+            }
+            bool ok[3], bad = false;
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                const bool below = clamp && pv[i] <= beta_p;
+                const bool exceeds = (use_cnt && cnt[i] > top_k) || mass[i] > top_p;
+                const bool pass = (!use_cnt || cnt[i] < top_k) && mass[i] < top_p;
+                ok[i] = !below && pass;
+                bad = bad || (below && !exceeds);
+            }
+            if (bad) { valid = false; break; }
+            const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
+            const uint32_t nl = s0 ? left : s1 ? py : s2 ? pz : pwv;
+            const uint32_t nr = s0 ? py : s1 ? pz : s2 ? pwv : right;
+            const uint32_t ncx = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
+            const float nmx = s0 ? mass_x : s1 ? mass[0] : s2 ? mass[1] : mass[2];
+            const uint32_t ncr = s0 ? cnt[0] : s1 ? cnt[1] : s2 ? cnt[2] : cnt_r;
+            const float nmr = s0 ? mass[0] : s1 ? mass[1] : s2 ? mass[2] : mass_r;
+            left = nl; right = nr; cnt_x = ncx; mass_x = nmx; cnt_r = ncr; mass_r = nmr;
+        }
+        conv_cnt = cnt_r;
+        conv_mass = mass_r;
+        conv_left_cnt = cnt_x;
+        return valid && (!clamp || left > beta_p);
+    };
+
+    float gtp[LPT];          // per virtual lane: mass above the threshold, ties with it, count above
+    uint32_t eqk[LPT], gtk[LPT];
+#pragma unroll
+    for (int j = 0; j < LPT; j++) { gtp[j] = 0.f; eqk[j] = 0u; gtk[j] = 0u; }
+    // Two attempts share one copy of the search loop: the candidate lists first (the first CR probabilities of every
+    // lane's list live in registers for the rounds -- unused places hold -1, which no pivot admits -- longer lists
+    // continue in shared memory), then, if they cannot settle the cutoff, the whole row on the global scratch row.
+    int m_own[LPT], n_row[LPT];
+    float creg[LPT][CR];
+    Row<1, false> row;
+    row.slab = reinterpret_cast<float4*>(p.scratch + (long long)b * V);
+    row.t = t;
+    row.tg = t;
+    bool long_lists = false;
+    uint32_t beta_p = 0u;
+    uint32_t list_total = (uint32_t)V, list_left = 0u;
+    bool whole = false;
+    auto lane_eval = [&](const float (&f)[4], uint32_t lo, uint32_t hi, uint32_t cnt_lo, float (&m)[NV], uint32_t (&c)[4],
+                         uint32_t& mn, uint32_t& mxv) {
+        c[0] = c[1] = c[2] = c[3] = 0u;
+        if (!whole) {
+            mn = 0xffffffffu;
+            mxv = 0u;
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < CR; i++) {
+                    const float q = creg[j][i];
+                    const uint32_t qb = __float_as_uint(q);
+                    if (q >= f[0]) { c[0]++; a0 += q; }
+                    if (q >= f[1]) { c[1]++; a1 += q; }
+                    if (q >= f[2]) { c[2]++; a2 += q; }
+                    if (q >= f[3]) { c[3]++; a3 += q; }
+                    if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
+                }
+                if (long_lists) {
+                    for (int i = CR; i < m_own[j]; i++) {
+                        const float q = cand[i * kLanes + j * NT + t];
+                        const uint32_t qb = __float_as_uint(q);
+                        if (q >= f[0]) { c[0]++; a0 += q; }
+                        if (q >= f[1]) { c[1]++; a1 += q; }
+                        if (q >= f[2]) { c[2]++; a2 += q; }
+                        if (q >= f[3]) { c[3]++; a3 += q; }
+                        if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
+                    }
+                }
+                m[j * 4 + 0] = a0; m[j * 4 + 1] = a1; m[j * 4 + 2] = a2; m[j * 4 + 3] = a3;
+            }
+        } else {
+            mn = 0u;
+            mxv = 1u;   // bounds are not tracked on the whole row
+            const bool compact = (lo != list_left) && (cnt_lo * 2u <= list_total);
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                float mj[4];
+                uint32_t c01, c23;
+                row.tg = j * NT + t;
+                if (compact) slab_pass<1, false, true>(row, n_row[j], f, __uint_as_float(lo), mj, c01, c23);
+                else slab_pass<1, false, false>(row, n_row[j], f, 0.f, mj, c01, c23);
+                m[j * 4 + 0] = mj[0]; m[j * 4 + 1] = mj[1]; m[j * 4 + 2] = mj[2]; m[j * 4 + 3] = 0.f;
+                c[0] += c01 & 0xffffu; c[1] += c01 >> 16; c[2] += c23 & 0xffffu;
+            }
+            if (compact) { list_total = cnt_lo; list_left = lo; }
+        }
+    };
+    for (int attempt = cand_ok ? 0 : 1; attempt < 2; attempt++) {
+        whole = (attempt == 1);
+        if (!whole) {
+            int m_max = 0;
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                m_own[j] = min(nc[j], cap);
+                m_max = max(m_max, m_own[j]);
+#pragma unroll
+                for (int i = 0; i < CR; i++) creg[j][i] = -1.f;
+                for (int i = 0; i < m_own[j]; i++) {
+                    const float q = cand[i * kLanes + j * NT + t] / denom;
+                    cand[i * kLanes + j * NT + t] = q;
+#pragma unroll
+                    for (int r = 0; r < CR; r++)
+                        if (i == r) creg[j][r] = q;
+                }
+            }
+            long_lists = __any_sync(FULL, m_max > CR);
+            beta_p = __float_as_uint(beta_e / denom);
+        } else {
+            if (emin == emax) {
+                // every element has the same probability: the reference's loop never starts, the whole row ties
+                left = __float_as_uint(pmin);
+                right = left + 1u;
+#pragma unroll
+                for (int j = 0; j < LPT; j++) {
+                    const int vl = j * NT + t;
+                    eqk[j] = (vl < V4) ? (uint32_t)(((V4 - vl + kLanes - 1) >> 10) * 4) : 0u;
+                }
+                break;
+            }
+            // p = exp2f(x - max) / denom (sampling.cu:573-590) into the global scratch row
+            list_left = __float_as_uint(pmin);
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                const int vl = j * NT + t;
+                const int Kt = (vl < V4) ? ((V4 - vl + kLanes - 1) >> 10) : 0;
+                n_row[j] = Kt * 4;
+                row.tg = vl;
+                for (int sidx = 0; sidx < Kt; sidx++) {
+                    float4 v = (sidx < NC) ? reinterpret_cast<const float4*>(cache + (size_t)sidx * kStripeBytes)[vl]
+                                           : xload_global(sidx * kLanes + vl);
+                    v.x = exp2f(v.x - mx) / denom; v.y = exp2f(v.y - mx) / denom;
+                    v.z = exp2f(v.z - mx) / denom; v.w = exp2f(v.w - mx) / denom;
+                    row.st(sidx, v);
+                }
+            }
+        }
+        const bool ok = run_search(lane_eval, !whole, beta_p, !whole && use_cnt && nstrict > top_k, nstrict);
+        const float thr_found = __uint_as_float(left);
+        if (!whole) {
+            if (!ok) continue;
+            path = 0;
+#pragma unroll
+            for (int j = 0; j < LPT; j++)
+                for (int i = 0; i < m_own[j]; i++) {
+                    const float q = cand[i * kLanes + j * NT + t];
+                    if (q == thr_found) eqk[j]++;
+                    if (q > thr_found) { gtk[j]++; gtp[j] += q; }
+                }
+            break;
+        }
+        // recount on the whole row (sampling.cu:657-680)
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            row.tg = j * NT + t;
+            const int slots = (n_row[j] + 3) >> 2;
+            for (int sidx = 0; sidx < slots; sidx++) {
+                const float4 v = row.ld(sidx);
+                const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    if (e[q] == thr_found) eqk[j]++;
+                    if (e[q] > thr_found) { gtk[j]++; gtp[j] += e[q]; }
+                }
+            }
+        }
+    }
+    stamp(6);
+    const bool early_exit = left < right - 1u;
+    const float thr = __uint_as_float(left);
+
+    // totals at the threshold (sampling.cu:657-680): lane 31 of a descending-offset scan holds the tree value
+    float sgtp;
+    uint32_t seqk, sgtk;
+    if (path == 0 && !early_exit) {
+        sgtp = conv_mass;
+        sgtk = conv_cnt;
+        seqk = conv_left_cnt - conv_cnt;
+    } else {
+        float m[NV];
+        uint32_t c[4] = {0u, 0u, 0u, 0u}, cnt[4], d0, d1;
+        float mass[4];
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            m[j * 4 + 0] = gtp[j]; m[j * 4 + 1] = 0.f; m[j * 4 + 2] = 0.f; m[j * 4 + 3] = 0.f;
+            c[0] += gtk[j];
+            c[1] += eqk[j];
+        }
+        totals(m, c, 0u, 0u, cnt, mass, d0, d1);
+        sgtp = mass[0];
+        sgtk = cnt[0];
+        seqk = cnt[1];
+    }
+
+    // ---- compensation factor for the boundary ties (sampling.cu:690-696, :903-908) ---------------------------
+    float comp = 1.0f;
+    if (seqk > 0) {
+        comp = fminf(sanitize((top_p - sgtp) / (thr * seqk)), comp);
+        if (use_cnt) comp = fminf(sanitize(float(top_k - sgtk) / seqk), comp);
+        comp = fmaxf(comp, 0.0f);
+    }
+
+    // ---- lane pick (sampling.cu:699-723) -----------------------------------------------------------------------
+    float incl[LPT];
+    {
+        float* box = box_of(phase);
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            const float actual_p = gtp[j] + (thr * eqk[j]) * comp;
+            incl[j] = warp_scan_desc(actual_p, lane);
+            if (lane == 31) box[j * WPB + pw] = incl[j];
+        }
+        __syncthreads();
+    }
+    float sum_p, randp;
+    {
+        const float4* box4 = reinterpret_cast<const float4*>(box_of(phase));
+        phase ^= 1;
+        // sequential prefix over the 32 warp totals (sampling.cu:85-92); this thread needs the prefix before each of
+        // its virtual warps j * WPB + pw, i.e. the running sum after warp w whenever w % WPB == pw - 1
+        float before[LPT];
+#pragma unroll
+        for (int j = 0; j < LPT; j++) before[j] = 0.f;
+        float s0 = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const float4 v = box4[q];
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int w = q * 4 + r;
+                s0 = (w == 0) ? e[r] : s0 + e[r];
+                if ((w % WPB) == pw - 1 && w / WPB < LPT) before[w / WPB] = s0;             // prefix before warp w + 1, same j
+                if (pw == 0 && (w % WPB) == WPB - 1 && w / WPB + 1 < LPT) before[w / WPB + 1] = s0;   // ... next j
+            }
+        }
+        sum_p = s0;
+        randp = sum_p * ux;
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            const int vw = j * WPB + pw;
+            const float pre_prev = before[j];
+            const float cumu_p = (vw > 0) ? incl[j] + pre_prev : incl[j];
+            const bool u = (randp <= cumu_p);
+            bool u_prev = __shfl_up_sync(FULL, u, 1);
+            if (lane == 0) u_prev = (vw > 0) ? (randp <= pre_prev) : false;
+            // exactly one lane sees the 0 -> 1 transition (the scan is non-decreasing); with none the reference
+            // keeps its initial value, lane 0
+            if (u != u_prev) *s_idxt = j * NT + t;
+        }
+    }
+    stamp(7);
+    if (t == 0) {   // advance the stored RNG state by one 4-word block
+        const uint4 nctr = ctr_next(rng.ctr);
+        uint4* st = reinterpret_cast<uint4*>(p.states + (long long)b * RS_STATE_BYTES);
+        st[0] = nctr;
+        st[1] = philox4x32_10(nctr, rng.key_pos.x, rng.key_pos.y);
+    }
+
+    // ---- element pick inside the chosen lane (sampling.cu:725-751) ---------------------------------------------
+    __syncthreads();
+    const int idxt = *s_idxt;
+    float oincl[LPT];
+    int idn_of[LPT];
+#pragma unroll
+    for (int j = 0; j < LPT; j++) {
+        const int vt = j * NT + t;   // thread index of the reference block
+        const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
+        float o0 = 0.f;
+        if (idn < V) {
+            const float x = scaled_logit(lrow[idn], rep ? prow[idn] : 0.f, rep, a_scale);
+            o0 = exp2f(x - mx) / denom;
+        }
+        const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
+        oincl[j] = warp_scan_desc(o, lane);
+        idn_of[j] = idn;
+        if (lane == 31) s_wtot[vt >> 5] = oincl[j];
+    }
+    __syncthreads();
+    float sum_o, rand2;
+    {
+        float opre[LPT];
+#pragma unroll
+        for (int j = 0; j < LPT; j++) opre[j] = 0.f;
+        float s0 = 0.f;
+        const float4* wt4 = reinterpret_cast<const float4*>(s_wtot);
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const float4 v = wt4[q];
+            const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int r = 0; r < 4; r++) {
+                const int w = q * 4 + r;
+                s0 = (w == 0) ? e[r] : s0 + e[r];
+                if ((w % WPB) == pw - 1 && w / WPB < LPT) opre[w / WPB] = s0;
+                if (pw == 0 && (w % WPB) == WPB - 1 && w / WPB + 1 < LPT) opre[w / WPB + 1] = s0;
+            }
+        }
+        sum_o = s0;
+        rand2 = sum_o * uy;
+#pragma unroll
+        for (int j = 0; j < LPT; j++) {
+            const int vw = j * WPB + pw;
+            const float cumu_o = (vw > 0) ? oincl[j] + opre[j] : oincl[j];
+            const bool uo = (rand2 <= cumu_o);
+            bool uo_prev = __shfl_up_sync(FULL, uo, 1);
+            if (lane == 0) uo_prev = (vw > 0) ? (rand2 <= opre[j]) : false;
+            if (uo != uo_prev) *s_token = (idn_of[j] < V) ? idn_of[j] : 0;
+        }
+    }
+    __syncthreads();
+    const int token = *s_token;
+    stamp(8);
+    if (t == 0) p.out[b] = token;
+
+    // ---- penalties: decay everything, add the hit on the sampled id (sampling.cu:427-437); the old values come
+    // through the copy pipeline, whose first stripes have been in flight since the second pass ended -------------
+    if (rep) {
+        int cslot = 0;
+        for (int k = K - 1; k >= 0; k--) {
+            request(false, true);
+            wait_stage();
+            const unsigned char* st = ring + (size_t)cslot * pl.stage_bytes;
+            const bool fullk = k < Kf;
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
+                const int l = j * NT + t, i4 = k * kLanes + l;
+                if (fullk || tail_ok[j]) {
+                    const float4 q4 = reinterpret_cast<const float4*>(st + kStripeBytes)[l];
+                    float e[4] = {q4.x, q4.y, q4.z, q4.w};
+                    if (i4 != (token >> 2)) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) e[q] = fmaf(e[q], p.decay, 0.f);
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const float old = e[q];
+                            e[q] = fmaf(old, p.decay, (i4 * 4 + q != token) ? 0.f : (old == 0.f ? p.presence : p.repetition));
+                        }
+                    }
+                    reinterpret_cast<float4*>(prow)[i4] = make_float4(e[0], e[1], e[2], e[3]);
+                }
+            }
+            cslot = (cslot + 1 == D) ? 0 : cslot + 1;
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    stamp(9);
+    if (t == 0 && p.dbg_trace) {
+        rs_trace tr;
+        tr.maxu = mx; tr.denom = denom; tr.pmin = pmin; tr.pmax = pmax; tr.threshold = thr; tr.comp = comp;
+        tr.sgtp = sgtp; tr.sum_p = sum_p; tr.randp = randp; tr.sum_o = sum_o; tr.rand2 = rand2;
+        tr.left = left; tr.seqk = seqk; tr.sgtk = sgtk; tr.rounds = rounds; tr.idxt = (uint32_t)idxt;
+        tr.early_exit = early_exit ? 1u : 0u;
+        tr.rnd[0] = rnd4[0]; tr.rnd[1] = rnd4[1]; tr.rnd[2] = rnd4[2]; tr.rnd[3] = rnd4[3];
+        tr.token = token;
+        tr.path = path;
+        tr.ncand = ncand;
+#pragma unroll
+        for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
+        tr.t_ns[0] = n_eval;
+        p.dbg_trace[b] = tr;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+// Shared memory of a row-CTA launch: fixed area, candidate lists (cap entries per virtual lane), copy stages, and the
+// stripes that stay on chip between the passes.
+RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int smem_budget) {
+    RowCtaPlan pl;
+    const int K = (V / 4 + kLanes - 1) / kLanes;
+    pl.stage_bytes = rep ? 2 * kStripeBytes : kStripeBytes;
+    pl.cap = (sel_rank > 0) ? 6 : 0;
+    pl.off_cand = kRowCtaFixedSmem;
+    pl.off_ring = pl.off_cand + pl.cap * kLanes * 4;
+    const int room = smem_budget - pl.off_ring;
+    // enough stages for the memory latency first (about 64 KiB in flight per CTA), then stripes kept on chip
+    int depth = rep ? 3 : 6;
+    if (depth > K + 1) depth = K + 1;
+    while (depth > 2 && depth * pl.stage_bytes > room) depth--;
+    pl.depth = depth;
+    int keep = (room - depth * pl.stage_bytes) / kStripeBytes;
+    if (keep > K) keep = K;
+    pl.cached = keep < 0 ? 0 : keep;
+    pl.off_cache = pl.off_ring + depth * pl.stage_bytes;
+    pl.smem_bytes = pl.off_cache + pl.cached * kStripeBytes;
+    return pl;
+}
+
+template <int LPT>
+static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t stream, int smem_optin, bool* attr_done) {
+    auto kern = rowcta_kernel<LPT>;
+    if (!*attr_done) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin) != cudaSuccess) return RS_ERR_CUDA;
+        *attr_done = true;
+    }
+    kern<<<(unsigned)p.B, kLanes / LPT, (size_t)pl.smem_bytes, stream>>>(p, pl);
+    return cudaGetLastError() == cudaSuccess ? RS_OK : RS_ERR_CUDA;
+}
+
+int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin) {
+    static std::mutex mu;
+    static bool attr_done[64][2] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RS_ERR_CUDA;
+    if (pl.depth < 2 || pl.depth > 8 || pl.smem_bytes > smem_optin) return RS_ERR_LIMIT;
+    std::lock_guard<std::mutex> lk(mu);
+    if (lanes_per_thread == 2) return rowcta_launch_t<2>(p, pl, stream, smem_optin, &attr_done[dev][0]);
+    return rowcta_launch_t<4>(p, pl, stream, smem_optin, &attr_done[dev][1]);
+}
+
+}  // namespace rs

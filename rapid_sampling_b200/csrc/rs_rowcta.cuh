@@ -1,0 +1,25 @@
+// Launch interface of the row-per-CTA sampler variant (rs_rowcta.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+namespace rs {
+
+struct Params;
+
+constexpr int kRowCtaFixedSmem = 2304;   // scalars, scan totals and the two exchange boxes ahead of the candidate lists
+
+// How a row-CTA launch lays out its dynamic shared memory.
+struct RowCtaPlan {
+    int depth;         // stages of a thread's copy pipeline (each one stripe of logits, plus one of penalties beside it)
+    int cached;        // leading stripes that stay on chip as scaled logits between the two passes
+    int cap;           // candidate entries per virtual lane
+    int stage_bytes;
+    int off_cand, off_ring, off_cache;
+    int smem_bytes;
+};
+
+RowCtaPlan rowcta_plan(int V, bool with_penalties, int sel_rank, int smem_budget);
+// lanes_per_thread: 2 (512 threads per row; batches that leave an SM to one row) or 4 (256 threads; two rows per SM)
+int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin);
+
+}  // namespace rs

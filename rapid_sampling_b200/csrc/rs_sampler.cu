@@ -21,7 +21,8 @@
 //
 // No tensor cores: nothing here is a contraction.  The bound is HBM bandwidth (4 bytes per
 // logit, 12 with penalties) for large batches and launch + barrier latency for tiny ones.
-#include "rs_device.cuh"
+#include "rs_common.cuh"
+#include "rs_rowcta.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "../../include/rapid_sampling_b200.h"
@@ -33,151 +34,6 @@
 #include <mutex>
 
 namespace rs {
-
-enum Kind : int { kTopP = 0, kGeneral = 1, kRepetition = 2 };
-
-struct Params {
-    const void* logits;      // already offset to position T-1 of row 0; fp32, fp16 or bf16 (dtype)
-    int dtype;               // RS_DTYPE_F32 / F16 / BF16 of the logits
-    long long row_stride;    // elements between consecutive rows (T*V)
-    float* penalties;        // (B,V) or null
-    unsigned char* states;   // B*64
-    int* out;                // B
-    float* scratch;          // B*V floats (global-row variant only)
-    float* dbg_probs;        // optional (B,V)
-    rs_trace* dbg_trace;     // optional B
-    int* status;             // device status word
-    int* status_mirror;      // optional: a word of pinned host memory the device can write (zero-copy), or null
-    uint32_t wait_polls;     // polls after which a bounded wait gives up
-    int B, V, kind, top_k;
-    int sel_rank;            // 0 = no candidate shortcut; else rank of the per-warp thread maximum used as bound
-    int cand_slots;          // float4 slots per lane of the candidate buffer (shared-memory variant)
-    float scale, top_p, presence, repetition, decay;
-    const struct RowArgs* rows;   // per-row parameters (ROWP kernels only), else null
-    float* out_prob;         // optional B: probability of the sampled id (ROWP kernels only)
-    float* out_kept;         // optional B: kept probability mass the id was drawn from (ROWP kernels only)
-};
-
-// Normalised parameters of one row, made on the device from the caller's per-row tensors.
-struct __align__(32) RowArgs {
-    int kind, top_k, sel_rank, pad0;
-    float scale, top_p, pad1, pad2;
-};
-
-// shared-memory map (bytes)
-constexpr int kXWords = 10;                      // words each warp contributes to an exchange
-template <int N> struct Packets { static constexpr int value = N; };   // 16-byte packets of an exchange record
-constexpr int kXStride = 12;                     // words between two warps' records in a mailbox (16-byte aligned records)
-constexpr int kMboxOff = 0;                      // 2 buffers of [32 warps][kXStride] words
-constexpr int kMboxBuf = kXStride * 32 * 4;
-constexpr int kMiscOff = 2 * kMboxBuf;           // mbarriers, small scalars, 32 warp totals
-constexpr int kSlabOff = kMiscOff + 256;
-constexpr uint32_t kDefaultWaitPolls = 1u << 22;
-
-__host__ __device__ constexpr int slab_bytes(int V, int C) { return ((V / 4 + 1023) / 1024) * (1024 / C) * 16; }
-
-template <int C, bool SMEM>
-struct Row {
-    static constexpr int L = kLanes / C;
-    float4* slab;
-    int t, tg;
-    __device__ __forceinline__ float4 ld(int s) const { return SMEM ? slab[s * L + t] : slab[s * kLanes + tg]; }
-    __device__ __forceinline__ void st(int s, float4 v) const {
-        if (SMEM) slab[s * L + t] = v; else slab[s * kLanes + tg] = v;
-    }
-};
-
-// Probability of one element, exactly as the streaming passes compute it.
-__device__ __forceinline__ float scaled_logit(float l, float pen, bool rep, float scale) {
-    return rep ? sanitize((sanitize(l) - pen) * scale) : sanitize(l * scale);
-}
-
-// One search pass over this lane's list in the slab: ordered masses and counts at three pivots
-// (f[3] is ignored here); optionally keeps only elements >= keepf (in place, order preserved, tail
-// padded with -1).  Counts are returned packed: c01 = n(f0) | n(f1) << 16, c23 = n(f2).
-template <int C, bool SMEM, bool COMPACT>
-__device__ __forceinline__ void slab_pass(const Row<C, SMEM>& row, int& n, const float (&f)[4], float keepf, float (&m)[4],
-                                          uint32_t& c01, uint32_t& c23) {
-    uint32_t cy = 0, cz = 0, cw = 0;
-    float my = 0.f, mz = 0.f, mw = 0.f;
-    const float py = f[0], pz = f[1], pw = f[2];
-    const int slots = (n + 3) >> 2;
-    float b0 = -1.f, b1 = -1.f, b2 = -1.f, b3 = -1.f;
-    int q = 0;
-#pragma unroll 2
-    for (int s = 0; s < slots; s++) {
-        const float4 v = row.ld(s);
-        const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float p = e[j];
-            if (p >= py) { cy++; my += p; }
-            if (p >= pz) { cz++; mz += p; }
-            if (p >= pw) { cw++; mw += p; }
-            if (COMPACT) {
-                if (p >= keepf) {
-                    const int k = q & 3;
-                    b0 = (k == 0) ? p : b0;
-                    b1 = (k == 1) ? p : b1;
-                    b2 = (k == 2) ? p : b2;
-                    b3 = (k == 3) ? p : b3;
-                    q++;
-                    if ((q & 3) == 0) {
-                        row.st((q >> 2) - 1, make_float4(b0, b1, b2, b3));
-                        b0 = b1 = b2 = b3 = -1.f;
-                    }
-                }
-            }
-        }
-    }
-    if (COMPACT) {
-        if (q & 3) row.st(q >> 2, make_float4(b0, b1, b2, b3));
-        n = q;
-    }
-    m[0] = my; m[1] = mz; m[2] = mw; m[3] = 0.f;
-    c01 = cy | (cz << 16);
-    c23 = cw;
-}
-
-// Sanitised scaled logit with the common case (finite product) kept to a multiply and a compare.
-__device__ __forceinline__ float scaled_fast(float l, float scale) {
-    const float x = l * scale;
-    return (fabsf(x) <= FLT_MAX) ? x : sanitize(x);
-}
-// The rare path, kept out of line so that the streaming loops stay short.
-__device__ __forceinline__ float4 sanitize4(float4 v) {
-    return make_float4(sanitize(v.x), sanitize(v.y), sanitize(v.z), sanitize(v.w));
-}
-// Four scaled logits; a single test per group finds any Inf / NaN product (x * 0 is NaN exactly for those).
-__device__ __forceinline__ float4 scaled4(float4 l, float scale) {
-    float4 v = make_float4(l.x * scale, l.y * scale, l.z * scale, l.w * scale);
-    const float probe = fmaf(v.w, 0.f, fmaf(v.z, 0.f, fmaf(v.y, 0.f, v.x * 0.f)));
-    if (probe != probe) v = sanitize4(v);
-    return v;
-}
-// Four penalised scaled logits, sanitize((sanitize(l) - pen) * scale).  If the plain product is finite, the logit
-// was finite too (an Inf / NaN logit keeps the product non-finite for any finite or non-finite penalty), both
-// sanitisers were identities and the product is the result; anything else takes the exact formula.
-__device__ __forceinline__ float4 scaled4_rep(float4 l, float4 q, float scale) {
-    float4 v = make_float4((l.x - q.x) * scale, (l.y - q.y) * scale, (l.z - q.z) * scale, (l.w - q.w) * scale);
-    const float probe = fmaf(v.w, 0.f, fmaf(v.z, 0.f, fmaf(v.y, 0.f, v.x * 0.f)));
-    if (probe != probe)
-        v = make_float4(scaled_logit(l.x, q.x, true, scale), scaled_logit(l.y, q.y, true, scale),
-                        scaled_logit(l.z, q.z, true, scale), scaled_logit(l.w, q.w, true, scale));
-    return v;
-}
-// Appends the candidates of one float4 group to the lane's list (rare; out of line).
-__device__ __forceinline__ void append_candidates(float4 v, float beta_e, float* list, int stride4, int cap, int& nc, int& ns) {
-    const float e[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-    for (int j = 0; j < 4; j++) {
-        if (e[j] >= beta_e) {
-            if (nc < cap) list[(nc >> 2) * stride4 + (nc & 3)] = e[j];
-            nc++;
-            ns += (e[j] > beta_e) ? 1 : 0;
-        }
-    }
-}
 
 // CTAs of one variant that the register file of an SM holds (64K registers): the streaming variant is compiled
 // for 64 registers per thread, the on-chip variants for up to 128.  The launch planner counts resident rows with it.
@@ -1071,6 +927,7 @@ static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_cluster_override{0};
 static std::atomic<int> g_path_override{0};
 static std::atomic<uint32_t> g_wait_polls{kDefaultWaitPolls};
+constexpr long long kRowCtaMinBatch = 149;   // more rows than SMs: one CTA per row, two rows per SM; below, the cluster variants fill the GPU better
 static thread_local char g_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -1173,6 +1030,7 @@ static int smem_need(int V, int C, int cand_slots) { return kSlabOff + cand_slot
 struct Plan {
     int C;
     bool smem;
+    bool rowcta;       // one CTA per row with several virtual lanes per thread (rs_rowcta.cu): large batches
     int sel_rank, cand_slots;
     size_t ws;
 };
@@ -1180,6 +1038,7 @@ static size_t ws_bytes(long long B, long long V) { return 256 + (size_t)B * (siz
 
 static Plan make_plan(const DeviceInfo& di, long long B, int V, int sel_rank, int cand_slots, size_t ws_avail) {
     Plan pl;
+    pl.rowcta = false;
     pl.sel_rank = sel_rank;
     pl.cand_slots = cand_slots;
     auto fits = [&](int C) { return smem_need(V, C, cand_slots) <= di.smem_optin; };
@@ -1227,7 +1086,17 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     if (rc) return rc;
     int sel_rank = 0, cand_slots = 0;
     choose_candidates(V, top_k, top_p, &sel_rank, &cand_slots);
-    const Plan pl = make_plan(*di, B, (int)V, sel_rank, cand_slots, workspace_bytes);
+    Plan pl = make_plan(*di, B, (int)V, sel_rank, cand_slots, workspace_bytes);
+    // Large fp32 batches: one CTA per row, several rows per SM.  Needs the scratch rows for its whole-row fallback.
+    {
+        const int mode = g_path_override.load();
+        const bool eligible = dtype == RS_DTYPE_F32 && workspace_bytes >= ws_bytes(B, V);
+        const bool wanted = (mode == 4) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        if (eligible && wanted) {
+            pl.rowcta = true;
+            pl.ws = ws_bytes(B, V);
+        }
+    }
     if (workspace_bytes < pl.ws) return RS_ERR_WORKSPACE;
     const bool use_smem = pl.smem;
     const int C = pl.C;
@@ -1262,6 +1131,15 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     p.cand_slots = cand_slots;
 
     cudaStream_t st = (cudaStream_t)stream;
+    if (pl.rowcta) {
+        // up to 148 rows: one CTA per SM with all of its shared memory; more: two CTAs share an SM
+        const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
+        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, budget);
+        rc = rowcta_launch(p, rp, (B <= di->sms) ? 2 : 4, st, di->smem_optin);
+        if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
+        else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta)");
+        return rc;
+    }
     if (!use_smem) return launch_one<8, false>(p, kSlabOff + cand_slots * (kLanes / 8) * 16, st, *di);
     const int smem = smem_need((int)V, C, cand_slots);
     switch (C) {
@@ -1590,7 +1468,7 @@ int rs_set_cluster_override(int cluster_ctas) {
 }
 
 int rs_set_path_override(int mode) {
-    return (mode >= 0 && mode <= 3) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
+    return (mode >= 0 && mode <= 4) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
 }
 
 uint64_t rs_kernel_launch_count(void) { return rs::g_launches.load(); }

@@ -69,7 +69,8 @@ class Abi:
         return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
 
     def workspace(self, B, V):
-        n = self.L.rs_workspace_bytes(B, V)
+        # always room for the scratch rows, so that every kernel variant can be forced (rs_set_path_override)
+        n = max(self.L.rs_workspace_bytes(B, V), 256 + 4 * B * V)
         dev = self.torch.cuda.current_device()
         w = self._ws.get(dev)
         if w is None or w.numel() < n:
@@ -84,7 +85,7 @@ class Abi:
         return st
 
     def sample(self, logits, states, temperature, top_k, top_p, penalties=None, presence=0.0, repetition=0.0,
-               decay=0.0, debug=False, check=True):
+               decay=0.0, debug=False, check=True, want_probs=True):
         torch = self.torch
         B, T, V = shape_of(logits, penalties)
         out = torch.empty(max(B, 0), dtype=torch.int32, device="cuda")
@@ -98,11 +99,11 @@ class Abi:
             assert rc == 0, self.abi.status_string(rc)
             return out
         if debug:
-            probs = torch.empty(B, V, dtype=torch.float32, device="cuda")
+            probs = torch.empty(B, V, dtype=torch.float32, device="cuda") if want_probs else None
             trace = torch.zeros(B * C.sizeof(self.abi.Trace), dtype=torch.uint8, device="cuda")
             rc = self.L.rs_sample_debug(logits.data_ptr(), B, T, V, pen, states.data_ptr(), out.data_ptr(), temperature,
                                         top_k, top_p, presence, repetition, decay, ws.data_ptr(), ws.numel(),
-                                        self.stream(), probs.data_ptr(), trace.data_ptr())
+                                        self.stream(), probs.data_ptr() if want_probs else None, trace.data_ptr())
         else:
             rc = self.L.rs_sample(logits.data_ptr(), B, T, V, pen, states.data_ptr(), out.data_ptr(), temperature, top_k,
                                   top_p, presence, repetition, decay, ws.data_ptr(), ws.numel(), self.stream())

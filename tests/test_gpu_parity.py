@@ -66,7 +66,7 @@ def test_ids_and_states_bit_identical_to_reference_kernel(abi, ref, kind, B, V, 
     abi.set_cluster(0)
     lg = make_logits(kind, B, V, seed, torch).cuda()
     try:
-        for mode in (0, 1, 2, 3):                  # automatic / whole-row search only / streaming / on-chip
+        for mode in (0, 1, 2, 3, 4):               # automatic / whole-row search only / streaming / on-chip / one CTA per row
             abi.set_path(mode)
             s_ref, s_our = ref.setup_rand(seed, B), abi.setup_rand(seed, B)
             for call in range(3):                  # consecutive calls advance the states
