@@ -18,6 +18,7 @@
 #include "rs_rowcta.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace rs {
 
@@ -25,9 +26,11 @@ namespace {
 
 // shared-memory map (bytes)
 constexpr int kOffScal = 0;        // s_idxt, s_token
-constexpr int kOffWtot = 64;       // 32 warp totals of a scan
-constexpr int kOffBoxC = 192;      // 2 x [16 physical warps][8 words]
-constexpr int kOffBox = 1216;      // 2 x [4 values][32 virtual warps] floats, value-major
+constexpr int kOffCmd = 16;        // the search leader's command to the evaluating warps: 4 pivots, lo, hi, count at lo, go
+constexpr int kOffFin = 48;        // the search's final state, published by the leader
+constexpr int kOffWtot = 128;      // 32 warp totals of a scan
+constexpr int kOffBoxC = 256;      // 2 x [16 physical warps][8 words]
+constexpr int kOffBox = 1280;      // 2 x [4 values][32 virtual warps] floats, value-major
 constexpr int kBoxBytes = 4 * 32 * 4;
 static_assert(kOffBox + 2 * kBoxBytes <= kRowCtaFixedSmem, "fixed shared-memory area too small");
 constexpr int kStripeBytes = 16384;   // 1024 float4 groups: one group per virtual lane
@@ -69,7 +72,12 @@ __device__ __forceinline__ void tree_levels(float* m, const int lane) {
 
 }  // namespace
 
-template <int LPT>
+// LPT: virtual lanes per thread.  REP: the call has penalties (sampling.cu:172-438), else not (:517-964).  D: stages of
+// a thread's copy pipeline.  All three are compile-time so that the streaming loops carry no tests on them.
+struct TagFull { static constexpr bool value = true; };
+struct TagRagged { static constexpr bool value = false; };
+
+template <int LPT, bool REP, int D>
 __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kernel(const Params p, const RowCtaPlan pl) {
     constexpr int NT = kLanes / LPT;   // threads; thread t plays virtual lanes j * NT + t
     constexpr int WPB = NT / 32;       // warps; physical warp pw plays virtual warps j * WPB + pw
@@ -83,11 +91,11 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     const int K = (V4 + kLanes - 1) >> 10;   // stripes of 1024 float4 groups
     const int a_kind = p.kind, a_top_k = p.top_k, a_sel_rank = p.sel_rank;
     const float a_scale = p.scale, a_top_p = p.top_p;
-    const bool rep = (a_kind == kRepetition);
+    constexpr bool rep = REP;
     const bool use_cnt = (a_kind != kTopP);
     const float* lrow = reinterpret_cast<const float*>(p.logits) + (long long)b * p.row_stride;
     float* prow = rep ? p.penalties + (long long)b * V : nullptr;
-    const int D = pl.depth, NC = pl.cached, cap = pl.cap;
+    const int NC = pl.cached, cap = pl.cap;
 
     int* s_idxt = reinterpret_cast<int*>(smem + kOffScal);
     int* s_token = reinterpret_cast<int*>(smem + kOffScal + 4);
@@ -106,26 +114,36 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     // A thread only ever copies, reads and overwrites its own 16-byte slots, so nothing but its own wait_group orders
     // anything.  Passes alternate their direction over the stripes (down, up, down): what one pass read last is what
     // the next one reads first, so a batch larger than L2 still finds the recent part of its rows there.
-    const int Kf = V4 >> 10, rem = V4 & 1023;       // full stripes; float4 groups in the ragged last one
+    const int Kf = V4 >> 10, rem = V4 & 1023;       // full stripes; float4 groups in the ragged last one (index Kf)
     bool tail_ok[LPT];
 #pragma unroll
     for (int j = 0; j < LPT; j++) tail_ok[j] = (j * NT + t) < rem;
+    constexpr uint32_t kStage = REP ? 2 * kStripeBytes : kStripeBytes;
     const uint32_t sm_ring = smem_addr(ring) + (uint32_t)t * 16u, sm_cache = smem_addr(cache) + (uint32_t)t * 16u;
     const float4* const gl = reinterpret_cast<const float4*>(lrow) + t;
     const float4* const gp = reinterpret_cast<const float4*>(prow) + t;
     int ik = 0, islot = 0, idir = 1;   // next stripe to request, its stage, and the direction of the pass
-    auto request = [&](const bool with_logits, const bool with_pen) {
-        if (ik >= 0 && ik < K) {
-            const uint32_t st = sm_ring + (uint32_t)islot * (uint32_t)pl.stage_bytes;
+    // LG / PN: the pass wants the stripe's logits / penalties
+    auto request = [&](auto lg_tag, auto pn_tag) {
+        constexpr bool LG = decltype(lg_tag)::value, PN = decltype(pn_tag)::value;
+        if ((unsigned)ik < (unsigned)K) {
+            const uint32_t st = sm_ring + (uint32_t)islot * kStage;
             const uint32_t ldst = (ik < NC) ? sm_cache + (uint32_t)ik * kStripeBytes : st;
             const float4* src = gl + (size_t)ik * kLanes;
             const float4* psrc = gp + (size_t)ik * kLanes;
-            const bool fullk = ik < Kf;
+            if (__builtin_expect(ik < Kf, 1)) {
 #pragma unroll
-            for (int j = 0; j < LPT; j++) {
-                if (fullk || tail_ok[j]) {
-                    if (with_logits) cp_async16(ldst + j * NT * 16, src + j * NT);
-                    if (with_pen) cp_async16(st + kStripeBytes + j * NT * 16, psrc + j * NT);
+                for (int j = 0; j < LPT; j++) {
+                    if (LG) cp_async16(ldst + j * NT * 16, src + j * NT);
+                    if (PN) cp_async16(st + kStripeBytes + j * NT * 16, psrc + j * NT);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < LPT; j++) {
+                    if (tail_ok[j]) {
+                        if (LG) cp_async16(ldst + j * NT * 16, src + j * NT);
+                        if (PN) cp_async16(st + kStripeBytes + j * NT * 16, psrc + j * NT);
+                    }
                 }
             }
         }
@@ -134,17 +152,19 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         islot = (islot + 1 == D) ? 0 : islot + 1;
     };
     auto wait_stage = [&]() {   // the oldest requested stage has landed
-        if (D == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
-        else if (D == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
-        else asm volatile("cp.async.wait_group 3;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(D - 1) : "memory");
     };
-    auto begin_pass = [&](const int first, const int dir, const bool with_logits, const bool with_pen) {
+    auto begin_pass = [&](const int first, const int dir, auto lg_tag, auto pn_tag) {
         ik = first;
         idir = dir;
         islot = 0;
-        for (int i = 0; i < D - 1; i++) request(with_logits, with_pen);
+#pragma unroll
+        for (int i = 0; i < D - 1; i++) request(lg_tag, pn_tag);
     };
-    begin_pass(K - 1, -1, true, rep);
+    using Yes = TagFull;
+    using No = TagRagged;
+    using Pen = std::conditional_t<REP, TagFull, TagRagged>;
+    begin_pass(K - 1, -1, Yes(), Pen());
 
     // exchange of warp values inside the CTA: two alternating boxes, one barrier per exchange
     int phase = 0;
@@ -189,29 +209,31 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     for (int j = 0; j < LPT; j++) tmax[j] = -INFINITY;
     {
         int cslot = 0;
-        for (int k = K - 1; k >= 0; k--) {
-            request(true, rep);
+        auto stripe = [&](auto full_tag, const int k) {
+            constexpr bool FULLK = decltype(full_tag)::value;
+            request(Yes(), Pen());
             wait_stage();
-            const unsigned char* st = ring + (size_t)cslot * pl.stage_bytes;
+            const unsigned char* st = ring + (size_t)cslot * kStage;
             const bool keep = (k < NC);
             unsigned char* own = cache + (size_t)k * kStripeBytes;
             const unsigned char* src = keep ? own : st;
-            const bool fullk = k < Kf;
 #pragma unroll
             for (int j = 0; j < LPT; j++) {
                 const int l = j * NT + t;
-                if (fullk || tail_ok[j]) {
+                if (FULLK || tail_ok[j]) {
                     float4 v = reinterpret_cast<const float4*>(src)[l];
-                    if (rep) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
+                    if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
                     else v = scaled4(v, a_scale);
                     tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
                     if (keep) reinterpret_cast<float4*>(own)[l] = v;
                 }
             }
             cslot = (cslot + 1 == D) ? 0 : cslot + 1;
-        }
+        };
+        if (rem) stripe(TagRagged(), Kf);
+        for (int k = Kf - 1; k >= 0; k--) stripe(TagFull(), k);
     }
-    begin_pass(NC, 1, true, rep);   // the second pass's first stripes travel while the maxima are reduced
+    begin_pass(NC, 1, Yes(), Pen());   // the second pass's first stripes travel while the maxima are reduced
     stamp(1);
     stamp(2);
     // row maximum, and per virtual warp its sel_rank-th largest lane maximum: at least sel_rank elements of that
@@ -280,29 +302,31 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
 #pragma unroll
         for (int j = 0; j < LPT; j++) { acc[j] = 0.f; nc[j] = 0; }
         int cslot = 0;
-        for (int k = 0; k < K; k++) {
+        auto stripe = [&](auto full_tag, const int k) {
+            constexpr bool FULLK = decltype(full_tag)::value;
             const bool kept = (k < NC);
-            const unsigned char* st = ring + (size_t)cslot * pl.stage_bytes;
+            const unsigned char* st = ring + (size_t)cslot * kStage;
             if (!kept) {
-                request(true, rep);
+                request(Yes(), Pen());
                 wait_stage();
                 cslot = (cslot + 1 == D) ? 0 : cslot + 1;
             }
             const unsigned char* src = kept ? cache + (size_t)k * kStripeBytes : st;
-            const bool fullk = k < Kf;
 #pragma unroll
             for (int j = 0; j < LPT; j++) {
                 const int l = j * NT + t;
-                if (fullk || tail_ok[j]) {
+                if (FULLK || tail_ok[j]) {
                     float4 v = reinterpret_cast<const float4*>(src)[l];
                     if (!kept) {
-                        if (rep) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
+                        if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
                         else v = scaled4(v, a_scale);
                     }
                     pass2_group(j, v);
                 }
             }
-        }
+        };
+        for (int k = 0; k < Kf; k++) stripe(TagFull(), k);
+        if (rem) stripe(TagRagged(), Kf);
         stamp(4);
         float* box = box_of(phase);
         uint32_t* boxc = boxc_of(phase);
@@ -348,9 +372,9 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         } else {
             beta_e *= 0.0625f;
         }
-        begin_pass(NC, 1, true, rep);   // the same pass again with the lowered bound
+        begin_pass(NC, 1, Yes(), Pen());   // the same pass again with the lowered bound
     }
-    if (rep) begin_pass(K - 1, -1, false, true);   // the update pass's first penalty stripes, in flight from here on
+    if (REP) begin_pass(K - 1, -1, No(), Yes());   // the update pass's first penalty stripes, in flight from here on
     const float pmin = emin / denom, pmax = emax / denom;   // division is monotone
     if (p.dbg_probs) {   // test instrumentation: the probabilities of the whole row
         float* dprow = p.dbg_probs + (long long)b * V;
@@ -373,8 +397,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     // warp values added in warp order, as thread 0 of the reference does (sampling.cu:34-42): lanes 0..3 of every
     // warp run the four 32-step chains on vector loads, lanes 4..9 add up the counts and bounds, and the ten results
     // reach the other lanes by shuffles.
-    auto totals = [&](float (&m)[NV], const uint32_t (&c)[4], uint32_t mn, uint32_t mxv, uint32_t (&cnt)[4], float (&mass)[4],
-                      uint32_t& vmin, uint32_t& vmax) {
+    auto publish_partials = [&](float (&m)[NV], const uint32_t (&c)[4], uint32_t mn, uint32_t mxv) {
         tree_levels<NV, 16>(m, lane);
         // value index i = j * 4 + pivot ended in the lanes whose upper bits spell i
         constexpr int SH = (NV == 32) ? 0 : (NV == 16) ? 1 : (NV == 8) ? 2 : 3;
@@ -393,7 +416,10 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
             *reinterpret_cast<uint4*>(boxc + pw * 8) = make_uint4(cs[0], cs[1], cs[2], cs[3]);
             *reinterpret_cast<uint2*>(boxc + pw * 8 + 4) = make_uint2(mn, mxv);
         }
-        __syncthreads();
+    };
+    auto combine_partials = [&](uint32_t (&cnt)[4], float (&mass)[4], uint32_t& vmin, uint32_t& vmax) {
+        const float* box = box_of(phase);
+        const uint32_t* boxc = boxc_of(phase);
         uint32_t r = 0u;
         if (lane < 4) {
             const float4* col = reinterpret_cast<const float4*>(box + lane * 32);
@@ -422,6 +448,12 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         }
         vmin = __shfl_sync(FULL, r, 8);
         vmax = __shfl_sync(FULL, r, 9);
+    };
+    auto totals = [&](float (&m)[NV], const uint32_t (&c)[4], uint32_t mn, uint32_t mxv, uint32_t (&cnt)[4], float (&mass)[4],
+                      uint32_t& vmin, uint32_t& vmax) {
+        publish_partials(m, c, mn, mxv);
+        __syncthreads();
+        combine_partials(cnt, mass, vmin, vmax);
         phase ^= 1;
     };
 
@@ -433,76 +465,130 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     uint32_t path = 1;
     uint32_t conv_cnt = 0, conv_left_cnt = 0;
     float conv_mass = 0.f;
+    // Warp 0 leads: it alone replays the reference's loop -- pivots, tests, bracket updates, the rounds that need no
+    // data -- and, when a round needs sums, publishes its four pivots; every warp then evaluates its own lanes, reduces
+    // them and stores the warp values, and only the leader adds them up.  Two named barriers per evaluated round:
+    // "partials stored" (the others only arrive) and "next command published".
+    //  * clamp (candidate list only): every probability above beta_p is on the list, so a pivot above beta_p sees exactly
+    //    the elements the reference sees.  A pivot u <= beta_p is not evaluated; instead the set {p > beta_p} is: if it
+    //    already holds more than top_k elements or more than top_p mass, so does the larger set {p >= u}, the reference's
+    //    test at u fails and its carried state keeps the loop going -- all it uses these values for.  Otherwise: not valid.
+    //  * frozen (candidate list only): once every element strictly inside (left, right) has one and the same value v, the
+    //    remaining rounds need no data: a pivot equal to `left` selects the set of `left`, a pivot in (left, v] the set
+    //    {p >= v}, a pivot above v the set of `right`.
+    volatile uint32_t* s_cmd = reinterpret_cast<volatile uint32_t*>(smem + kOffCmd);
+    volatile uint32_t* s_fin = reinterpret_cast<volatile uint32_t*>(smem + kOffFin);
     auto run_search = [&](auto&& lane_eval, const bool clamp, const uint32_t beta_p, const bool sure_cnt,
                           const uint32_t n_above) -> bool {
         const uint32_t ustar = clamp ? beta_p + 1u : 0u;
-        left = __float_as_uint(pmin);
-        right = __float_as_uint(pmax) + 1u;
-        rounds = 0;
+        // leader state
+        uint32_t l_left = __float_as_uint(pmin), l_right = __float_as_uint(pmax) + 1u, l_rounds = 0, l_evals = 0;
         uint32_t cnt_x = (uint32_t)V, cnt_r = 0u;
         float mass_x = 1.0f, mass_r = 0.f;
-        bool frozen = false, valid = true;
+        bool frozen = false, valid = true, have_vals = false, waiting = false;
         uint32_t v_bits = 0, cnt_v = 0;
         float mass_v = 0.f;
-        while (rounds < 64u) {
-            const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
-            if (!(go && left < right - 1u)) break;
-            rounds++;
-            const uint32_t pz = (left + right) >> 1, py = (left + pz) >> 1, pwv = (pz + right) >> 1;
-            const uint32_t pv[3] = {py, pz, pwv};
-            uint32_t cnt[4];
-            float mass[4];
-            if (clamp && sure_cnt && pwv <= beta_p) {
-                left = pwv;
-                cnt_x = n_above;
-                mass_x = 0.f;
-                continue;
+        uint32_t pv[3] = {0u, 0u, 0u};
+        uint32_t cnt[4] = {0u, 0u, 0u, 0u};
+        float mass[4] = {0.f, 0.f, 0.f, 0.f};
+        for (;;) {
+            if (pw == 0) {
+                bool finished = false;
+                if (waiting) {    // the sums of the round that was asked for
+                    uint32_t vmin, vmax;
+                    combine_partials(cnt, mass, vmin, vmax);
+                    if (clamp && l_left >= beta_p && vmin >= vmax) {   // one distinct value inside (none: vmin > vmax)
+                        frozen = true;
+                        v_bits = (vmin == vmax) ? vmin : l_left;
+                        cnt_v = cnt[3];      // the set {p >= left + 1} is {p >= v}
+                        mass_v = mass[3];
+                    }
+                    have_vals = true;
+                    waiting = false;
+                }
+                for (;;) {
+                    if (have_vals) {   // the three tests and the bracket update (sampling.cu:618-651)
+                        have_vals = false;
+                        bool ok[3], bad = false;
+#pragma unroll
+                        for (int i = 0; i < 3; i++) {
+                            const bool below = clamp && pv[i] <= beta_p;
+                            const bool exceeds = (use_cnt && cnt[i] > top_k) || mass[i] > top_p;
+                            const bool pass = (!use_cnt || cnt[i] < top_k) && mass[i] < top_p;
+                            ok[i] = !below && pass;
+                            bad = bad || (below && !exceeds);
+                        }
+                        if (bad) { valid = false; finished = true; break; }
+                        const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
+                        const uint32_t nl = s0 ? l_left : s1 ? pv[0] : s2 ? pv[1] : pv[2];
+                        const uint32_t nr = s0 ? pv[0] : s1 ? pv[1] : s2 ? pv[2] : l_right;
+                        const uint32_t ncx = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
+                        const float nmx = s0 ? mass_x : s1 ? mass[0] : s2 ? mass[1] : mass[2];
+                        const uint32_t ncr = s0 ? cnt[0] : s1 ? cnt[1] : s2 ? cnt[2] : cnt_r;
+                        const float nmr = s0 ? mass[0] : s1 ? mass[1] : s2 ? mass[2] : mass_r;
+                        l_left = nl; l_right = nr; cnt_x = ncx; mass_x = nmx; cnt_r = ncr; mass_r = nmr;
+                    }
+                    const bool go = use_cnt ? (cnt_x > top_k || mass_x > top_p) : (mass_x > top_p);
+                    if (!(go && l_left < l_right - 1u) || l_rounds >= 64u) { finished = true; break; }
+                    l_rounds++;
+                    const uint32_t pz = (l_left + l_right) >> 1, py = (l_left + pz) >> 1, pwv = (pz + l_right) >> 1;
+                    pv[0] = py; pv[1] = pz; pv[2] = pwv;
+                    if (clamp && sure_cnt && pwv <= beta_p) {
+                        // all three pivots lie at or below the bound, and more than top_k elements are known to lie
+                        // strictly above it: every test fails, the lower end moves to the last pivot, no data is needed
+                        l_left = pwv;
+                        cnt_x = n_above;
+                        mass_x = 0.f;
+                        continue;
+                    }
+                    if (frozen) {
+#pragma unroll
+                        for (int i = 0; i < 3; i++) {
+                            const bool at_left = (pv[i] == l_left), le_v = (pv[i] <= v_bits);
+                            cnt[i] = at_left ? cnt_x : le_v ? cnt_v : cnt_r;
+                            mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
+                        }
+                        have_vals = true;
+                        continue;
+                    }
+                    l_evals++;
+                    waiting = true;
+                    break;
+                }
+                if (lane == 0) {
+                    if (waiting) {
+                        s_cmd[0] = max(pv[0], ustar); s_cmd[1] = max(pv[1], ustar); s_cmd[2] = max(pv[2], ustar);
+                        s_cmd[3] = max(l_left + 1u, ustar);
+                        s_cmd[4] = l_left; s_cmd[5] = l_right; s_cmd[6] = cnt_x; s_cmd[7] = 1u;
+                    } else {
+                        s_cmd[7] = 0u;
+                        s_fin[0] = l_left; s_fin[1] = l_right; s_fin[2] = l_rounds; s_fin[3] = l_evals;
+                        s_fin[4] = cnt_r; s_fin[5] = cnt_x; s_fin[6] = __float_as_uint(mass_r); s_fin[7] = valid ? 1u : 0u;
+                    }
+                }
+                (void)finished;
             }
-            if (!frozen) {
-                n_eval++;
-                const float f[4] = {__uint_as_float(max(py, ustar)), __uint_as_float(max(pz, ustar)),
-                                    __uint_as_float(max(pwv, ustar)), __uint_as_float(max(left + 1u, ustar))};
+            asm volatile("bar.sync 2, %0;" ::"n"(NT) : "memory");      // command published
+            if (s_cmd[7] == 0u) break;
+            {
+                const float f[4] = {__uint_as_float(s_cmd[0]), __uint_as_float(s_cmd[1]), __uint_as_float(s_cmd[2]),
+                                    __uint_as_float(s_cmd[3])};
+                const uint32_t lo = s_cmd[4], hi = s_cmd[5], cnt_lo = s_cmd[6];
                 float m[NV];
-                uint32_t c[4], mn, mxv, vmin, vmax;
-                lane_eval(f, left, right, cnt_x, m, c, mn, mxv);
-                totals(m, c, mn, mxv, cnt, mass, vmin, vmax);
-                if (clamp && left >= beta_p && vmin >= vmax) {
-                    frozen = true;
-                    v_bits = (vmin == vmax) ? vmin : left;
-                    cnt_v = cnt[3];
-                    mass_v = mass[3];
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 3; i++) {
-                    const bool at_left = (pv[i] == left), le_v = (pv[i] <= v_bits);
-                    cnt[i] = at_left ? cnt_x : le_v ? cnt_v : cnt_r;
-                    mass[i] = at_left ? mass_x : le_v ? mass_v : mass_r;
-                }
+                uint32_t c[4], mn, mxv;
+                lane_eval(f, lo, hi, cnt_lo, m, c, mn, mxv);
+                publish_partials(m, c, mn, mxv);
             }
-            bool ok[3], bad = false;
-#pragma unroll
-            for (int i = 0; i < 3; i++) {
-                const bool below = clamp && pv[i] <= beta_p;
-                const bool exceeds = (use_cnt && cnt[i] > top_k) || mass[i] > top_p;
-                const bool pass = (!use_cnt || cnt[i] < top_k) && mass[i] < top_p;
-                ok[i] = !below && pass;
-                bad = bad || (below && !exceeds);
-            }
-            if (bad) { valid = false; break; }
-            const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
-            const uint32_t nl = s0 ? left : s1 ? py : s2 ? pz : pwv;
-            const uint32_t nr = s0 ? py : s1 ? pz : s2 ? pwv : right;
-            const uint32_t ncx = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
-            const float nmx = s0 ? mass_x : s1 ? mass[0] : s2 ? mass[1] : mass[2];
-            const uint32_t ncr = s0 ? cnt[0] : s1 ? cnt[1] : s2 ? cnt[2] : cnt_r;
-            const float nmr = s0 ? mass[0] : s1 ? mass[1] : s2 ? mass[2] : mass_r;
-            left = nl; right = nr; cnt_x = ncx; mass_x = nmx; cnt_r = ncr; mass_r = nmr;
+            if (pw == 0) asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");      // partials stored: the leader waits,
+            else asm volatile("bar.arrive 1, %0;" ::"n"(NT) : "memory");            // the others go on to the next command
         }
-        conv_cnt = cnt_r;
-        conv_mass = mass_r;
-        conv_left_cnt = cnt_x;
-        return valid && (!clamp || left > beta_p);
+        left = s_fin[0]; right = s_fin[1]; rounds = s_fin[2]; n_eval += s_fin[3];
+        conv_cnt = s_fin[4];
+        conv_left_cnt = s_fin[5];
+        conv_mass = __uint_as_float(s_fin[6]);
+        const bool was_valid = s_fin[7] != 0u;
+        __syncthreads();     // everybody has read the final state before anything reuses the exchange area
+        return was_valid && (!clamp || left > beta_p);
     };
 
     float gtp[LPT];          // per virtual lane: mass above the threshold, ties with it, count above
@@ -802,15 +888,15 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     // through the copy pipeline, whose first stripes have been in flight since the second pass ended -------------
     if (rep) {
         int cslot = 0;
-        for (int k = K - 1; k >= 0; k--) {
-            request(false, true);
+        auto stripe = [&](auto full_tag, const int k) {
+            constexpr bool FULLK = decltype(full_tag)::value;
+            request(No(), Yes());
             wait_stage();
-            const unsigned char* st = ring + (size_t)cslot * pl.stage_bytes;
-            const bool fullk = k < Kf;
+            const unsigned char* st = ring + (size_t)cslot * kStage;
 #pragma unroll
             for (int j = 0; j < LPT; j++) {
                 const int l = j * NT + t, i4 = k * kLanes + l;
-                if (fullk || tail_ok[j]) {
+                if (FULLK || tail_ok[j]) {
                     const float4 q4 = reinterpret_cast<const float4*>(st + kStripeBytes)[l];
                     float e[4] = {q4.x, q4.y, q4.z, q4.w};
                     if (i4 != (token >> 2)) {
@@ -827,7 +913,9 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 }
             }
             cslot = (cslot + 1 == D) ? 0 : cslot + 1;
-        }
+        };
+        if (rem) stripe(TagRagged(), Kf);
+        for (int k = Kf - 1; k >= 0; k--) stripe(TagFull(), k);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     stamp(9);
@@ -850,31 +938,31 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
 
 // ------------------------------------------------------------------------------------------------ host side
 // Shared memory of a row-CTA launch: fixed area, candidate lists (cap entries per virtual lane), copy stages, and the
-// stripes that stay on chip between the passes.
-RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int smem_budget) {
+// stripes that stay on chip between the passes.  The pipeline depth is a compile-time property of the four kernel
+// instantiations: without penalties 4 stages of 16 KiB; with penalties 3 stages of 32 KiB when a row has an SM to
+// itself (lanes_per_thread 2), 2 stages when two rows share one.
+static int rowcta_depth(bool rep, int lanes_per_thread) { return rep ? (lanes_per_thread == 2 ? 3 : 2) : 4; }
+
+RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int smem_budget) {
     RowCtaPlan pl;
     const int K = (V / 4 + kLanes - 1) / kLanes;
     pl.stage_bytes = rep ? 2 * kStripeBytes : kStripeBytes;
     pl.cap = (sel_rank > 0) ? 6 : 0;
     pl.off_cand = kRowCtaFixedSmem;
     pl.off_ring = pl.off_cand + pl.cap * kLanes * 4;
-    const int room = smem_budget - pl.off_ring;
-    // enough stages for the memory latency first (about 64 KiB in flight per CTA), then stripes kept on chip
-    int depth = rep ? 3 : 6;
-    if (depth > K + 1) depth = K + 1;
-    while (depth > 2 && depth * pl.stage_bytes > room) depth--;
-    pl.depth = depth;
-    int keep = (room - depth * pl.stage_bytes) / kStripeBytes;
+    pl.depth = rowcta_depth(rep, lanes_per_thread);
+    const int room = smem_budget - pl.off_ring - pl.depth * pl.stage_bytes;
+    int keep = room / kStripeBytes;
     if (keep > K) keep = K;
     pl.cached = keep < 0 ? 0 : keep;
-    pl.off_cache = pl.off_ring + depth * pl.stage_bytes;
+    pl.off_cache = pl.off_ring + pl.depth * pl.stage_bytes;
     pl.smem_bytes = pl.off_cache + pl.cached * kStripeBytes;
     return pl;
 }
 
-template <int LPT>
+template <int LPT, bool REP, int D>
 static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t stream, int smem_optin, bool* attr_done) {
-    auto kern = rowcta_kernel<LPT>;
+    auto kern = rowcta_kernel<LPT, REP, D>;
     if (!*attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin) != cudaSuccess) return RS_ERR_CUDA;
         *attr_done = true;
@@ -885,13 +973,17 @@ static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t s
 
 int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin) {
     static std::mutex mu;
-    static bool attr_done[64][2] = {};
+    static bool attr_done[64][4] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RS_ERR_CUDA;
-    if (pl.depth < 2 || pl.depth > 8 || pl.smem_bytes > smem_optin) return RS_ERR_LIMIT;
+    const bool rep = p.penalties != nullptr;
+    if (pl.depth != rowcta_depth(rep, lanes_per_thread) || pl.smem_bytes > smem_optin) return RS_ERR_LIMIT;
     std::lock_guard<std::mutex> lk(mu);
-    if (lanes_per_thread == 2) return rowcta_launch_t<2>(p, pl, stream, smem_optin, &attr_done[dev][0]);
-    return rowcta_launch_t<4>(p, pl, stream, smem_optin, &attr_done[dev][1]);
+    if (lanes_per_thread == 2)
+        return rep ? rowcta_launch_t<2, true, 3>(p, pl, stream, smem_optin, &attr_done[dev][0])
+                   : rowcta_launch_t<2, false, 4>(p, pl, stream, smem_optin, &attr_done[dev][1]);
+    return rep ? rowcta_launch_t<4, true, 2>(p, pl, stream, smem_optin, &attr_done[dev][2])
+               : rowcta_launch_t<4, false, 4>(p, pl, stream, smem_optin, &attr_done[dev][3]);
 }
 
 }  // namespace rs

@@ -18,7 +18,7 @@ struct RowCtaPlan {
     int smem_bytes;
 };
 
-RowCtaPlan rowcta_plan(int V, bool with_penalties, int sel_rank, int smem_budget);
+RowCtaPlan rowcta_plan(int V, bool with_penalties, int sel_rank, int lanes_per_thread, int smem_budget);
 // lanes_per_thread: 2 (512 threads per row; batches that leave an SM to one row) or 4 (256 threads; two rows per SM)
 int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin);
 

@@ -927,7 +927,7 @@ static std::atomic<uint64_t> g_launches{0};
 static std::atomic<int> g_cluster_override{0};
 static std::atomic<int> g_path_override{0};
 static std::atomic<uint32_t> g_wait_polls{kDefaultWaitPolls};
-constexpr long long kRowCtaMinBatch = 149;   // more rows than SMs: one CTA per row, two rows per SM; below, the cluster variants fill the GPU better
+constexpr long long kRowCtaMinBatch = 112;   // from here on one CTA per row (two rows per SM beyond 148 rows) beats the cluster variants
 static thread_local char g_err[256] = "";
 
 static int cuda_fail(cudaError_t e, const char* what) {
@@ -1134,8 +1134,9 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     if (pl.rowcta) {
         // up to 148 rows: one CTA per SM with all of its shared memory; more: two CTAs share an SM
         const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
-        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, budget);
-        rc = rowcta_launch(p, rp, (B <= di->sms) ? 2 : 4, st, di->smem_optin);
+        const int lpt = (B <= di->sms) ? 2 : 4;
+        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, lpt, budget);
+        rc = rowcta_launch(p, rp, lpt, st, di->smem_optin);
         if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
         else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta)");
         return rc;
