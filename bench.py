@@ -32,9 +32,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 L2_BYTES = 126 * 1000 * 1000
-# per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of sampler_kernel from the ncu
-# captures summarised under profiles/, keyed by workload; None where no capture exists.
-NCU_TRAFFIC = {"C2": 1.157e6, "C3": 39.02e6, "C4": 160.66e6}
+MIN_LATENCY_CALLS = 1000      # the headline latency is a median over at least this many calls, whatever --steps says
+MIN_E2E_STEPS = 200
+EXTRA_CALLS = 200             # calls per side for the other workloads reported beside the headline
+# Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the sampler kernel, copied from the ncu
+# capture named beside it; a workload without a capture of the current kernel has no entry.
+PROFILED_TRAFFIC = {"C2": (1.157e6, "profiles/sampler_kernel_C2_C3_C4_vector_exchange.md")}
 
 
 def workload(name):
@@ -164,6 +167,186 @@ def cpu_torch_f64(w, budget_s=6.0, max_calls=16):
     dt = time.perf_counter() - t0
     return {"rows_per_s": w["B"] * calls / dt, "ms_per_call": dt / calls * 1e3, "threads": torch.get_num_threads(),
             "cpu_count": os.cpu_count()}
+
+
+def hbm_peak():
+    """Measured HBM copy bandwidth of this pool's B200s (GB/s) when the driver's file is present, else the fallback."""
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def alg_bytes(w, esz=4):
+    """Algorithmic bytes of one call: logits of the read position once, plus fp32 penalties read and written."""
+    return ((8 if w["rep"] else 0) + esz) * w["V"] * w["B"]
+
+
+def make_pool(w, dev, torch, rank=0, min_sets=2, max_sets=256):
+    """Logits sets that together exceed L2, so that consecutive calls read their rows from HBM."""
+    row_bytes = w["B"] * w["T"] * w["V"] * 4
+    n = max(min_sets, min(max_sets, -(-int(1.6 * L2_BYTES) // row_bytes)))
+    return [gen_logits(w, w["seed"] + 1000 * i + 7 * rank, dev, torch) for i in range(n)]
+
+
+def sampler_call(ext, w, states, pen):
+    if w["rep"]:
+        return lambda lg: ext.batch_sampling_repetition_temperature_topk_topp(lg, pen, states, 0.1, 0.1, 0.95, w["temperature"],
+                                                                              w["top_k"], w["top_p"])
+    return lambda lg: ext.batch_sampling_temperature_topk_topp(lg, states, w["temperature"], w["top_k"], w["top_p"])
+
+
+def time_calls(call, pool, n, torch, warm=5):
+    """(ms per call over n back-to-back calls, median us of per-call event pairs)."""
+    for i in range(warm):
+        call(pool[i % len(pool)])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        call(pool[i % len(pool)])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    for i in range(n):
+        evs[i][0].record()
+        call(pool[i % len(pool)])
+        evs[i][1].record()
+    torch.cuda.synchronize()
+    lat = sorted(x.elapsed_time(y) * 1e3 for x, y in evs)
+    return ms, lat[len(lat) // 2]
+
+
+def reference_cuda_on(ref, w, pool, n, torch):
+    """The reference's own CUDA kernel (oracle/_ref) on the same logits; 3-D workloads give it the last position only
+    (it indexes its (B, V) scratch with the 3-D offset, sampling.cu:488 against :206)."""
+    if w["T"] != 1:
+        pool = [x[:, -1, :].contiguous() for x in pool]
+        w = dict(w, T=1)
+    pen = torch.zeros(w["B"], w["V"], device=pool[0].device) if w["rep"] else None
+    st = ref.setup_rand(w["seed"], w["B"])
+    ms, med = time_calls(sampler_call(ref, w, st, pen), pool, n, torch)
+    return {"median_us": med, "ms_per_call": ms, "rows_per_s": w["B"] / (ms * 1e-3)}
+
+
+def ids_equal_to_reference(ext, ref, w, pool, torch, calls=3):
+    """Same states, same logits: the ids of `calls` consecutive calls must be identical to the reference kernel's."""
+    from rapid_sampling_b200.sharding import setup_rand_rows
+    dev = pool[0].device
+    st_o, st_r = setup_rand_rows(w["seed"], 0, w["B"]), ref.setup_rand(w["seed"], w["B"])
+    pen_o = torch.zeros(w["B"], w["V"], device=dev) if w["rep"] else None
+    pen_r = torch.zeros(w["B"], w["V"], device=dev) if w["rep"] else None
+    co, cr = sampler_call(ext, w, st_o, pen_o), sampler_call(ref, dict(w, T=1), st_r, pen_r)
+    ok = True
+    for i in range(calls):
+        lg = pool[i % len(pool)]
+        ok = ok and bool(torch.equal(co(lg), cr(lg if w["T"] == 1 else lg[:, -1, :].contiguous())))
+    return ok and bool(torch.equal(st_o, st_r)) and (pen_o is None or bool(torch.equal(pen_o, pen_r)))
+
+
+def other_workloads(ext, ref, dev, torch, names=("C1", "C3", "C4", "C5")):
+    """The workloads that are not the headline, each timed over EXTRA_CALLS calls beside the reference's CUDA kernel
+    on the same logits (one GPU).  Reported as extra keys of the headline's line, outside its timed region."""
+    from rapid_sampling_b200.sharding import setup_rand_rows
+    peak, _ = hbm_peak()
+    out = {}
+    for name in names:
+        w = workload(name)
+        pool = make_pool(w, dev, torch, max_sets=(2 if name == "C5" else 256))
+        pen = torch.zeros(w["B"], w["V"], device=dev) if w["rep"] else None
+        st = setup_rand_rows(w["seed"], 0, w["B"])
+        ms, med = time_calls(sampler_call(ext, w, st, pen), pool, EXTRA_CALLS, torch)
+        row = {"median_us": med, "ms_per_call": ms, "rows_per_s": w["B"] / (ms * 1e-3), "calls": EXTRA_CALLS,
+               "roofline_frac": alg_bytes(w) / (ms * 1e-3) / 1e9 / peak, "algorithmic_bytes": alg_bytes(w)}
+        if ref is not None:
+            r = reference_cuda_on(ref, w, pool, EXTRA_CALLS, torch)
+            row.update(reference_cuda_median_us=r["median_us"], speedup_vs_reference_cuda=r["median_us"] / med,
+                       ids_equal=ids_equal_to_reference(ext, ref, w, pool, torch))
+        else:
+            row["reference_cuda_median_us"] = None
+        out[name] = row
+        del pool, pen
+        torch.cuda.empty_cache()
+    return out
+
+
+def multi_gpu_extras(ext, rank, world, dev, torch, dist, calls=100):
+    """What only a multi-GPU run can show, measured after the headline on every rank (rank 0 reports): C3 and C4
+    batch-sharded with the same per-GPU batch (weak) and with the batch divided over the ranks (strong), and C5
+    vocab-parallel with the ids checked to be identical on all ranks."""
+    from rapid_sampling_b200.sharding import row_range, setup_rand_rows
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+    out = {}
+    for name in ("C3", "C4"):
+        w = workload(name)
+        for mode in ("weak", "strong"):
+            if mode == "weak":
+                wl, first = w, rank * w["B"]
+            else:
+                a0, a1 = row_range(w["B"], rank, world)
+                wl, first = dict(w, B=a1 - a0), a0
+            if wl["B"] == 0:
+                continue
+            pool = make_pool(wl, dev, torch, rank=rank)
+            pen = torch.zeros(wl["B"], wl["V"], device=dev) if wl["rep"] else None
+            st = setup_rand_rows(w["seed"], first, wl["B"])
+            call = sampler_call(ext, wl, st, pen)
+            for i in range(5):
+                call(pool[i % len(pool)])
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(calls):
+                call(pool[i % len(pool)])
+            e1.record()
+            torch.cuda.synchronize()
+            ms = max_over_ranks(e0.elapsed_time(e1)) / calls
+            total_rows = w["B"] * world if mode == "weak" else w["B"]
+            out["%s_%s" % (name, mode)] = {"rows_per_gpu": wl["B"], "total_rows": total_rows, "ms_per_call": ms,
+                                           "rows_per_s": total_rows / (ms * 1e-3), "collectives_on_data_path": 0}
+            del pool, pen
+            torch.cuda.empty_cache()
+    # C5 vocab-parallel: V / world columns per rank, NCCL collectives between the stages
+    w = workload("C5")
+    B, T, V = w["B"], w["T"], w["V"]
+    s = VocabParallelSampler(B, V, rank, world, T=T)
+    pool = []
+    for i in range(2):
+        full = gen_logits(dict(w, T=1), w["seed"] + 1000 * i, dev, torch)          # the same rows on every rank (same seed)
+        shard = full[:, s.col0:s.col0 + s.V_local]
+        pool.append(shard.unsqueeze(1).expand(B, T, s.V_local).contiguous())
+        del full
+    st = setup_rand_rows(w["seed"], 0, B)
+    ids = None
+    for i in range(5):
+        ids = s.sample(pool[i % 2], st, w["temperature"], w["top_k"], w["top_p"])
+    chk = ids.to(torch.int64).sum().reshape(1)
+    lo, hi = chk.clone(), chk.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(calls):
+        s.sample(pool[i % 2], st, w["temperature"], w["top_k"], w["top_p"])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / calls
+    out["C5_vocab_parallel"] = {"columns_per_gpu": s.V_local, "ms_per_call": ms, "rows_per_s": B / (ms * 1e-3),
+                                "protocol": s.last_protocol, "ids_identical_on_all_ranks": bool(int(lo[0]) == int(hi[0])),
+                                "collectives_per_call": "2 all-reduces + 2 all-gathers (NCCL)"}
+    s.release_graphs()
+    return out
 
 
 def bench_vocab_parallel(a, w, rank, local_rank, world, dev, base, K, Wm, torch, dist):
@@ -302,6 +485,7 @@ def run_sweep(a):
                     speedup_geomean=float(np.exp(np.log(ratio).mean())), speedup_min=float(ratio.min()),
                     speedup_max=float(ratio.max()), ids_differ=mismatched)
     print(json.dumps(line))
+    return line
 
 
 def main():
@@ -312,6 +496,8 @@ def main():
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the headline workload: skip the reference-CUDA arm, the other workloads and the multi-GPU extras")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"], help="storage type of the logits (ours only)")
     ap.add_argument("--vp", action="store_true", help="vocab-parallel: every rank holds V/N columns of every row")
     ap.add_argument("--vp-graph", action="store_true", help="vocab-parallel: replay the stages from a CUDA graph per input buffer")
@@ -319,7 +505,8 @@ def main():
     ap.add_argument("--sweep-out", default="sweep_results.json")
     a = ap.parse_args()
     if a.sweep:
-        return run_sweep(a)
+        run_sweep(a)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -419,7 +606,7 @@ def main():
         total_ms = float(t[0])
 
     # ---- per-call latency (median), events around every call --------------------------------------
-    nlat = min(K, 1000)
+    nlat = max(K, MIN_LATENCY_CALLS) if a.impl == "ours" else max(min(K, MIN_LATENCY_CALLS), 200)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nlat)]
     for i in range(nlat):
         evs[i][0].record()
@@ -429,7 +616,7 @@ def main():
     lat = sorted(x.elapsed_time(y) * 1e3 for x, y in evs)
     median_us = lat[len(lat) // 2]
     # wall-clock per call with a sync, the reference bench's own method (bench.py:73-92)
-    nw = min(K, 200)
+    nw = max(min(K, 1000), 200)
     walls = []
     for i in range(nw):
         t0 = time.perf_counter()
@@ -445,7 +632,7 @@ def main():
     e2e = None
     if host_pool is not None:
         stage = torch.empty(B, V, device=dev, dtype=tdt)
-        ke = max(3, min(K, 200))
+        ke = max(min(K, 1000), MIN_E2E_STEPS)
 
         def e2e_step(i):
             stage.copy_(host_pool[i % host_n], non_blocking=True)
@@ -466,18 +653,31 @@ def main():
                "steps": ke, "ms_per_step": dt / ke * 1e3}
     clk = clocks.stop()
 
+    # ---- beside the headline, outside its timed region --------------------------------------------------
+    extras = {}
+    if a.impl == "ours" and not a.no_extras and a.dtype == "f32":
+        del host_pool
+        if world > 1:
+            extras["multi_gpu"] = multi_gpu_extras(ext, rank, world, dev, torch, dist)
+        elif rank == 0:
+            from oracle import build_ref
+            ref = build_ref.load_ref()
+            if ref is not None:
+                extras["reference_cuda"] = dict(reference_cuda_on(ref, w, pool, max(min(K, 1000), 200), torch),
+                                                what="the reference's own CUDA kernel (compiled unmodified) on the same logits pool")
+            else:
+                extras["reference_cuda"] = {"unavailable": "oracle/_ref was not built (needs the reference sources at build time)"}
+            del pool
+            torch.cuda.empty_cache()
+            extras["configs"] = other_workloads(ext, ref, dev, torch, names=[c for c in ("C1", "C2", "C3", "C4", "C5") if c != a.config])
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     ms_per_step = total_ms / K
     alg_bytes = ((8 if w["rep"] else 0) + esz) * V * B     # logits read once (+ fp32 penalties read + write)
-    peak, peak_src = 6650.0, "fallback"
-    try:
-        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
-        peak_src = "measured"
-    except Exception:
-        pass
+    peak, peak_src = hbm_peak()
     achieved = alg_bytes / (ms_per_step * 1e-3) / 1e9
     base["dtype"] = "f32" if esz == 4 else a.dtype + " logits, fp32 arithmetic"
     line = dict(base, impl=a.impl, value=world * B * K / (total_ms * 1e-3), ms_per_step=ms_per_step,
@@ -485,7 +685,10 @@ def main():
                 wall_sync_median_us=wall_median_us, clocks=clk, e2e=e2e, gpu_launches=int(gpu_launches),
                 roofline={"bound": "hbm", "kernel": "sampler_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                           "frac": achieved / peak, "peak_source": peak_src + " HBM copy bandwidth",
-                          "algorithmic_bytes_per_launch": alg_bytes, "traffic": NCU_TRAFFIC.get(a.config)})
+                          "algorithmic_bytes_per_launch": alg_bytes, "traffic": PROFILED_TRAFFIC.get(a.config, (None, None))[0],
+                          "traffic_source": PROFILED_TRAFFIC.get(a.config, (None, None))[1]})
+    line.update(extras)
+    line["latency_calls"] = nlat
     line["config"]["l2"] = "inputs rotate through a pool of %d logits sets (%.0f MB > L2)" % (pool_n, pool_n * row_bytes / 1e6)
     if a.impl == "ours" and not a.no_cpu_baseline:
         line["cpu_baseline"] = cpu_port_baseline(w)
