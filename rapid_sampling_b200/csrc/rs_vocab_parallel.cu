@@ -409,16 +409,23 @@ __device__ __forceinline__ float f_bound_e(const float* stat2, int S, int b, flo
     return 0.f;
 }
 
-// pass 2: denominator partial and the octave histogram of the large elements
+// pass 2: denominator partial and the octave histogram of the large elements.  The histogram masses are accumulated
+// as integers: an element of octave k is e = m * 2^-(k + 24) with an integer m < 2^24 (its significand), so the sum of
+// the m's of up to 2^20 elements fits 64 bits and does not depend on the order in which the atomics land -- the
+// bound every rank derives from the reduced histogram is the same in every run.
 __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits, long long row_stride, float* penalties, int n,
                                                              float scale, int S, const float* stat1, float* stat2) {
     __shared__ float sh[32];
-    __shared__ float hist[32][2 * kFBins];     // one histogram per warp: atomics only collide inside a warp
+    __shared__ unsigned long long hist_m[32][kFBins];   // one histogram per warp: atomics only collide inside a warp
+    __shared__ unsigned int hist_c[32][kFBins];
     const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x, w = t >> 5;
     const VpRow r = vp_row(logits, row_stride, penalties, n, b);
     const FSub sb = f_sub(n, S, s);
     const float gmax = f_gmax(stat1, S, b);
-    for (int i = t; i < 32 * 2 * kFBins; i += kVpThreads) (&hist[0][0])[i] = 0.f;
+    for (int i = t; i < 32 * kFBins; i += kVpThreads) {
+        (&hist_m[0][0])[i] = 0ull;
+        (&hist_c[0][0])[i] = 0u;
+    }
     __syncthreads();
     float acc = 0.f;
     for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
@@ -432,12 +439,13 @@ __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits
             // The histogram only steers the choice of the bound (the finishing kernel checks the result exactly), so
             // below the top ten octaves one group in 64 stands for its neighbours: few shared-memory atomics.
             if (d > -(float)kFBins) {
-                const bool top = d > -10.f;
-                if (top || (g & 63) == 0) {
-                    int k = (int)(-d);                 // octave: e in (2^-(k+1), 2^-k]
-                    if (e < exp2f(-(float)k) * 0.5f) k++;      // guard the octave edge against rounding of exp2f
-                    const float wgt = top ? 1.f : 64.f;
-                    if (k < kFBins) { atomicAdd(&hist[w][2 * k], e * wgt); atomicAdd(&hist[w][2 * k + 1], wgt); }
+                int k = (int)(-d);                 // octave: e in (2^-(k+1), 2^-k]
+                if (e < exp2f(-(float)k) * 0.5f) k++;      // guard the octave edge against rounding of exp2f
+                if (k < 10 || (g & 63) == 0) {
+                    if (k < kFBins) {
+                        atomicAdd(&hist_m[w][k], (unsigned long long)__float2uint_rn(ldexpf(e, k + 24)));
+                        atomicAdd(&hist_c[w][k], 1u);
+                    }
                 }
             }
         }
@@ -446,10 +454,13 @@ __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits
     __syncthreads();
     float* o = stat2 + (size_t)(b * S + s) * kFStat2;
     if (t == 0) { o[0] = d; o[1] = 0.f; }
-    if (t < 2 * kFBins) {
-        float a = hist[0][t];
-        for (int k = 1; k < 32; k++) a += hist[k][t];
-        o[2 + t] = a;
+    if (t < kFBins) {
+        unsigned long long m = 0ull;
+        unsigned int c = 0u;
+        for (int k = 0; k < 32; k++) { m += hist_m[k][t]; c += hist_c[k][t]; }
+        const float wgt = (t < 10) ? 1.f : 64.f;       // octaves below the top ten were sampled 1-in-64
+        o[2 + 2 * t] = ldexpf((float)m, -(t + 24)) * wgt;
+        o[3 + 2 * t] = (float)c * wgt;
     }
 }
 

@@ -54,7 +54,8 @@ class CudaCompute:
 
 
 class VocabParallelSampler:
-    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1, fast=True, graph=False):
+    def __init__(self, B, V_global, rank, world, group=None, device="cuda", compute=None, T=1, fast=True, graph=False,
+                 defer_check=False):
         if V_global % world or (V_global // world) % 4:
             raise ValueError("V=%d cannot be split into %d shards of a multiple of 4 columns" % (V_global, world))
         self.B, self.T, self.V_global, self.rank, self.world, self.group = B, T, V_global, rank, world, group
@@ -92,6 +93,10 @@ class VocabParallelSampler:
         self.use_graph = graph and fast
         self._graphs = {}
         self.last_protocol = None
+        # defer_check: `sample()` does not wait for the device's validity flag; call `validate()` before trusting the
+        # ids of the last call (a decode loop does so when it reads the ids on the host)
+        self.defer_check = defer_check
+        self._pending = None
 
     def release_graphs(self):
         """Drops the recorded CUDA graphs.  Call it before the process group is destroyed (and before the process
@@ -150,9 +155,28 @@ class VocabParallelSampler:
                 g.replay()
         else:
             self._fast_stages(penalties)
+        if self.defer_check:
+            # No host synchronisation: the ids are returned as they are.  The device has already withheld the state
+            # advance and the penalty update if some row could not be settled; `validate()` finds out and repeats.
+            self._pending = (bind_args, penalties)
+            return self.f_ids - 1
         if int(self.f_all_valid.item()) == 0:            # the one host synchronisation of the fast protocol
             return None
         return self.f_ids - 1
+
+    def validate(self):
+        """After `sample()` calls made with `defer_check=True`: reads the device's verdict on the LAST call (one host
+        synchronisation, typically the one the caller needs anyway to read the ids).  If some row's candidate list
+        could not settle its cutoff, that call changed nothing on the device; it is repeated here with the staged
+        protocol and the corrected ids are returned.  Otherwise returns None: the ids already returned stand."""
+        if self._pending is None:
+            return None
+        bind_args, penalties = self._pending
+        self._pending = None
+        if int(self.f_all_valid.item()) != 0:
+            return None
+        self.compute.bind(self, *bind_args)
+        return self._sample_staged(penalties)
 
     def sample(self, logits, states, temperature, top_k, top_p, penalties=None, presence_penalty=0.0,
                repetition_penalty=0.0, penalty_decay=0.0):
@@ -170,6 +194,11 @@ class VocabParallelSampler:
             if ids is not None:
                 self.last_protocol = "fast"
                 return ids
+        return self._sample_staged(penalties)
+
+    def _sample_staged(self, penalties):
+        c = self.compute
+        self.last_protocol = "staged"
         c.stage("max")
         self._reduce(self.gmax, dist.ReduceOp.MAX)
         c.stage("sum")

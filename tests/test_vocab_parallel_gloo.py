@@ -13,7 +13,7 @@ import torch.multiprocessing as mp
 CONFIGS = [(0.8, 50, 0.9), (1.0, -1, 0.3), (1.0, 5, 1.0), (1.3, -1, 1.0)]
 
 
-def _worker(rank, world, port, q, fast=False):
+def _worker(rank, world, port, q, fast=False, defer=False):
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     sys.path.insert(0, root)
@@ -26,7 +26,7 @@ def _worker(rank, world, port, q, fast=False):
     B, V = 6, 4096
     full = make_logits("normal3", B, V, 5, torch)
     s = VocabParallelSampler(B, V, rank, world, device="cpu", compute=NumpyFastCompute() if fast else NumpyCompute(),
-                             fast=fast)
+                             fast=fast, defer_check=defer)
     shard = full[:, s.col0:s.col0 + s.V_local].contiguous()
     states = torch.from_numpy(co.setup_rand(17, B))
     pen = torch.zeros(B, s.V_local)
@@ -34,6 +34,10 @@ def _worker(rank, world, port, q, fast=False):
     for temp, k, p in CONFIGS:
         ids = s.sample(shard, states, temp, k, p, penalties=pen, presence_penalty=0.1, repetition_penalty=0.2,
                        penalty_decay=0.5).clone()
+        if defer:      # no verdict was awaited inside sample(): ask now; a repeat with the staged protocol replaces the ids
+            fixed = s.validate()
+            if fixed is not None:
+                ids = fixed.clone()
         if s.last_protocol == "fast":
             thr = np.array([s.compute._thr[b] for b in range(B)], dtype=np.float32)
         else:
@@ -44,8 +48,8 @@ def _worker(rank, world, port, q, fast=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("fast", [False, True])
-def test_two_rank_vocab_parallel_driver(fast):
+@pytest.mark.parametrize("fast,defer", [(False, False), (True, False), (True, True)])
+def test_two_rank_vocab_parallel_driver(fast, defer):
     from helpers import kept_set_flips_ok, make_logits
     from oracle import c_oracle as co
     from oracle import cpu_ref
@@ -55,7 +59,7 @@ def test_two_rank_vocab_parallel_driver(fast):
     s.close()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, fast)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q, fast, defer)) for r in range(2)]
     for p in procs:
         p.start()
     res = dict()
