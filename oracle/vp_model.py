@@ -222,24 +222,28 @@ class NumpyFastCompute(NumpyCompute):
         elif name == "f_compact":
             lmax = s.f_send.numel() // (2 * B)
             send = s.f_send.numpy().view(np.uint32).reshape(B, lmax, 2)
-            cnt = s.f_send_cnt.numpy().view(np.uint32)
+            cnt = s.f_send_cnt.numpy().view(np.uint32).reshape(B, -1)     # one count per segment; the model fills segment 0 only
+            cnt[:] = 0
+            seg = lmax // cnt.shape[1]
             for b in range(B):
                 idx = self._lists[b]
-                if idx is None or len(idx) > lmax:
-                    cnt[b] = 0xffffffff
+                if idx is None or len(idx) > seg:
+                    cnt[b, 0] = 0xffffffff
                     continue
-                cnt[b] = len(idx)
+                cnt[b, 0] = len(idx)
                 send[b, :len(idx), 0] = self._evals[b][idx].view(np.uint32)
                 send[b, :len(idx), 1] = (idx + s.col0).astype(np.uint32)
         elif name == "f_finish":
             lmax = s.f_send.numel() // (2 * B)
             gath = s.f_gath.numpy().view(np.uint32).reshape(s.world, B, lmax, 2)
-            gcnt = s.f_gath_cnt.numpy().view(np.uint32).reshape(s.world, B)
+            gcnt = s.f_gath_cnt.numpy().view(np.uint32).reshape(s.world, B, -1)
+            seg = lmax // gcnt.shape[2]
+            gcnt = gcnt[:, :, 0]
             denom, bound = self._denom_bound()
             ids, valid = s.f_ids.numpy(), s.f_valid.numpy()
             for b in range(B):
-                ok = bool(bound[b] > 0) and bool((gcnt[:, b] <= lmax).all())
-                parts = [gath[r, b, :min(int(gcnt[r, b]), lmax)] for r in range(s.world)]
+                ok = bool(bound[b] > 0) and bool((gcnt[:, b] <= seg).all())
+                parts = [gath[r, b, :min(int(gcnt[r, b]), seg)] for r in range(s.world)]
                 ent = np.concatenate(parts, axis=0)
                 p = (ent[:, 0].copy().view(np.float32) / denom[b]).astype(np.float32)
                 pb = p.view(np.uint32).astype(np.uint64)

@@ -330,11 +330,11 @@ static VpLayout vp_layout(long long B, int world) {
 //   vpf_max     per (row, sub-block): max of x                                  -> all-reduce MAX  [B][S]
 //   vpf_sum     per (row, sub-block): denominator partial, octave histogram     -> all-reduce SUM  [B][S][2 + 2*32]
 //               (count and mass per octave; exact in the top 10 octaves, a 1-in-64 sample of groups below)
-//   vpf_extract per (row, sub-block): per-thread candidate slots (e >= bound)
-//   vpf_compact per row: ordered list of (e, column)                             -> all-gather  [B][Lmax][2] + counts
+//   vpf_extract per (row, sub-block): ordered list of (e, column) with e >= bound,
+//               written into the sub-block's segment of the row's list           -> all-gather  [B][S][Lmax/S][2] + counts
 //   vpf_finish  per row, on every rank: probabilities staged in shared memory, threshold, weights, pick; validity
 // =====================================================================================================
-constexpr int kFCap = 16;       // candidates a thread may hold per sub-block
+constexpr int kFCap = 12;       // candidates a thread may hold per sub-block (96 KiB of shared memory: two CTAs per SM)
 constexpr int kFMaxSub = 8;
 constexpr int kFBins = 32;      // octaves of e = exp2(x - max) below 1 that the mass histogram resolves
 // candidates a rank may contribute per row: the union over ranks stays near 32K entries
@@ -347,6 +347,40 @@ __device__ __forceinline__ FSub f_sub(int n, int S, int s) {
     r.g0 = min(s * per, G);
     r.g1 = min(r.g0 + per, G);
     return r;
+}
+// The shard passes are latency-bound when a thread has one load in flight: they fetch kFAhead groups ahead of the
+// arithmetic (raw logits and penalties first, the scaling afterwards, in the same order as before).
+constexpr int kFAhead = 2;
+struct FRaw { float4 l, q; };
+__device__ __forceinline__ FRaw vp_raw4(const VpRow& r, int g) {
+    FRaw x;
+    x.l = reinterpret_cast<const float4*>(r.logits)[g];
+    x.q = r.penalties ? reinterpret_cast<const float4*>(r.penalties)[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+    return x;
+}
+__device__ __forceinline__ float4 vp_x4_of(const VpRow& r, const FRaw& x, float scale) {
+    float4 v = x.l;
+    if (r.penalties) {
+        const float4 q = x.q;
+        v.x = sanitize((sanitize(v.x) - q.x) * scale); v.y = sanitize((sanitize(v.y) - q.y) * scale);
+        v.z = sanitize((sanitize(v.z) - q.z) * scale); v.w = sanitize((sanitize(v.w) - q.w) * scale);
+    } else {
+        v.x = sanitize(v.x * scale); v.y = sanitize(v.y * scale); v.z = sanitize(v.z * scale); v.w = sanitize(v.w * scale);
+    }
+    return v;
+}
+// calls body(g, x4) for this thread's groups g0 + t, g0 + t + 1024, ... < g1, in that order
+template <class F>
+__device__ __forceinline__ void vp_for_groups(const VpRow& r, int g0, int g1, float scale, F&& body) {
+    for (int g = g0 + (int)threadIdx.x; g < g1; g += kFAhead * kVpThreads) {
+        FRaw raw[kFAhead];
+#pragma unroll
+        for (int u = 0; u < kFAhead; u++)
+            if (g + u * kVpThreads < g1) raw[u] = vp_raw4(r, g + u * kVpThreads);
+#pragma unroll
+        for (int u = 0; u < kFAhead; u++)
+            if (g + u * kVpThreads < g1) body(g + u * kVpThreads, vp_x4_of(r, raw[u], scale));
+    }
 }
 __device__ __forceinline__ float4 vp_x4(const VpRow& r, int g, float scale) {
     float4 v = reinterpret_cast<const float4*>(r.logits)[g];
@@ -438,7 +472,8 @@ __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits
             acc += e;
             // The histogram only steers the choice of the bound (the finishing kernel checks the result exactly), so
             // below the top ten octaves one group in 64 stands for its neighbours: few shared-memory atomics.
-            if (d > -(float)kFBins) {
+            // (one octave of slack in the cheap test; the exact octave decides)
+            if (d > -11.f || ((g & 63) == 0 && d > -(float)kFBins)) {
                 int k = (int)(-d);                 // octave: e in (2^-(k+1), 2^-k]
                 if (e < exp2f(-(float)k) * 0.5f) k++;      // guard the octave edge against rounding of exp2f
                 if (k < 10 || (g & 63) == 0) {
@@ -464,77 +499,64 @@ __global__ void __launch_bounds__(kVpThreads) vpf_sum_kernel(const float* logits
     }
 }
 
-// pass 3: every element with e >= bound goes to its thread's list (order: column order within the thread)
+// pass 3: every element with e >= bound, as (e, global column), in the fixed order (thread, position within the thread),
+// written straight into this sub-block's segment of the list that is all-gathered next.  A thread first collects its
+// candidates in shared memory (at most kFCap), a block scan of the counts gives every thread its place, and the entries
+// are copied in that order; a thread or segment that overflows marks the segment, which makes the finishing kernel
+// reject the row (the driver then repeats the call with the staged protocol).
 __global__ void __launch_bounds__(kVpThreads) vpf_extract_kernel(const float* logits, long long row_stride, float* penalties,
                                                                  int n, float scale, int S, const float* stat1,
-                                                                 const float* stat2, float top_k, float top_p,
-                                                                 uint32_t* tcnt, uint32_t* tent, long long col0) {
-    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x;
+                                                                 const float* stat2, float top_k, float top_p, int seg,
+                                                                 uint32_t* send /* [B][S][seg][2] */,
+                                                                 uint32_t* send_cnt /* [B][S] */, long long col0) {
+    extern __shared__ uint2 s_ent[];       // [kFCap][kVpThreads]
+    __shared__ uint32_t s_wsum[32];
+    const int b = blockIdx.x / S, s = blockIdx.x % S, t = threadIdx.x, lane = t & 31, w = t >> 5;
     const VpRow r = vp_row(logits, row_stride, penalties, n, b);
     const FSub sb = f_sub(n, S, s);
     const float gmax = f_gmax(stat1, S, b);
     const float denom = f_denom(stat2, S, b);
     const float bound = f_bound_e(stat2, S, b, denom, top_k, top_p);
     uint32_t nc = 0;
-    uint32_t* ent = tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2;
     if (bound > 0.f) {
         const float bx = log2f(bound) - 1.f;       // cheap pre-test in the x domain, one octave of slack
-        for (int g = sb.g0 + t; g < sb.g1; g += kVpThreads) {
-            const float4 v = vp_x4(r, g, scale);
+        vp_for_groups(r, sb.g0, sb.g1, scale, [&](int g, float4 v) {
             const float x[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 if (x[j] - gmax >= bx) {
                     const float e = exp2f(x[j] - gmax);
                     if (e >= bound) {
-                        if (nc < kFCap) { ent[nc * 2] = __float_as_uint(e); ent[nc * 2 + 1] = (uint32_t)(col0 + 4 * g + j); }
+                        if (nc < (uint32_t)kFCap) s_ent[nc * kVpThreads + t] = make_uint2(__float_as_uint(e), (uint32_t)(col0 + 4 * g + j));
                         nc++;
                     }
                 }
             }
-        }
+        });
     } else {
         nc = kFCap + 1;     // no usable bound: flag the row through the overflow path
     }
-    tcnt[(size_t)(b * S + s) * kVpThreads + t] = nc;
-}
-
-// Ordered compaction of a row's per-thread lists (sub-block, thread, entry) into one list for the all-gather.
-__global__ void __launch_bounds__(kVpThreads) vpf_compact_kernel(int S, int lmax, const uint32_t* tcnt, const uint32_t* tent,
-                                                                 uint32_t* send /* [B][Lmax][2] */, uint32_t* send_cnt) {
-    __shared__ int s_over;
-    __shared__ uint32_t sh[2][32];     // warp totals, double-buffered over the sub-blocks
-    const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
-    if (t == 0) s_over = 0;
-    __syncthreads();
-    uint32_t base = 0;                  // entries of the sub-blocks before this one (every thread keeps its own copy)
-    for (int s = 0; s < S; s++) {
-        const uint32_t raw = tcnt[(size_t)(b * S + s) * kVpThreads + t];
-        if (raw > (uint32_t)kFCap) s_over = 1;
-        const uint32_t c = min(raw, (uint32_t)kFCap);
-        uint32_t incl = c;
+    const uint32_t c = min(nc, (uint32_t)kFCap);
+    uint32_t incl = c;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += v;
-        }
-        if (lane == 31) sh[s & 1][w] = incl;
-        __syncthreads();
-        uint32_t pre = 0, tot = 0;
-        for (int k = 0; k < 32; k++) {
-            const uint32_t x = sh[s & 1][k];
-            pre += (k < w) ? x : 0u;
-            tot += x;
-        }
-        const uint32_t off = base + pre + incl - c;
-        const uint2* ent = reinterpret_cast<const uint2*>(tent + ((size_t)(b * S + s) * kVpThreads + t) * kFCap * 2);
-        uint2* dst = reinterpret_cast<uint2*>(send) + (size_t)b * lmax;
-        for (uint32_t i = 0; i < c; i++)
-            if (off + i < (uint32_t)lmax) dst[off + i] = ent[i];
-        base += tot;
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
     }
-    __syncthreads();
-    if (t == 0) send_cnt[b] = s_over ? 0xffffffffu : base;   // beyond Lmax / flagged: the finishing kernel rejects the row
+    if (lane == 31) s_wsum[w] = incl;
+    const int over = __syncthreads_or(nc > (uint32_t)kFCap ? 1 : 0);
+    uint32_t pre = 0, tot = 0;
+    for (int k = 0; k < 32; k++) {
+        const uint32_t x = s_wsum[k];
+        pre += (k < w) ? x : 0u;
+        tot += x;
+    }
+    const bool bad = over || tot > (uint32_t)seg;
+    if (!bad) {
+        uint2* dst = reinterpret_cast<uint2*>(send) + (size_t)(b * S + s) * seg + (pre + incl - c);
+        for (uint32_t i = 0; i < c; i++) dst[i] = s_ent[i * kVpThreads + t];
+    }
+    if (t == 0) send_cnt[b * S + s] = bad ? 0xffffffffu : tot;
 }
 
 // block-wide fixed-order sums of NV per-thread values at once: warp trees, then threads 0..NV-1 add the 32 warp values
@@ -590,49 +612,63 @@ __device__ __forceinline__ void f_block_sums30(float (&v)[30], float* sh /* [32]
     for (int i = 0; i < 30; i++) v[i] = sh[32 * 32 + i];
 }
 
-__global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, int lmax, const float* stat1, const float* stat2,
-                                                                const uint32_t* gath /* [world][B][Lmax][2] */,
-                                                                const uint32_t* gath_cnt /* [world][B] */, float top_k,
+__global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, int seg, const float* stat1, const float* stat2,
+                                                                const uint32_t* gath /* [world][B][S][seg][2] */,
+                                                                const uint32_t* gath_cnt /* [world][B][S] */, float top_k,
                                                                 float top_p, int use_p, const unsigned char* states,
                                                                 int* ids, int* valid) {
     __shared__ float sh[32 * 32 + 32];
     __shared__ float s_scan[32];
     __shared__ int s_hit;
+    __shared__ uint32_t s_segoff[kFMaxSub * 8 + 1];   // first flat position of every (rank, sub-block) segment of this row
+    __shared__ int s_segbad;
     extern __shared__ float s_pr[];   // the probabilities of the row's candidates, list order (up to 32768)
     const int b = blockIdx.x, t = threadIdx.x, lane = t & 31, w = t >> 5;
     const float denom = f_denom(stat2, S, b);
     const float bound = f_bound_e(stat2, S, b, denom, top_k, top_p);
     bool ok_row = bound > 0.f;
-    uint32_t M = 0;
-    for (int r = 0; r < world; r++) {
-        const uint32_t c = gath_cnt[r * B + b];
-        if (c > (uint32_t)lmax) ok_row = false;
-        M += min(c, (uint32_t)lmax);
+    const int nseg = world * S;
+    if (t == 0) {
+        uint32_t run = 0;
+        int bad = 0;
+        for (int i = 0; i < nseg; i++) {
+            const uint32_t c = gath_cnt[((size_t)(i / S) * B + b) * S + (i % S)];
+            if (c > (uint32_t)seg) bad = 1;
+            s_segoff[i] = run;
+            run += min(c, (uint32_t)seg);
+        }
+        s_segoff[nseg] = run;
+        s_segbad = bad;
     }
-    // flat position -> (rank, entry); each thread owns a contiguous block of q positions (keeps list order)
+    __syncthreads();
+    const uint32_t M = s_segoff[nseg];
+    if (s_segbad) ok_row = false;
+    // flat position -> (rank, sub-block, entry); each thread owns a contiguous block of q positions (keeps list order)
     const uint32_t q = (M + kVpThreads - 1) / kVpThreads;
     const uint32_t p0 = min((uint32_t)t * q, M), p1 = min(p0 + q, M);
-    auto entry = [&](uint32_t pos, float& pr, uint32_t& col) {
-        uint32_t r = 0, rem = pos;
-        for (;;) {
-            const uint32_t c = min(gath_cnt[r * B + b], (uint32_t)lmax);
-            if (rem < c) break;
-            rem -= c;
-            r++;
-        }
-        const uint32_t* e = gath + (((size_t)r * B + b) * lmax + rem) * 2;
+    auto entry_in = [&](int i, uint32_t pos, float& pr, uint32_t& col) {     // pos lies in segment i
+        const uint32_t* e = gath + ((((size_t)(i / S) * B + b) * S + (i % S)) * seg + (pos - s_segoff[i])) * 2;
         pr = __uint_as_float(e[0]) / denom;
         col = e[1];
+    };
+    auto entry = [&](uint32_t pos, float& pr, uint32_t& col) {
+        int i = 0;
+        while (i + 1 < nseg && pos >= s_segoff[i + 1]) i++;
+        entry_in(i, pos, pr, col);
     };
     // every probability > bound / denom is on the list (division is monotone; an element just below the bound may
     // round to the same quotient, hence strictly); 16-ary search over that range; the set at its lower end must
     // already fail the test, else the list is too thin
     const uint32_t beta_p = __float_as_uint(bound / denom);
     uint32_t left = beta_p + 1u, right = 0x3f800001u;
-    for (uint32_t pos = p0; pos < p1; pos++) {      // one look-up and division per candidate; the rounds read shared memory
-        float pr; uint32_t col;
-        entry(pos, pr, col);
-        s_pr[pos] = pr;
+    {
+        int i = 0;
+        for (uint32_t pos = p0; pos < p1; pos++) {      // one look-up and division per candidate; the rounds read shared memory
+            while (i + 1 < nseg && pos >= s_segoff[i + 1]) i++;
+            float pr; uint32_t col;
+            entry_in(i, pos, pr, col);
+            s_pr[pos] = pr;
+        }
     }
     {
         float v[2] = {0.f, 0.f};
@@ -740,7 +776,7 @@ __global__ void vpf_advance_kernel(unsigned char* states, int B, const int* gate
     st[1] = philox4x32_10(nctr, key.x, key.y);
 }
 
-struct VpfLayout { size_t stat1, stat2, tcnt, tent, send, send_cnt, gath, gath_cnt, ids, valid, total; };
+struct VpfLayout { size_t stat1, stat2, send, send_cnt, gath, gath_cnt, ids, valid, total; };
 static VpfLayout vpf_layout(long long B, int world, int S) {
     const int lmax = f_lmax(world);
     VpfLayout l;
@@ -748,12 +784,10 @@ static VpfLayout vpf_layout(long long B, int world, int S) {
     auto take = [&](size_t n) { size_t at = o; o += (n + 63) & ~(size_t)63; return at; };
     l.stat1 = take((size_t)B * S);
     l.stat2 = take((size_t)B * S * kFStat2);
-    l.tcnt = take((size_t)B * S * kVpThreads);
-    l.tent = take((size_t)B * S * kVpThreads * kFCap * 2);
-    l.send = take((size_t)B * lmax * 2);
-    l.send_cnt = take(B);
+    l.send = take((size_t)B * lmax * 2);                 // S segments of lmax / S entries per row
+    l.send_cnt = take((size_t)B * S);                    // one count per segment
     l.gath = take((size_t)world * B * lmax * 2);
-    l.gath_cnt = take((size_t)world * B);
+    l.gath_cnt = take((size_t)world * B * S);
     l.ids = take(B);
     l.valid = take(B + 1);   // per-row flags, then one flag for the whole call
     l.total = o;
@@ -878,13 +912,24 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
             else if (stage == RS_VPF_SUM)
                 vpf_sum_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
                                                                 fw + f.stat2);
-            else if (stage == RS_VPF_EXTRACT)
-                vpf_extract_kernel<<<grid * S, kVpThreads, 0, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
-                                                                    fw + f.stat2, fk, fp, uw + f.tcnt, uw + f.tent,
-                                                                    (long long)c->col0);
-            else if (stage == RS_VPF_COMPACT)
-                vpf_compact_kernel<<<grid, kVpThreads, 0, st>>>(S, lmax, uw + f.tcnt, uw + f.tent, uw + f.send, uw + f.send_cnt);
-            else if (stage == RS_VPF_FINISH) {
+            else if (stage == RS_VPF_EXTRACT) {
+                constexpr size_t kExtractSmem = (size_t)kFCap * kVpThreads * sizeof(uint2);
+                static bool attr_done_x[64] = {};     // per device
+                int dev = 0;
+                if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RS_ERR_CUDA;
+                if (!attr_done_x[dev]) {
+                    if (cudaFuncSetAttribute(vpf_extract_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kExtractSmem) !=
+                        cudaSuccess)
+                        return RS_ERR_CUDA;
+                    attr_done_x[dev] = true;
+                }
+                vpf_extract_kernel<<<grid * S, kVpThreads, kExtractSmem, st>>>(lg, stride, c->penalties, (int)n, scale, S, fw + f.stat1,
+                                                                               fw + f.stat2, fk, fp, lmax / S, uw + f.send,
+                                                                               uw + f.send_cnt, (long long)c->col0);
+            } else if (stage == RS_VPF_COMPACT) {
+                // nothing to do: the extraction writes the ordered list itself (the stage stays for drivers that name it)
+                return RS_OK;
+            } else if (stage == RS_VPF_FINISH) {
                 // the union of the ranks' lists is staged in shared memory: 4 bytes per candidate
                 constexpr size_t kFinishSmem = 160 * 1024;
                 if ((size_t)lmax * c->world * sizeof(float) > kFinishSmem) return RS_ERR_LIMIT;
@@ -897,7 +942,7 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
                         return RS_ERR_CUDA;
                     attr_done[dev] = true;
                 }
-                vpf_finish_kernel<<<grid, kVpThreads, (size_t)lmax * c->world * sizeof(float), st>>>((int)B, S, c->world, lmax, fw + f.stat1, fw + f.stat2, uw + f.gath,
+                vpf_finish_kernel<<<grid, kVpThreads, (size_t)lmax * c->world * sizeof(float), st>>>((int)B, S, c->world, lmax / S, fw + f.stat1, fw + f.stat2, uw + f.gath,
                                                                uw + f.gath_cnt, fk, fp, use_p, (const unsigned char*)c->states,
                                                                (int*)(uw + f.ids), (int*)(uw + f.valid));
             } else

@@ -84,9 +84,9 @@ class VocabParallelSampler:
         self.f_stat1 = self.ws[f[0]:f[0] + B * S]
         self.f_stat2 = self.ws[f[1]:f[1] + B * S * f[10]]
         self.f_send = self.ws[f[2]:f[2] + B * Lmax * 2]
-        self.f_send_cnt = self.ws[f[3]:f[3] + B]
+        self.f_send_cnt = self.ws[f[3]:f[3] + B * S]          # one count per (row, sub-block) segment
         self.f_gath = self.ws[f[4]:f[4] + world * B * Lmax * 2]
-        self.f_gath_cnt = self.ws[f[5]:f[5] + world * B]
+        self.f_gath_cnt = self.ws[f[5]:f[5] + world * B * S]
         self.f_ids = self.ws[f[6]:f[6] + B].view(torch.int32)
         self.f_valid = self.ws[f[7]:f[7] + B].view(torch.int32)
         self.f_all_valid = self.ws[f[7] + B:f[7] + B + 1].view(torch.int32)   # cleared if any row could not be settled
