@@ -503,6 +503,10 @@ def main():
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--path-mode", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="force a kernel variant (rs_set_path_override): 1 whole-row search, 2 streaming cluster, 3 on-chip cluster, "
+                         "4 one CTA per row; for profiling one variant on a workload the planner would give to another")
+    ap.add_argument("--per-row", action="store_true", help="ours only: per-row temperature / top_k / top_p tensors (rs_sample_rows)")
     ap.add_argument("--no-extras", action="store_true",
                     help="only the headline workload: skip the reference-CUDA arm, the other workloads and the multi-GPU extras")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16", "bf16"], help="storage type of the logits (ours only)")
@@ -579,7 +583,20 @@ def main():
     f_plain = ext.batch_sampling_temperature_topk_topp_any if lowp else ext.batch_sampling_temperature_topk_topp
     f_rep = ext.batch_sampling_repetition_temperature_topk_topp_any if lowp else ext.batch_sampling_repetition_temperature_topk_topp
 
+    if a.impl == "ours" and a.path_mode:
+        from rapid_sampling_b200 import abi
+        abi.load().rs_set_path_override(a.path_mode)
+        base["config"]["path_mode"] = a.path_mode
+    if a.impl == "ours" and a.per_row:
+        t_row = torch.full((B,), w["temperature"], device=dev, dtype=torch.float32)
+        k_row = torch.full((B,), w["top_k"], device=dev, dtype=torch.int32)
+        p_row = torch.full((B,), w["top_p"], device=dev, dtype=torch.float32)
+        base["config"]["per_row_parameters"] = True
+
     def call(lg):
+        if a.impl == "ours" and a.per_row:
+            return ext.batch_sampling_rows(lg, states, t_row, k_row, p_row, penalties=pen, presence_penalty=0.1,
+                                           repetition_penalty=0.1, penalty_decay=0.95)
         if w["rep"]:
             return f_rep(lg, pen, states, 0.1, 0.1, 0.95, w["temperature"], w["top_k"], w["top_p"])
         return f_plain(lg, states, w["temperature"], w["top_k"], w["top_p"])
@@ -662,7 +679,7 @@ def main():
 
     # ---- beside the headline, outside its timed region --------------------------------------------------
     extras = {}
-    if a.impl == "ours" and not a.no_extras and a.dtype == "f32":
+    if a.impl == "ours" and not a.no_extras and a.dtype == "f32" and not a.path_mode and not a.per_row:
         del host_pool
         if world > 1:
             extras["multi_gpu"] = multi_gpu_extras(ext, rank, world, dev, torch, dist)

@@ -73,12 +73,15 @@ __device__ __forceinline__ void tree_levels(float* m, const int lane) {
 }  // namespace
 
 // LPT: virtual lanes per thread.  REP: the call has penalties (sampling.cu:172-438), else not (:517-964).  D: stages of
-// a thread's copy pipeline.  All three are compile-time so that the streaming loops carry no tests on them.
+// a thread's copy pipeline.  NH: stages per stripe (2: a stage holds half a stripe, which buys twice the stages -- and
+// bytes in flight -- from the same shared memory when two rows with penalties share an SM).  All compile-time, so that
+// the streaming loops carry no tests on them.
 struct TagFull { static constexpr bool value = true; };
 struct TagRagged { static constexpr bool value = false; };
 
-template <int LPT, bool REP, int D>
+template <int LPT, bool REP, int D, int NH>
 __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kernel(const Params p, const RowCtaPlan pl) {
+    constexpr int SL = LPT / NH;       // lanes of a thread that one copy stage serves (NH stages make up a stripe)
     constexpr int NT = kLanes / LPT;   // threads; thread t plays virtual lanes j * NT + t
     constexpr int WPB = NT / 32;       // warps; physical warp pw plays virtual warps j * WPB + pw
     constexpr int NV = LPT * 4;        // ordered masses a thread holds in a search round
@@ -118,37 +121,42 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     bool tail_ok[LPT];
 #pragma unroll
     for (int j = 0; j < LPT; j++) tail_ok[j] = (j * NT + t) < rem;
-    constexpr uint32_t kStage = REP ? 2 * kStripeBytes : kStripeBytes;
+    constexpr uint32_t kPart = kStripeBytes / NH;              // bytes of logits (or of penalties) in a stage
+    constexpr uint32_t kStage = REP ? 2 * kPart : kPart;
     const uint32_t sm_ring = smem_addr(ring) + (uint32_t)t * 16u, sm_cache = smem_addr(cache) + (uint32_t)t * 16u;
     const float4* const gl = reinterpret_cast<const float4*>(lrow) + t;
     const float4* const gp = reinterpret_cast<const float4*>(prow) + t;
-    int ik = 0, islot = 0, idir = 1;   // next stripe to request, its stage, and the direction of the pass
+    int ik = 0, ih = 0, islot = 0, idir = 1;   // next stripe (and part of it) to request, its stage, the direction of the pass
     // LG / PN: the pass wants the stripe's logits / penalties
     auto request = [&](auto lg_tag, auto pn_tag) {
         constexpr bool LG = decltype(lg_tag)::value, PN = decltype(pn_tag)::value;
         if ((unsigned)ik < (unsigned)K) {
             const uint32_t st = sm_ring + (uint32_t)islot * kStage;
-            const uint32_t ldst = (ik < NC) ? sm_cache + (uint32_t)ik * kStripeBytes : st;
+            const bool keep = (ik < NC);
+            const uint32_t ldst = keep ? sm_cache + (uint32_t)ik * kStripeBytes : st;
             const float4* src = gl + (size_t)ik * kLanes;
             const float4* psrc = gp + (size_t)ik * kLanes;
-            if (__builtin_expect(ik < Kf, 1)) {
+            const bool fullk = ik < Kf;
 #pragma unroll
-                for (int j = 0; j < LPT; j++) {
-                    if (LG) cp_async16(ldst + j * NT * 16, src + j * NT);
-                    if (PN) cp_async16(st + kStripeBytes + j * NT * 16, psrc + j * NT);
-                }
-            } else {
+            for (int h = 0; h < NH; h++) {
+                if (NH == 1 || h == ih) {
 #pragma unroll
-                for (int j = 0; j < LPT; j++) {
-                    if (tail_ok[j]) {
-                        if (LG) cp_async16(ldst + j * NT * 16, src + j * NT);
-                        if (PN) cp_async16(st + kStripeBytes + j * NT * 16, psrc + j * NT);
+                    for (int jj = 0; jj < SL; jj++) {
+                        const int j = h * SL + jj;
+                        if (fullk || tail_ok[j]) {
+                            // a kept stripe has the stripe's own layout, a stage holds only this part's lanes
+                            if (LG) cp_async16(ldst + (keep ? j : jj) * NT * 16, src + j * NT);
+                            if (PN) cp_async16(st + kPart + jj * NT * 16, psrc + j * NT);
+                        }
                     }
                 }
             }
         }
         cp_commit();
-        ik += idir;
+        if (NH == 1 || ++ih == NH) {
+            ih = 0;
+            ik += idir;
+        }
         islot = (islot + 1 == D) ? 0 : islot + 1;
     };
     auto wait_stage = [&]() {   // the oldest requested stage has landed
@@ -156,6 +164,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     };
     auto begin_pass = [&](const int first, const int dir, auto lg_tag, auto pn_tag) {
         ik = first;
+        ih = 0;
         idir = dir;
         islot = 0;
 #pragma unroll
@@ -211,24 +220,26 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         int cslot = 0;
         auto stripe = [&](auto full_tag, const int k) {
             constexpr bool FULLK = decltype(full_tag)::value;
-            request(Yes(), Pen());
-            wait_stage();
-            const unsigned char* st = ring + (size_t)cslot * kStage;
             const bool keep = (k < NC);
             unsigned char* own = cache + (size_t)k * kStripeBytes;
-            const unsigned char* src = keep ? own : st;
 #pragma unroll
-            for (int j = 0; j < LPT; j++) {
-                const int l = j * NT + t;
-                if (FULLK || tail_ok[j]) {
-                    float4 v = reinterpret_cast<const float4*>(src)[l];
-                    if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
-                    else v = scaled4(v, a_scale);
-                    tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
-                    if (keep) reinterpret_cast<float4*>(own)[l] = v;
+            for (int h = 0; h < NH; h++) {
+                request(Yes(), Pen());
+                wait_stage();
+                const unsigned char* st = ring + (size_t)cslot * kStage;
+#pragma unroll
+                for (int jj = 0; jj < SL; jj++) {
+                    const int j = h * SL + jj;
+                    if (FULLK || tail_ok[j]) {
+                        float4 v = keep ? reinterpret_cast<const float4*>(own)[j * NT + t] : reinterpret_cast<const float4*>(st)[jj * NT + t];
+                        if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
+                        else v = scaled4(v, a_scale);
+                        tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
+                        if (keep) reinterpret_cast<float4*>(own)[j * NT + t] = v;
+                    }
                 }
+                cslot = (cslot + 1 == D) ? 0 : cslot + 1;
             }
-            cslot = (cslot + 1 == D) ? 0 : cslot + 1;
         };
         if (rem) stripe(TagRagged(), Kf);
         for (int k = Kf - 1; k >= 0; k--) stripe(TagFull(), k);
@@ -305,23 +316,26 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         auto stripe = [&](auto full_tag, const int k) {
             constexpr bool FULLK = decltype(full_tag)::value;
             const bool kept = (k < NC);
-            const unsigned char* st = ring + (size_t)cslot * kStage;
-            if (!kept) {
-                request(Yes(), Pen());
-                wait_stage();
-                cslot = (cslot + 1 == D) ? 0 : cslot + 1;
-            }
-            const unsigned char* src = kept ? cache + (size_t)k * kStripeBytes : st;
+            const unsigned char* own = cache + (size_t)k * kStripeBytes;
 #pragma unroll
-            for (int j = 0; j < LPT; j++) {
-                const int l = j * NT + t;
-                if (FULLK || tail_ok[j]) {
-                    float4 v = reinterpret_cast<const float4*>(src)[l];
-                    if (!kept) {
-                        if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kStripeBytes)[l], a_scale);
-                        else v = scaled4(v, a_scale);
+            for (int h = 0; h < NH; h++) {
+                const unsigned char* st = ring + (size_t)cslot * kStage;
+                if (!kept) {
+                    request(Yes(), Pen());
+                    wait_stage();
+                    cslot = (cslot + 1 == D) ? 0 : cslot + 1;
+                }
+#pragma unroll
+                for (int jj = 0; jj < SL; jj++) {
+                    const int j = h * SL + jj;
+                    if (FULLK || tail_ok[j]) {
+                        float4 v = kept ? reinterpret_cast<const float4*>(own)[j * NT + t] : reinterpret_cast<const float4*>(st)[jj * NT + t];
+                        if (!kept) {
+                            if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
+                            else v = scaled4(v, a_scale);
+                        }
+                        pass2_group(j, v);
                     }
-                    pass2_group(j, v);
                 }
             }
         };
@@ -890,14 +904,17 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         int cslot = 0;
         auto stripe = [&](auto full_tag, const int k) {
             constexpr bool FULLK = decltype(full_tag)::value;
+#pragma unroll
+            for (int h = 0; h < NH; h++) {
             request(No(), Yes());
             wait_stage();
             const unsigned char* st = ring + (size_t)cslot * kStage;
 #pragma unroll
-            for (int j = 0; j < LPT; j++) {
+            for (int jj = 0; jj < SL; jj++) {
+                const int j = h * SL + jj;
                 const int l = j * NT + t, i4 = k * kLanes + l;
                 if (FULLK || tail_ok[j]) {
-                    const float4 q4 = reinterpret_cast<const float4*>(st + kStripeBytes)[l];
+                    const float4 q4 = reinterpret_cast<const float4*>(st + kPart)[jj * NT + t];
                     float e[4] = {q4.x, q4.y, q4.z, q4.w};
                     if (i4 != (token >> 2)) {
 #pragma unroll
@@ -913,6 +930,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 }
             }
             cslot = (cslot + 1 == D) ? 0 : cslot + 1;
+            }
         };
         if (rem) stripe(TagRagged(), Kf);
         for (int k = Kf - 1; k >= 0; k--) stripe(TagFull(), k);
@@ -938,15 +956,17 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
 
 // ------------------------------------------------------------------------------------------------ host side
 // Shared memory of a row-CTA launch: fixed area, candidate lists (cap entries per virtual lane), copy stages, and the
-// stripes that stay on chip between the passes.  The pipeline depth is a compile-time property of the four kernel
-// instantiations: without penalties 4 stages of 16 KiB; with penalties 3 stages of 32 KiB when a row has an SM to
-// itself (lanes_per_thread 2), 2 stages when two rows share one.
-static int rowcta_depth(bool rep, int lanes_per_thread) { return rep ? (lanes_per_thread == 2 ? 3 : 2) : 4; }
+// stripes that stay on chip between the passes.  The pipeline shape is a compile-time property of the four kernel
+// instantiations:
+// without penalties 4 stages of a whole stripe (16 KiB); with penalties 3 stages of 32 KiB when a row has an SM to itself
+// (lanes_per_thread 2), and 5 stages of half a stripe (16 KiB: 8 of logits, 8 of penalties) when two rows share one.
+static int rowcta_depth(bool rep, int lanes_per_thread) { return rep ? (lanes_per_thread == 2 ? 3 : 5) : 4; }
+static int rowcta_parts(bool rep, int lanes_per_thread) { return (rep && lanes_per_thread == 4) ? 2 : 1; }
 
 RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int smem_budget) {
     RowCtaPlan pl;
     const int K = (V / 4 + kLanes - 1) / kLanes;
-    pl.stage_bytes = rep ? 2 * kStripeBytes : kStripeBytes;
+    pl.stage_bytes = (rep ? 2 : 1) * kStripeBytes / rowcta_parts(rep, lanes_per_thread);
     pl.cap = (sel_rank > 0) ? 6 : 0;
     pl.off_cand = kRowCtaFixedSmem;
     pl.off_ring = pl.off_cand + pl.cap * kLanes * 4;
@@ -954,15 +974,16 @@ RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int 
     const int room = smem_budget - pl.off_ring - pl.depth * pl.stage_bytes;
     int keep = room / kStripeBytes;
     if (keep > K) keep = K;
+    if (rowcta_parts(rep, lanes_per_thread) > 1) keep = 0;      // half-stripe stages keep nothing on chip
     pl.cached = keep < 0 ? 0 : keep;
     pl.off_cache = pl.off_ring + pl.depth * pl.stage_bytes;
     pl.smem_bytes = pl.off_cache + pl.cached * kStripeBytes;
     return pl;
 }
 
-template <int LPT, bool REP, int D>
+template <int LPT, bool REP, int D, int NH>
 static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t stream, int smem_optin, bool* attr_done) {
-    auto kern = rowcta_kernel<LPT, REP, D>;
+    auto kern = rowcta_kernel<LPT, REP, D, NH>;
     if (!*attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin) != cudaSuccess) return RS_ERR_CUDA;
         *attr_done = true;
@@ -980,10 +1001,10 @@ int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, c
     if (pl.depth != rowcta_depth(rep, lanes_per_thread) || pl.smem_bytes > smem_optin) return RS_ERR_LIMIT;
     std::lock_guard<std::mutex> lk(mu);
     if (lanes_per_thread == 2)
-        return rep ? rowcta_launch_t<2, true, 3>(p, pl, stream, smem_optin, &attr_done[dev][0])
-                   : rowcta_launch_t<2, false, 4>(p, pl, stream, smem_optin, &attr_done[dev][1]);
-    return rep ? rowcta_launch_t<4, true, 2>(p, pl, stream, smem_optin, &attr_done[dev][2])
-               : rowcta_launch_t<4, false, 4>(p, pl, stream, smem_optin, &attr_done[dev][3]);
+        return rep ? rowcta_launch_t<2, true, 3, 1>(p, pl, stream, smem_optin, &attr_done[dev][0])
+                   : rowcta_launch_t<2, false, 4, 1>(p, pl, stream, smem_optin, &attr_done[dev][1]);
+    return rep ? rowcta_launch_t<4, true, 5, 2>(p, pl, stream, smem_optin, &attr_done[dev][2])
+               : rowcta_launch_t<4, false, 4, 1>(p, pl, stream, smem_optin, &attr_done[dev][3]);
 }
 
 }  // namespace rs
