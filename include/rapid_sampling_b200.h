@@ -209,6 +209,26 @@ int rs_vp_fast_layout(int64_t B, int64_t V_local, int32_t world, int64_t offsets
 int rs_vp_stage(const rs_vp_call* call, int32_t stage, int32_t round);
 
 /*
+ * lm_head epilogue hook for the vocab-parallel fast protocol.  No counterpart in the reference (it allocates, launches
+ * and reads a finished logits tensor per call, sampling.cu:488, :498, :1014, :1024).  A tensor-parallel lm_head produces
+ * this rank's (B, V_local) logits tile by tile; instead of a separate pass over the finished shard for the row maxima
+ * (stage RS_VPF_MAX), the producer hands every tile over as soon as it exists:
+ *
+ *   rs_vp_tile_begin(call)                                  once per sampling call, before the first tile
+ *   rs_vp_tile_max(call, tile, ld, col_begin, ncols)        per tile, any order, any tile width; `tile` points at row 0
+ *                                                           of the tile (position T-1), rows `ld` elements apart,
+ *                                                           holding local columns [col_begin, col_begin + ncols)
+ *   all-reduce MAX of region [0] of rs_vp_fast_layout, then RS_VPF_SUM, RS_VPF_EXTRACT, ... as usual
+ *
+ * Both calls are asynchronous on call->stream, use only the preallocated workspace and allocate nothing.  The fold is an
+ * atomic maximum, so the result does not depend on the order of the tiles.  call->penalties (if any) must be final when
+ * a tile is handed over; call->logits is not read by these two calls (the later stages read it, so the tiles must end up
+ * in that buffer).
+ */
+int rs_vp_tile_begin(const rs_vp_call* call);
+int rs_vp_tile_max(const rs_vp_call* call, const float* tile_device, int64_t ld, int64_t col_begin, int64_t ncols);
+
+/*
  * Device status word.  The kernels never trap: a condition they cannot report through a return code is written to
  * the first int32 of the workspace, which stays set until it is cleared.  Values: RS_OK; RS_ERR_TIMEOUT (a bounded
  * on-chip wait gave up: the rows of the CTAs that saw it report id -1 and leave their RNG state and penalties

@@ -18,7 +18,7 @@ RS_DTYPE_F32, RS_DTYPE_F16, RS_DTYPE_BF16 = 0, 1, 2
 RS_STATIC_SCRATCH_FLOATS = 4194304
 
 SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_typed", "rs_sample_static_scratch", "rs_rows_workspace_bytes", "rs_sample_rows",
-           "rs_device_status", "rs_clear_status", "rs_set_status_mirror", "rs_set_wait_polls", "rs_selftest_bounded_wait", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_fast_layout", "rs_vp_stage", "rs_status_string",
+           "rs_device_status", "rs_clear_status", "rs_set_status_mirror", "rs_set_wait_polls", "rs_selftest_bounded_wait", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_fast_layout", "rs_vp_stage", "rs_vp_tile_begin", "rs_vp_tile_max", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
 
@@ -71,6 +71,8 @@ def load():
     L.rs_vp_layout.argtypes = [i64, C.c_int32, C.POINTER(C.c_int64)]
     L.rs_vp_fast_layout.argtypes = [i64, i64, C.c_int32, C.POINTER(C.c_int64)]
     L.rs_vp_stage.argtypes = [C.POINTER(VpCall), C.c_int32, C.c_int32]
+    L.rs_vp_tile_begin.argtypes = [C.POINTER(VpCall)]
+    L.rs_vp_tile_max.argtypes = [C.POINTER(VpCall), vp, i64, i64, i64]
     L.rs_device_status.argtypes = [vp, vp]
     L.rs_clear_status.argtypes = [vp, vp]
     L.rs_set_status_mirror.argtypes = [vp]

@@ -415,6 +415,42 @@ __global__ void __launch_bounds__(kVpThreads) vpf_max_kernel(const float* logits
     }
 }
 
+// lm_head epilogue hook, first stage fed tile by tile.  A producer of logits (the epilogue of a tensor-parallel lm_head
+// GEMM, or this kernel run on a tile it has just written) folds a tile's row maxima into stat1 as the tile appears, so
+// that no separate pass over the shard is needed for the maximum.  The fold is an atomic maximum, hence independent of
+// the order in which tiles arrive.  Only slot 0 of a row's S sub-block slots is used; the others stay at -inf.
+__device__ __forceinline__ void vp_fold_row_max(float* slot, float v) {
+    if (v >= 0.f) atomicMax(reinterpret_cast<int*>(slot), __float_as_int(v));
+    else atomicMin(reinterpret_cast<unsigned int*>(slot), __float_as_uint(v));
+}
+__global__ void vpf_tile_begin_kernel(float* stat1, int n, int* all_valid) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) stat1[i] = -INFINITY;
+    if (i == 0) *all_valid = 1;
+}
+// one CTA per (row, chunk of 4096 columns of the tile); ld = elements between consecutive rows of the tile buffer
+__global__ void __launch_bounds__(256) vpf_tile_max_kernel(const float* tile, long long ld, const float* pen_tile, long long pen_ld,
+                                                           int ncols, float scale, int S, float* stat1) {
+    __shared__ float sh[8];
+    const int b = blockIdx.y, t = threadIdx.x;
+    const float* lrow = tile + (long long)b * ld;
+    const float* prow = pen_tile ? pen_tile + (long long)b * pen_ld : nullptr;
+    const int c0 = blockIdx.x * 4096, c1 = min(c0 + 4096, ncols);
+    float m = -INFINITY;
+    for (int c = c0 + t; c < c1; c += 256) {
+        const float l = lrow[c];
+        const float x = prow ? sanitize((sanitize(l) - prow[c]) * scale) : sanitize(l * scale);
+        m = fmaxf(m, x);
+    }
+    m = warp_max(m);
+    if ((t & 31) == 0) sh[t >> 5] = m;
+    __syncthreads();
+    if (t < 32) {
+        m = warp_max(t < 8 ? sh[t] : -INFINITY);
+        if (t == 0) vp_fold_row_max(stat1 + (size_t)b * S, m);
+    }
+}
+
 __device__ __forceinline__ float f_gmax(const float* stat1, int S, int b) {
     float mx = -INFINITY;
     for (int s = 0; s < S; s++) mx = fmaxf(mx, stat1[b * S + s]);
@@ -830,6 +866,46 @@ int rs_vp_layout(int64_t B, int32_t world, int64_t offsets_floats[6]) {
     offsets_floats[0] = (int64_t)l.gmax; offsets_floats[1] = (int64_t)l.gsum; offsets_floats[2] = (int64_t)l.tallies;
     offsets_floats[3] = (int64_t)l.gtally; offsets_floats[4] = (int64_t)l.weights; offsets_floats[5] = (int64_t)l.ids;
     return RS_OK;
+}
+
+static int vp_tile_common(const rs_vp_call* c, float** stat1, int** all_valid, int* S_out, float* scale) {
+    using namespace rs;
+    if (!c) return RS_ERR_POINTER;
+    const int64_t B = c->B, n = c->V_local, V = c->V_global;
+    if (!(V > 0 && V <= 1048576 && V % 4 == 0) || !(n > 0 && n <= V) || n % 4 != 0 || n * (int64_t)c->world != V) return RS_ERR_VOCAB;
+    if (!(B > 0) || c->world <= 0 || c->rank < 0 || c->rank >= c->world) return RS_ERR_BATCH;
+    if (!(c->temperature >= 0.001 && c->temperature <= 1000)) return RS_ERR_TEMPERATURE;
+    if (!c->workspace || ((uintptr_t)c->workspace & 15)) return RS_ERR_POINTER;
+    const int S = vpf_subblocks(B, n);
+    const VpfLayout f = vpf_layout(B, c->world, S);
+    float* fw = (float*)c->workspace + vp_layout(B, c->world).total;
+    *stat1 = fw + f.stat1;
+    *all_valid = (int*)(fw + f.valid) + B;
+    *S_out = S;
+    *scale = (float)(1.4426950408889634074 / c->temperature);
+    return RS_OK;
+}
+
+int rs_vp_tile_begin(const rs_vp_call* c) {
+    float* stat1; int* all_valid; int S; float scale;
+    const int rc = vp_tile_common(c, &stat1, &all_valid, &S, &scale);
+    if (rc) return rc;
+    const int n = (int)(c->B * S);
+    rs::vpf_tile_begin_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)c->stream>>>(stat1, n, all_valid);
+    return cudaGetLastError() == cudaSuccess ? RS_OK : RS_ERR_CUDA;
+}
+
+int rs_vp_tile_max(const rs_vp_call* c, const float* tile_device, int64_t ld, int64_t col_begin, int64_t ncols) {
+    float* stat1; int* all_valid; int S; float scale;
+    const int rc = vp_tile_common(c, &stat1, &all_valid, &S, &scale);
+    if (rc) return rc;
+    if (!tile_device || ((uintptr_t)tile_device & 3)) return RS_ERR_POINTER;
+    if (ncols <= 0 || col_begin < 0 || col_begin + ncols > c->V_local || ld < ncols) return RS_ERR_VOCAB;
+    const float* pen = c->penalties ? c->penalties + col_begin : nullptr;
+    dim3 grid((unsigned)((ncols + 4095) / 4096), (unsigned)c->B);
+    rs::vpf_tile_max_kernel<<<grid, 256, 0, (cudaStream_t)c->stream>>>(tile_device, (long long)ld, pen, (long long)c->V_local,
+                                                                       (int)ncols, scale, S, stat1);
+    return cudaGetLastError() == cudaSuccess ? RS_OK : RS_ERR_CUDA;
 }
 
 int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {

@@ -45,6 +45,17 @@ class CudaCompute:
         c.presence_penalty, c.repetition_penalty, c.penalty_decay = presence, repetition, decay
         c.rank, c.world = s.rank, s.world
 
+    def tile_begin(self):
+        rc = self.L.rs_vp_tile_begin(C.byref(self.call))
+        if rc != 0:
+            raise RuntimeError(abi.status_string(rc))
+
+    def tile_max(self, tile, col_begin):
+        """tile: (B, ncols) fp32 view (last dimension contiguous) of local columns [col_begin, col_begin + ncols)."""
+        rc = self.L.rs_vp_tile_max(C.byref(self.call), tile.data_ptr(), tile.stride(0), col_begin, tile.shape[1])
+        if rc != 0:
+            raise RuntimeError(abi.status_string(rc))
+
     def stage(self, name, rnd=0):
         rc = self.L.rs_vp_stage(C.byref(self.call), STAGES[name], rnd)
         if rc != 0:
@@ -97,6 +108,7 @@ class VocabParallelSampler:
         # ids of the last call (a decode loop does so when it reads the ids on the host)
         self.defer_check = defer_check
         self._pending = None
+        self._max_from_tiles = False
 
     def release_graphs(self):
         """Drops the recorded CUDA graphs.  Call it before the process group is destroyed (and before the process
@@ -115,11 +127,25 @@ class VocabParallelSampler:
         else:
             out.copy_(inp)
 
+    def begin_tiles(self, logits, states, temperature, top_k, top_p, penalties=None, presence_penalty=0.0,
+                    repetition_penalty=0.0, penalty_decay=0.0):
+        """lm_head epilogue hook: call before the producer hands over the first tile of this step's logits; then
+        `push_tile(tile, col_begin)` per tile as it is produced (any order), then `sample(..., max_from_tiles=True)` with
+        the same arguments.  `logits` is the buffer the tiles end up in (the later stages read it)."""
+        self._tile_args = (logits, states, penalties, float(temperature), int(top_k), float(top_p), float(presence_penalty),
+                           float(repetition_penalty), float(penalty_decay))
+        self.compute.bind(self, *self._tile_args)
+        self.compute.tile_begin()
+
+    def push_tile(self, tile, col_begin):
+        self.compute.tile_max(tile, col_begin)
+
     def _fast_stages(self, penalties):
-        """The device side of the fast protocol: five kernels, three collectives, then the state advance and the penalty
+        """The device side of the fast protocol: four kernels, four collectives, then the state advance and the penalty
         update, which the device applies only if every row was settled."""
         c = self.compute
-        c.stage("f_max")
+        if not self._max_from_tiles:
+            c.stage("f_max")
         self._reduce(self.f_stat1, dist.ReduceOp.MAX)
         c.stage("f_sum")
         self._reduce(self.f_stat2, dist.ReduceOp.SUM)
@@ -179,7 +205,7 @@ class VocabParallelSampler:
         return self._sample_staged(penalties)
 
     def sample(self, logits, states, temperature, top_k, top_p, penalties=None, presence_penalty=0.0,
-               repetition_penalty=0.0, penalty_decay=0.0):
+               repetition_penalty=0.0, penalty_decay=0.0, max_from_tiles=False):
         """logits: this rank's (B, V_local) or (B, T, V_local) fp32 shard; states: replica of setup_rand(seed, B).
         Returns int32 (B,) global token ids, identical on every rank; states / penalties updated in place."""
         assert logits.shape[-1] == self.V_local and logits.dtype == torch.float32
@@ -189,6 +215,7 @@ class VocabParallelSampler:
                      float(repetition_penalty), float(penalty_decay))
         c.bind(self, *bind_args)
         self.last_protocol = "staged"
+        self._max_from_tiles = bool(max_from_tiles) and self.fast and not self.use_graph
         if self.fast:
             ids = self._sample_fast(bind_args, penalties)
             if ids is not None:

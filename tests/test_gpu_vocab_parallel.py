@@ -270,3 +270,70 @@ def test_deferred_check_single_rank(abi):
             got = fixed.clone()
         assert sync.last_protocol == proto
         assert torch.equal(got, want) and torch.equal(st_s, st_l)
+
+
+def test_lm_head_tile_hook_matches_the_max_pass(abi):
+    """The row maxima of the first stage fed tile by tile (as an lm_head epilogue would hand its output over), in a
+    shuffled order and with uneven tile widths, on 2 emulated ranks: same ids, states and penalties as the normal call."""
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    B, V, N = 8, 65536, 2
+    full = make_logits("peaked", B, V, 4, torch)
+    ref_s = [VocabParallelSampler(B, V, r, N) for r in range(N)]
+    hook_s = [VocabParallelSampler(B, V, r, N) for r in range(N)]
+    shards = [full[:, s.col0:s.col0 + s.V_local].contiguous().cuda() for s in ref_s]
+    st_ref = [abi.setup_rand(9, B) for _ in range(N)]
+    st_hook = [abi.setup_rand(9, B) for _ in range(N)]
+    pen_ref = [torch.zeros(B, s.V_local, device="cuda") for s in ref_s]
+    pen_hook = [torch.zeros(B, s.V_local, device="cuda") for s in ref_s]
+    g = torch.Generator().manual_seed(1)
+    for call in range(3):
+        want = emulated_sample(ref_s, shards, st_ref, 0.8, 50, 0.9, pen_ref)
+        # hook path: stage 1 from tiles, the remaining stages as in emulated_sample
+        for r, s in enumerate(hook_s):
+            s.begin_tiles(shards[r], st_hook[r], 0.8, 50, 0.9, penalties=pen_hook[r], presence_penalty=0.1,
+                          repetition_penalty=0.2, penalty_decay=0.5)
+            edges = sorted(set([0, s.V_local] + [int(x) * 4 for x in torch.randint(1, s.V_local // 4, (9,), generator=g)]))
+            tiles = list(zip(edges[:-1], edges[1:]))
+            for i in torch.randperm(len(tiles), generator=g).tolist():
+                a, b_ = tiles[i]
+                s.push_tile(shards[r][:, a:b_], a)
+        # emulate the all-reduce MAX and run the remaining stages
+        stack = torch.stack([s.f_stat1 for s in hook_s]).max(dim=0).values
+        for s in hook_s:
+            s.f_stat1.copy_(stack)
+        for name in ("f_sum",):
+            for s in hook_s:
+                s.compute.stage(name)
+        red = torch.stack([s.f_stat2 for s in hook_s]).sum(dim=0)
+        for s in hook_s:
+            s.f_stat2.copy_(red)
+        for s in hook_s:
+            s.compute.stage("f_extract")
+        for s in hook_s:
+            s.f_gath.copy_(torch.cat([x.f_send for x in hook_s]))
+            s.f_gath_cnt.copy_(torch.cat([x.f_send_cnt for x in hook_s]))
+        for name, rnd in (("f_finish", 0), ("f_advance", 0), ("penalty", 1)):
+            for s in hook_s:
+                s.compute.stage(name, rnd)
+        torch.cuda.synchronize()
+        for r in range(N):
+            assert int(hook_s[r].f_all_valid.item()) == 1
+            assert torch.equal(hook_s[r].f_ids - 1, want[r]), (call, r)
+            assert torch.equal(st_hook[r], st_ref[r]) and torch.equal(pen_hook[r], pen_ref[r])
+
+
+def test_lm_head_tile_hook_through_the_driver(abi):
+    """Single rank, through VocabParallelSampler.sample(max_from_tiles=True)."""
+    from rapid_sampling_b200.vocab_parallel import VocabParallelSampler
+    B, V = 8, 65536
+    shard = make_logits("peaked", B, V, 4, torch).cuda()
+    a, h = VocabParallelSampler(B, V, 0, 1), VocabParallelSampler(B, V, 0, 1)
+    st_a, st_h = abi.setup_rand(9, B), abi.setup_rand(9, B)
+    for call in range(3):
+        want = a.sample(shard, st_a, 0.8, 50, 0.9).clone()
+        h.begin_tiles(shard, st_h, 0.8, 50, 0.9)
+        for c0 in (32768, 0, 49152, 16384):
+            h.push_tile(shard[:, c0:c0 + 16384], c0)
+        got = h.sample(shard, st_h, 0.8, 50, 0.9, max_from_tiles=True).clone()
+        assert h.last_protocol == "fast"
+        assert torch.equal(got, want) and torch.equal(st_a, st_h)
