@@ -17,6 +17,9 @@
 #include "rs_common.cuh"
 #include "rs_rowcta.cuh"
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include <mutex>
 #include <type_traits>
 
@@ -45,6 +48,9 @@ __device__ __forceinline__ float fromkey(uint32_t k) {
 }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 // The xor trees (offsets 16, 8, 4, 2, 1) of N values per lane at once.  While more than one value is left, a lane
@@ -75,11 +81,13 @@ __device__ __forceinline__ void tree_levels(float* m, const int lane) {
 // LPT: virtual lanes per thread.  REP: the call has penalties (sampling.cu:172-438), else not (:517-964).  D: stages of
 // a thread's copy pipeline.  NH: stages per stripe (2: a stage holds half a stripe, which buys twice the stages -- and
 // bytes in flight -- from the same shared memory when two rows with penalties share an SM).  All compile-time, so that
-// the streaming loops carry no tests on them.
+// the streaming loops carry no tests on them.  LOWP: the logits are fp16 or bf16 (p.dtype says which); a group of four
+// is then an 8-byte copy into the first half of the lane's 16-byte slot and is widened exactly to fp32 when it is read.
+// Per-row parameters (p.rows) are a run-time matter: they only replace values that are kernel parameters anyway.
 struct TagFull { static constexpr bool value = true; };
 struct TagRagged { static constexpr bool value = false; };
 
-template <int LPT, bool REP, int D, int NH>
+template <int LPT, bool REP, int D, int NH, bool LOWP>
 __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kernel(const Params p, const RowCtaPlan pl) {
     constexpr int SL = LPT / NH;       // lanes of a thread that one copy stage serves (NH stages make up a stripe)
     constexpr int NT = kLanes / LPT;   // threads; thread t plays virtual lanes j * NT + t
@@ -92,11 +100,37 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     const int b = blockIdx.x;
     const int V = p.V, V4 = V >> 2;
     const int K = (V4 + kLanes - 1) >> 10;   // stripes of 1024 float4 groups
-    const int a_kind = p.kind, a_top_k = p.top_k, a_sel_rank = p.sel_rank;
-    const float a_scale = p.scale, a_top_p = p.top_p;
+    int a_kind = p.kind, a_top_k = p.top_k, a_sel_rank = p.sel_rank;
+    float a_scale = p.scale, a_top_p = p.top_p;
+    if (p.rows) {   // this row's own normalised parameters
+        const RowArgs ra = p.rows[b];
+        a_kind = ra.kind; a_top_k = ra.top_k; a_sel_rank = ra.sel_rank; a_scale = ra.scale; a_top_p = ra.top_p;
+    }
     constexpr bool rep = REP;
     const bool use_cnt = (a_kind != kTopP);
-    const float* lrow = reinterpret_cast<const float*>(p.logits) + (long long)b * p.row_stride;
+    const char* lrow_b = reinterpret_cast<const char*>(p.logits) + (long long)b * p.row_stride * (LOWP ? 2 : 4);
+    const float* lrow = reinterpret_cast<const float*>(lrow_b);      // as such for fp32 logits only
+    const bool is_f16 = LOWP && p.dtype == RS_DTYPE_F16;
+    // four logits of a group / one logit, widened exactly to fp32
+    auto widen4 = [&](const uint2 r) -> float4 {
+        if (is_f16) {
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&r.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&r.y));
+            return make_float4(a.x, a.y, c.x, c.y);
+        }
+        return make_float4(__uint_as_float(r.x << 16), __uint_as_float(r.x & 0xffff0000u), __uint_as_float(r.y << 16),
+                           __uint_as_float(r.y & 0xffff0000u));
+    };
+    auto raw4 = [&](const unsigned char* slot16) -> float4 {        // a lane's 16-byte slot as it was copied
+        if (!LOWP) return *reinterpret_cast<const float4*>(slot16);
+        return widen4(*reinterpret_cast<const uint2*>(slot16));
+    };
+    auto logit1 = [&](int i) -> float {
+        if (!LOWP) return lrow[i];
+        const unsigned short h = reinterpret_cast<const unsigned short*>(lrow_b)[i];
+        if (is_f16) return __half2float(__ushort_as_half(h));
+        return __uint_as_float((uint32_t)h << 16);
+    };
     float* prow = rep ? p.penalties + (long long)b * V : nullptr;
     const int NC = pl.cached, cap = pl.cap;
 
@@ -124,7 +158,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     constexpr uint32_t kPart = kStripeBytes / NH;              // bytes of logits (or of penalties) in a stage
     constexpr uint32_t kStage = REP ? 2 * kPart : kPart;
     const uint32_t sm_ring = smem_addr(ring) + (uint32_t)t * 16u, sm_cache = smem_addr(cache) + (uint32_t)t * 16u;
-    const float4* const gl = reinterpret_cast<const float4*>(lrow) + t;
+    const char* const gl = lrow_b + (size_t)t * (LOWP ? 8 : 16);   // this thread's group of stripe 0, lane j = 0
     const float4* const gp = reinterpret_cast<const float4*>(prow) + t;
     int ik = 0, ih = 0, islot = 0, idir = 1;   // next stripe (and part of it) to request, its stage, the direction of the pass
     // LG / PN: the pass wants the stripe's logits / penalties
@@ -134,7 +168,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
             const uint32_t st = sm_ring + (uint32_t)islot * kStage;
             const bool keep = (ik < NC);
             const uint32_t ldst = keep ? sm_cache + (uint32_t)ik * kStripeBytes : st;
-            const float4* src = gl + (size_t)ik * kLanes;
+            const char* src = gl + (size_t)ik * kLanes * (LOWP ? 8 : 16);
             const float4* psrc = gp + (size_t)ik * kLanes;
             const bool fullk = ik < Kf;
 #pragma unroll
@@ -145,7 +179,10 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                         const int j = h * SL + jj;
                         if (fullk || tail_ok[j]) {
                             // a kept stripe has the stripe's own layout, a stage holds only this part's lanes
-                            if (LG) cp_async16(ldst + (keep ? j : jj) * NT * 16, src + j * NT);
+                            if (LG) {
+                                if (LOWP) cp_async8(ldst + (keep ? j : jj) * NT * 16, src + (size_t)j * NT * 8);
+                                else cp_async16(ldst + (keep ? j : jj) * NT * 16, src + (size_t)j * NT * 16);
+                            }
                             if (PN) cp_async16(st + kPart + jj * NT * 16, psrc + j * NT);
                         }
                     }
@@ -206,7 +243,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
 
     // x of one float4 group as the streaming passes compute it, read from global memory (slow paths only)
     auto xload_global = [&](int g) -> float4 {
-        float4 v = __ldg(reinterpret_cast<const float4*>(lrow) + g);
+        float4 v = LOWP ? widen4(__ldg(reinterpret_cast<const uint2*>(lrow_b) + g)) : __ldg(reinterpret_cast<const float4*>(lrow) + g);
         if (rep) v = scaled4_rep(v, __ldcg(reinterpret_cast<const float4*>(prow) + g), a_scale);
         else v = scaled4(v, a_scale);
         return v;
@@ -231,7 +268,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 for (int jj = 0; jj < SL; jj++) {
                     const int j = h * SL + jj;
                     if (FULLK || tail_ok[j]) {
-                        float4 v = keep ? reinterpret_cast<const float4*>(own)[j * NT + t] : reinterpret_cast<const float4*>(st)[jj * NT + t];
+                        float4 v = keep ? raw4(own + (size_t)(j * NT + t) * 16) : raw4(st + (size_t)(jj * NT + t) * 16);
                         if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
                         else v = scaled4(v, a_scale);
                         tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
@@ -329,7 +366,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 for (int jj = 0; jj < SL; jj++) {
                     const int j = h * SL + jj;
                     if (FULLK || tail_ok[j]) {
-                        float4 v = kept ? reinterpret_cast<const float4*>(own)[j * NT + t] : reinterpret_cast<const float4*>(st)[jj * NT + t];
+                        float4 v = kept ? reinterpret_cast<const float4*>(own)[j * NT + t] : raw4(st + (size_t)(jj * NT + t) * 16);
                         if (!kept) {
                             if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
                             else v = scaled4(v, a_scale);
@@ -853,7 +890,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         const int idn = idxt * 4 + (vt >> 2) * 4 * kLanes + (vt & 3);
         float o0 = 0.f;
         if (idn < V) {
-            const float x = scaled_logit(lrow[idn], rep ? prow[idn] : 0.f, rep, a_scale);
+            const float x = scaled_logit(logit1(idn), rep ? prow[idn] : 0.f, rep, a_scale);
             o0 = exp2f(x - mx) / denom;
         }
         const float o = (o0 < thr) ? 0.f : (o0 == thr) ? (o0 * comp) : o0;
@@ -896,7 +933,15 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     __syncthreads();
     const int token = *s_token;
     stamp(8);
-    if (t == 0) p.out[b] = token;
+    if (t == 0) {
+        p.out[b] = token;
+        if (p.out_prob) {   // the sampled id's probability under the full softmax (its penalty is still the old one here)
+            const float x = scaled_logit(logit1(token), rep ? prow[token] : 0.f, rep, a_scale);
+            p.out_prob[b] = exp2f(x - mx) / denom;
+        }
+        if (p.out_kept) p.out_kept[b] = sum_p;
+    }
+    if (REP && p.out_prob) __syncthreads();     // nobody updates that penalty before it has been read
 
     // ---- penalties: decay everything, add the hit on the sampled id (sampling.cu:427-437); the old values come
     // through the copy pipeline, whose first stripes have been in flight since the second pass ended -------------
@@ -981,9 +1026,9 @@ RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int 
     return pl;
 }
 
-template <int LPT, bool REP, int D, int NH>
+template <int LPT, bool REP, int D, int NH, bool LOWP>
 static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t stream, int smem_optin, bool* attr_done) {
-    auto kern = rowcta_kernel<LPT, REP, D, NH>;
+    auto kern = rowcta_kernel<LPT, REP, D, NH, LOWP>;
     if (!*attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin) != cudaSuccess) return RS_ERR_CUDA;
         *attr_done = true;
@@ -992,19 +1037,26 @@ static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t s
     return cudaGetLastError() == cudaSuccess ? RS_OK : RS_ERR_CUDA;
 }
 
+template <bool LOWP>
+static int rowcta_launch_d(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, bool rep, cudaStream_t stream, int smem_optin,
+                           bool* attr_done) {
+    if (lanes_per_thread == 2)
+        return rep ? rowcta_launch_t<2, true, 3, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 0)
+                   : rowcta_launch_t<2, false, 4, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 1);
+    return rep ? rowcta_launch_t<4, true, 5, 2, LOWP>(p, pl, stream, smem_optin, attr_done + 2)
+               : rowcta_launch_t<4, false, 4, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 3);
+}
+
 int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin) {
     static std::mutex mu;
-    static bool attr_done[64][4] = {};
+    static bool attr_done[64][8] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return RS_ERR_CUDA;
     const bool rep = p.penalties != nullptr;
     if (pl.depth != rowcta_depth(rep, lanes_per_thread) || pl.smem_bytes > smem_optin) return RS_ERR_LIMIT;
     std::lock_guard<std::mutex> lk(mu);
-    if (lanes_per_thread == 2)
-        return rep ? rowcta_launch_t<2, true, 3, 1>(p, pl, stream, smem_optin, &attr_done[dev][0])
-                   : rowcta_launch_t<2, false, 4, 1>(p, pl, stream, smem_optin, &attr_done[dev][1]);
-    return rep ? rowcta_launch_t<4, true, 5, 2>(p, pl, stream, smem_optin, &attr_done[dev][2])
-               : rowcta_launch_t<4, false, 4, 1>(p, pl, stream, smem_optin, &attr_done[dev][3]);
+    if (p.dtype == RS_DTYPE_F32) return rowcta_launch_d<false>(p, pl, lanes_per_thread, rep, stream, smem_optin, attr_done[dev]);
+    return rowcta_launch_d<true>(p, pl, lanes_per_thread, rep, stream, smem_optin, attr_done[dev] + 4);
 }
 
 }  // namespace rs

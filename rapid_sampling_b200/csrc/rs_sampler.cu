@@ -1087,10 +1087,10 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     int sel_rank = 0, cand_slots = 0;
     choose_candidates(V, top_k, top_p, &sel_rank, &cand_slots);
     Plan pl = make_plan(*di, B, (int)V, sel_rank, cand_slots, workspace_bytes);
-    // Large fp32 batches: one CTA per row, several rows per SM.  Needs the scratch rows for its whole-row fallback.
+    // Large batches: one CTA per row, several rows per SM.  Needs the scratch rows for its whole-row fallback.
     {
         const int mode = g_path_override.load();
-        const bool eligible = dtype == RS_DTYPE_F32 && workspace_bytes >= ws_bytes(B, V);
+        const bool eligible = workspace_bytes >= ws_bytes(B, V);
         const bool wanted = (mode == 4) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
         if (eligible && wanted) {
             pl.rowcta = true;
@@ -1178,7 +1178,16 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     if (workspace_bytes < 256 + rab) return RS_ERR_WORKSPACE;
     // rows differ in top_k: the candidate buffer takes the widest size
     const bool allow_cand = g_path_override.load() != 1;
-    const Plan pl = make_plan(*di, B, (int)V, allow_cand ? 8 : 0, allow_cand ? 4 : 0, workspace_bytes - rab);
+    Plan pl = make_plan(*di, B, (int)V, allow_cand ? 8 : 0, allow_cand ? 4 : 0, workspace_bytes - rab);
+    {   // large batches: one CTA per row, as for per-call parameters
+        const int mode = g_path_override.load();
+        const bool eligible = workspace_bytes - rab >= ws_bytes(B, V);
+        const bool wanted = (mode == 4) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        if (eligible && wanted) {
+            pl.rowcta = true;
+            pl.ws = ws_bytes(B, V);
+        }
+    }
     if (workspace_bytes < pl.ws + rab) return RS_ERR_WORKSPACE;
     if (pl.smem && pl.C != 8 && pl.C != 16) return RS_ERR_LIMIT;   // forced widths exist for the per-call entry only
 
@@ -1217,6 +1226,15 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     p.decay = (float)decay;
     p.sel_rank = 0;
     p.cand_slots = pl.cand_slots;
+    if (pl.rowcta) {
+        const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
+        const int lpt = (B <= di->sms) ? 2 : 4;
+        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, allow_cand ? 8 : 0, lpt, budget);
+        rc = rowcta_launch(p, rp, lpt, st, di->smem_optin);
+        if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
+        else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta, per-row)");
+        return rc;
+    }
     if (!pl.smem) return launch_rows<8, false>(p, kSlabOff + pl.cand_slots * (kLanes / 8) * 16, st, *di);
     const int smem = smem_need((int)V, pl.C, pl.cand_slots);
     return pl.C == 8 ? launch_rows<8, true>(p, smem, st, *di) : launch_rows<16, true>(p, smem, st, *di);

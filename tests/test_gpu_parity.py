@@ -315,10 +315,11 @@ def test_sixteen_bit_logits_equal_reference_on_widened_logits(abi, ref, dtype):
     try:
         for kind, B, V, temp, k, p, rep in [("peaked", 16, 151936, 0.8, 50, 0.9, False), ("normal3", 4, 262144, 1.0, -1, 0.3, False),
                                             ("uniform", 4, 32768, 1.0, -1, 0.5, False), ("normal3", 32, 65536, 0.8, 50, 0.9, True),
-                                            ("special", 4, 50304, 1.3, 100, 0.9, False)]:
+                                            ("special", 4, 50304, 1.3, 100, 0.9, False), ("normal3", 200, 32768, 0.8, 50, 0.9, True),
+                                            ("uniform", 160, 16380, 1.0, -1, 0.6, False)]:
             lg16 = make_logits(kind, B, V, 23, torch).to(dtype).cuda()
             lg32 = lg16.float()
-            for mode in (0, 2, 3):
+            for mode in (0, 2, 3, 4):
                 abi.set_path(mode)
                 s_ref, s_our = ref.setup_rand(2, B), abi.setup_rand(2, B)
                 pen_ref = torch.zeros(B, V, device="cuda") if rep else None

@@ -22,7 +22,8 @@ def row_settings(B):
 
 
 @pytest.mark.parametrize("B,V,kind,rep", [(9, 32768, "normal3", False), (9, 65536, "peaked", True), (200, 32768, "normal3", False),
-                                          (170, 16384, "uniform", True), (3, 524288, "normal3", False)])
+                                          (170, 16384, "uniform", True), (3, 524288, "normal3", False),
+                                          (300, 65536, "peaked", True), (130, 65536, "normal3", True), (330, 50300, "normal3", False)])
 def test_rows_equal_one_row_reference_calls(ref, B, V, kind, rep):
     import rapid_sampling_b200 as rs
     lg = make_logits(kind, B, V, 31, torch).cuda()
@@ -47,9 +48,10 @@ def test_rows_equal_one_row_reference_calls(ref, B, V, kind, rep):
             assert torch.equal(pen_o, pen_r)
 
 
-def test_rows_bf16_logits_and_neutral_defaults(ref):
+@pytest.mark.parametrize("B", [12, 160])     # the larger batch runs one CTA per row
+def test_rows_bf16_logits_and_neutral_defaults(ref, B):
     import rapid_sampling_b200 as rs
-    B, V = 12, 65536
+    V = 65536
     lg = make_logits("normal3", B, V, 5, torch).cuda().bfloat16()
     t, k, p = row_settings(B)
     st_o, st_r = rs.setup_rand(3, B), ref.setup_rand(3, B)
@@ -65,10 +67,11 @@ def test_rows_bf16_logits_and_neutral_defaults(ref):
     assert torch.equal(a, b_) and torch.equal(st_a, st_b)
 
 
-def test_rows_probability_and_kept_mass():
+@pytest.mark.parametrize("B", [9, 153])      # the larger batch runs one CTA per row
+def test_rows_probability_and_kept_mass(B):
     import rapid_sampling_b200 as rs
     from oracle import cpu_ref
-    B, V = 9, 32768
+    V = 32768
     lg = make_logits("normal3", B, V, 77, torch)
     t, k, p = row_settings(B)
     ids, prob, kept = rs.batch_sampling_rows(lg.cuda(), rs.setup_rand(1, B), t.cuda(), k.cuda(), p.cuda(), return_prob=True)
@@ -108,12 +111,13 @@ def test_rows_bad_temperature_sets_status_and_spares_other_rows(abi):
                             None, None, ws.data_ptr(), 256, abi.stream()) == abi.abi.RS_ERR_WORKSPACE
 
 
-def test_rows_probability_is_taken_before_the_penalty_update():
+@pytest.mark.parametrize("B", [12, 300])     # the larger batch runs one CTA per row
+def test_rows_probability_is_taken_before_the_penalty_update(B):
     """With penalties, the reported probability of the sampled id must come from the penalties as they were BEFORE
     the call (the same values the softmax ran on), on every call of a chain."""
     import rapid_sampling_b200 as rs
     from oracle import cpu_ref
-    B, V = 12, 32768
+    V = 32768
     lg = make_logits("peaked", B, V, 13, torch)
     t, k, p = row_settings(B)
     pen = torch.zeros(B, V, device="cuda")
