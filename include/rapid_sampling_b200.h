@@ -46,7 +46,9 @@ typedef struct rs_trace {
     uint32_t path;   /* 0 = cutoff found on the candidate list, 1 = whole-row search */
     uint32_t ncand;  /* elements on the candidate list */
     uint32_t t_ns[10]; /* ns since kernel entry of the owner CTA's thread 0 at: 1 row resident, 2 pass 1, 3 exchange,
-                          4 pass 2, 5 exchange, 6 search+recount, 7 lane pick, 8 element pick */
+                          4 pass 2, 5 exchange, 6 search+recount, 7 lane pick, 8 element pick, 9 end.  Entry 0: rounds of
+                          the search that needed block-wide sums (bits 0-15); the one-CTA-per-row kernel adds the outcome
+                          of its one-warp integer search in bits 16-19 (1 settled, 2 list too short, 0 undecided or not tried) */
 } rs_trace;
 
 /*
@@ -268,8 +270,9 @@ int rs_set_cluster_override(int cluster_ctas);
 
 /* Strategy override: 0 = automatic, 1 = always search the whole row (no candidate shortcut), 2 = always the
  * streaming cluster variant, 3 = always the on-chip cluster variant when the row fits, 4 = always one CTA per row
- * (fp32 logits with a full-size workspace; other calls keep the automatic choice).  Results are identical;
- * testing / benchmarking aid.  Returns the previous value. */
+ * (calls with a full-size workspace; other calls keep the automatic choice), 5 = as 4 with the exact block-wide search
+ * only (no one-warp search on integer masses first).  Results are identical; testing / benchmarking aid.  Returns the
+ * previous value. */
 int rs_set_path_override(int mode);
 
 /* Number of sampler kernels launched through this library since it was loaded. */

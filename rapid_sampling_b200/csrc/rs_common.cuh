@@ -77,7 +77,7 @@ __device__ __forceinline__ void slab_pass(const Row<C, SMEM>& row, int& n, const
     const int slots = (n + 3) >> 2;
     float b0 = -1.f, b1 = -1.f, b2 = -1.f, b3 = -1.f;
     int q = 0;
-#pragma unroll 2
+#pragma unroll ((SMEM || COMPACT || C > 1) ? 2 : 4)
     for (int s = 0; s < slots; s++) {
         const float4 v = row.ld(s);
         const float e[4] = {v.x, v.y, v.z, v.w};

@@ -9,8 +9,9 @@
 //     16-byte copies (cp.async) into shared memory: several stripes in flight per thread, no registers held by loads
 //     in flight, and no barrier of any kind in the streaming passes.  The first stripes stay on chip as scaled logits,
 //     so the second pass re-reads only the rest (from L2);
-//   * the cutoff search runs on the short candidate list (first entries in registers) with one CTA barrier per
-//     evaluated round;
+//   * the cutoff search runs on the short candidate list: first in one warp on exact integer masses, which settles
+//     every row whose masses stay clear of top_p by more than the fp32 rounding of the reference's sums (nearly all);
+//     else with the reference's fp32 sums, block-wide, one CTA barrier per evaluated round;
 //   * with penalties, the first stripes of the update pass are already in flight while the search runs.
 // Rows whose candidate list cannot settle the cutoff search the whole row on a global scratch row, dropping, in place
 // and order-preserving, every element below the current lower bound as the bracket rises.
@@ -35,7 +36,9 @@ constexpr int kOffWtot = 128;      // 32 warp totals of a scan
 constexpr int kOffBoxC = 256;      // 2 x [16 physical warps][8 words]
 constexpr int kOffBox = 1280;      // 2 x [4 values][32 virtual warps] floats, value-major
 constexpr int kBoxBytes = 4 * 32 * 4;
-static_assert(kOffBox + 2 * kBoxBytes <= kRowCtaFixedSmem, "fixed shared-memory area too small");
+constexpr int kOffQuick = kOffBox + 2 * kBoxBytes;   // the row's candidates as one unordered list of (bits of p, p in units of 2^-30)
+constexpr int kQuickCap = 512;
+static_assert(kOffQuick + kQuickCap * 8 <= kRowCtaFixedSmem, "fixed shared-memory area too small");
 constexpr int kStripeBytes = 16384;   // 1024 float4 groups: one group per virtual lane
 
 // order-preserving map float -> u32 (no NaN here: inputs are sanitised), so that integer warp reductions serve floats
@@ -140,9 +143,12 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     float* cand = reinterpret_cast<float*>(smem + pl.off_cand);          // entry i of virtual lane v at cand[i * 1024 + v]
     unsigned char* ring = smem + pl.off_ring;                            // D stages of pl.stage_bytes
     unsigned char* cache = smem + pl.off_cache;                          // NC stripes of scaled logits
+    uint32_t* s_ncl = reinterpret_cast<uint32_t*>(smem + kOffScal + 8);  // entries of the unordered candidate list
+    uint2* qlist = reinterpret_cast<uint2*>(smem + kOffQuick);
     if (t == 0) {
         *s_idxt = 0;
         *s_token = 0;
+        *s_ncl = 0u;
     }
 
     // ---- the thread's private copy pipeline ------------------------------------------------------------------
@@ -345,10 +351,9 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                     (v.w >= beta_e ? v.w : 0.f);
         }
     };
-    auto pass2 = [&](const bool last) -> bool {
-        emin = INFINITY; emax = -INFINITY; csum = 0.f; ns = 0;
-#pragma unroll
-        for (int j = 0; j < LPT; j++) { acc[j] = 0.f; nc[j] = 0; }
+    // One pass over the row as scaled logits x, stripes in ascending order (every lane's chain order): the kept
+    // stripes from shared memory, the rest through the copy pipeline (which begin_pass(NC, 1, ...) has started).
+    auto stream_x = [&](auto&& fn) {
         int cslot = 0;
         auto stripe = [&](auto full_tag, const int k) {
             constexpr bool FULLK = decltype(full_tag)::value;
@@ -371,13 +376,19 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                             if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
                             else v = scaled4(v, a_scale);
                         }
-                        pass2_group(j, v);
+                        fn(j, k, v);
                     }
                 }
             }
         };
         for (int k = 0; k < Kf; k++) stripe(TagFull(), k);
         if (rem) stripe(TagRagged(), Kf);
+    };
+    auto pass2 = [&](const bool last) -> bool {
+        emin = INFINITY; emax = -INFINITY; csum = 0.f; ns = 0;
+#pragma unroll
+        for (int j = 0; j < LPT; j++) { acc[j] = 0.f; nc[j] = 0; }
+        stream_x([&](const int j, const int, const float4 v) { pass2_group(j, v); });
         stamp(4);
         float* box = box_of(phase);
         uint32_t* boxc = boxc_of(phase);
@@ -659,6 +670,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     uint32_t beta_p = 0u;
     uint32_t list_total = (uint32_t)V, list_left = 0u;
     bool whole = false;
+    int quick = 0;           // outcome of the one-warp search on integer masses: 0 not settled that way, 1 settled, 2 list too short
     auto lane_eval = [&](const float (&f)[4], uint32_t lo, uint32_t hi, uint32_t cnt_lo, float (&m)[NV], uint32_t (&c)[4],
                          uint32_t& mn, uint32_t& mxv) {
         c[0] = c[1] = c[2] = c[3] = 0u;
@@ -711,16 +723,35 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     for (int attempt = cand_ok ? 0 : 1; attempt < 2; attempt++) {
         whole = (attempt == 1);
         if (!whole) {
-            int m_max = 0;
+            int m_max = 0, mine = 0;
 #pragma unroll
             for (int j = 0; j < LPT; j++) {
                 m_own[j] = min(nc[j], cap);
                 m_max = max(m_max, m_own[j]);
+                mine += m_own[j];
+            }
+            // a place for this thread's entries in the row's unordered list (short lists only)
+            const bool listed = pl.quick && ncand <= (uint32_t)kQuickCap;
+            uint32_t at = 0u;
+            if (listed) {
+                uint32_t incl = (uint32_t)mine;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const uint32_t v = __shfl_up_sync(FULL, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                uint32_t base = 0u;
+                if (lane == 31 && incl) base = atomicAdd(s_ncl, incl);
+                at = __shfl_sync(FULL, base, 31) + incl - (uint32_t)mine;
+            }
+#pragma unroll
+            for (int j = 0; j < LPT; j++) {
 #pragma unroll
                 for (int i = 0; i < CR; i++) creg[j][i] = -1.f;
                 for (int i = 0; i < m_own[j]; i++) {
                     const float q = cand[i * kLanes + j * NT + t] / denom;
                     cand[i * kLanes + j * NT + t] = q;
+                    if (listed) qlist[at++] = make_uint2(__float_as_uint(q), __float2uint_rn(q * 1073741824.f));
 #pragma unroll
                     for (int r = 0; r < CR; r++)
                         if (i == r) creg[j][r] = q;
@@ -728,6 +759,78 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
             }
             long_lists = __any_sync(FULL, m_max > CR);
             beta_p = __float_as_uint(beta_e / denom);
+            if (listed) {
+                // ---- the whole search in warp 0, on integer masses.  The reference's loop only ever asks whether a mass
+                // is below or above top_p (sampling.cu:598, :618-651).  The sum of the admitted p in units of 2^-30 is exact
+                // up to half a unit per entry and does not depend on the order; the reference's fp32 value differs from
+                // the true sum by at most one rounding per addition on the longest path (cap in a lane, 5 in the warp
+                // tree, 31 over the warps).  Outside that margin around top_p the answer is certain and the loop is
+                // replayed here without any exchange; inside it (or when a count does not already decide), the exact
+                // search below takes over from the start.
+                __syncthreads();
+                if (pw == 0) {
+                    const uint32_t n = min(*s_ncl, (uint32_t)kQuickCap);
+                    // entries up to the next multiple of 256 read as "never admitted", so that the loops need no bounds
+                    for (uint32_t i = n + (uint32_t)lane; i < ((n + 255u) & ~255u); i += 32u) qlist[i] = make_uint2(0u, 0u);
+                    __syncwarp();
+                    const uint32_t margin = (uint32_t)((cap + 38) * 66 + kQuickCap / 2 + 8);
+                    const uint32_t tp_lo = __float2uint_rd(top_p * 1073741824.f), tp_hi = __float2uint_ru(top_p * 1073741824.f);
+                    const uint32_t ustar = beta_p + 1u;
+                    uint32_t l_left = __float_as_uint(pmin), l_right = __float_as_uint(pmax) + 1u, l_rounds = 0u;
+                    uint32_t cnt_x = (uint32_t)V;
+                    bool above_x = 1.0f > top_p;        // the reference starts from mass 1
+                    int verdict = 1;                     // 1 settled, 2 the list cannot settle it, 0 uncertain
+                    for (;;) {
+                        const bool go = use_cnt ? (cnt_x > top_k || above_x) : above_x;
+                        if (!(go && l_left < l_right - 1u) || l_rounds >= 64u) break;
+                        l_rounds++;
+                        const uint32_t pz = (l_left + l_right) >> 1, py = (l_left + pz) >> 1, pwv = (pz + l_right) >> 1;
+                        const uint32_t pv[3] = {py, pz, pwv};
+                        const uint32_t e0 = max(py, ustar), e1 = max(pz, ustar), e2 = max(pwv, ustar);
+                        uint32_t c0 = 0u, c1 = 0u, c2 = 0u, q0 = 0u, q1 = 0u, q2 = 0u;
+                        for (uint32_t i0 = 0u; i0 < n; i0 += 256u) {
+                            uint2 en[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) en[i] = qlist[i0 + (uint32_t)(i * 32 + lane)];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                if (en[i].x >= e0) { c0++; q0 += en[i].y; }
+                                if (en[i].x >= e1) { c1++; q1 += en[i].y; }
+                                if (en[i].x >= e2) { c2++; q2 += en[i].y; }
+                            }
+                        }
+                        const uint32_t cnt[3] = {__reduce_add_sync(FULL, c0), __reduce_add_sync(FULL, c1), __reduce_add_sync(FULL, c2)};
+                        const uint32_t qm[3] = {__reduce_add_sync(FULL, q0), __reduce_add_sync(FULL, q1), __reduce_add_sync(FULL, q2)};
+                        bool ok[3], above[3], bad = false, unsure = false;
+#pragma unroll
+                        for (int i = 0; i < 3; i++) {
+                            const bool lt = qm[i] + margin < tp_lo, gt = qm[i] > tp_hi + margin;
+                            const bool by_cnt = use_cnt && cnt[i] > top_k;
+                            unsure = unsure || (!lt && !gt && !by_cnt);
+                            above[i] = gt;
+                            const bool below = pv[i] <= beta_p;
+                            const bool exceeds = by_cnt || gt;
+                            const bool pass = (!use_cnt || cnt[i] < top_k) && lt;
+                            ok[i] = !below && pass;
+                            bad = bad || (below && !exceeds);
+                        }
+                        if (unsure) { verdict = 0; break; }
+                        if (bad) { verdict = 2; break; }
+                        const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
+                        const uint32_t nl = s0 ? l_left : s1 ? pv[0] : s2 ? pv[1] : pv[2];
+                        const uint32_t nr = s0 ? pv[0] : s1 ? pv[1] : s2 ? pv[2] : l_right;
+                        cnt_x = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
+                        above_x = s0 ? above_x : s1 ? above[0] : s2 ? above[1] : above[2];
+                        l_left = nl; l_right = nr;
+                    }
+                    if (verdict == 1 && !(l_left > beta_p)) verdict = 2;
+                    if (lane == 0) { s_fin[0] = l_left; s_fin[1] = l_right; s_fin[2] = l_rounds; s_fin[7] = (uint32_t)verdict; }
+                }
+                __syncthreads();
+                quick = (int)s_fin[7];
+                if (quick == 1) { left = s_fin[0]; right = s_fin[1]; rounds = s_fin[2]; }
+                __syncthreads();     // everybody has read the outcome before the exact search may reuse the area
+            }
         } else {
             if (emin == emax) {
                 // every element has the same probability: the reference's loop never starts, the whole row ties
@@ -741,23 +844,24 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 break;
             }
             // p = exp2f(x - max) / denom (sampling.cu:573-590) into the global scratch row
+            // (one more pass of the copy pipeline over the row; the penalty stripes requested ahead are given up)
             list_left = __float_as_uint(pmin);
 #pragma unroll
             for (int j = 0; j < LPT; j++) {
                 const int vl = j * NT + t;
-                const int Kt = (vl < V4) ? ((V4 - vl + kLanes - 1) >> 10) : 0;
-                n_row[j] = Kt * 4;
-                row.tg = vl;
-                for (int sidx = 0; sidx < Kt; sidx++) {
-                    float4 v = (sidx < NC) ? reinterpret_cast<const float4*>(cache + (size_t)sidx * kStripeBytes)[vl]
-                                           : xload_global(sidx * kLanes + vl);
-                    v.x = exp2f(v.x - mx) / denom; v.y = exp2f(v.y - mx) / denom;
-                    v.z = exp2f(v.z - mx) / denom; v.w = exp2f(v.w - mx) / denom;
-                    row.st(sidx, v);
-                }
+                n_row[j] = (vl < V4) ? ((V4 - vl + kLanes - 1) >> 10) * 4 : 0;
             }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            begin_pass(NC, 1, Yes(), Pen());
+            stream_x([&](const int j, const int k, float4 v) {
+                v.x = exp2f(v.x - mx) / denom; v.y = exp2f(v.y - mx) / denom;
+                v.z = exp2f(v.z - mx) / denom; v.w = exp2f(v.w - mx) / denom;
+                row.slab[(size_t)k * kLanes + j * NT + t] = v;
+            });
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        const bool ok = run_search(lane_eval, !whole, beta_p, !whole && use_cnt && nstrict > top_k, nstrict);
+        if (!whole && quick == 2) continue;
+        const bool ok = (!whole && quick == 1) ? true : run_search(lane_eval, !whole, beta_p, !whole && use_cnt && nstrict > top_k, nstrict);
         const float thr_found = __uint_as_float(left);
         if (!whole) {
             if (!ok) continue;
@@ -776,6 +880,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         for (int j = 0; j < LPT; j++) {
             row.tg = j * NT + t;
             const int slots = (n_row[j] + 3) >> 2;
+#pragma unroll 4
             for (int sidx = 0; sidx < slots; sidx++) {
                 const float4 v = row.ld(sidx);
                 const float e[4] = {v.x, v.y, v.z, v.w};
@@ -786,6 +891,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 }
             }
         }
+        if (REP) begin_pass(K - 1, -1, No(), Yes());   // the update pass's first penalty stripes again
     }
     stamp(6);
     const bool early_exit = left < right - 1u;
@@ -794,7 +900,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     // totals at the threshold (sampling.cu:657-680): lane 31 of a descending-offset scan holds the tree value
     float sgtp;
     uint32_t seqk, sgtk;
-    if (path == 0 && !early_exit) {
+    if (path == 0 && !early_exit && quick != 1) {
         sgtp = conv_mass;
         sgtk = conv_cnt;
         seqk = conv_left_cnt - conv_cnt;
@@ -994,7 +1100,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         tr.ncand = ncand;
 #pragma unroll
         for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
-        tr.t_ns[0] = n_eval;
+        tr.t_ns[0] = n_eval | ((uint32_t)quick << 16) | (ncand <= (uint32_t)kQuickCap ? 0x100000u : 0u);
         p.dbg_trace[b] = tr;
     }
 }
@@ -1023,6 +1129,7 @@ RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int 
     pl.cached = keep < 0 ? 0 : keep;
     pl.off_cache = pl.off_ring + pl.depth * pl.stage_bytes;
     pl.smem_bytes = pl.off_cache + pl.cached * kStripeBytes;
+    pl.quick = 1;
     return pl;
 }
 

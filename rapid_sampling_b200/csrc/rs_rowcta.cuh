@@ -6,7 +6,7 @@ namespace rs {
 
 struct Params;
 
-constexpr int kRowCtaFixedSmem = 2304;   // scalars, scan totals and the two exchange boxes ahead of the candidate lists
+constexpr int kRowCtaFixedSmem = 6400;   // scalars, scan totals, the two exchange boxes and the unordered candidate list ahead of the per-lane lists
 
 // How a row-CTA launch lays out its dynamic shared memory.
 struct RowCtaPlan {
@@ -16,6 +16,7 @@ struct RowCtaPlan {
     int stage_bytes;
     int off_cand, off_ring, off_cache;
     int smem_bytes;
+    int quick;         // 1: try the one-warp search on integer masses first (0: test instrumentation, exact search only)
 };
 
 RowCtaPlan rowcta_plan(int V, bool with_penalties, int sel_rank, int lanes_per_thread, int smem_budget);

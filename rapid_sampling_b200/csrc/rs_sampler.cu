@@ -1091,7 +1091,7 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     {
         const int mode = g_path_override.load();
         const bool eligible = workspace_bytes >= ws_bytes(B, V);
-        const bool wanted = (mode == 4) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        const bool wanted = (mode == 4 || mode == 5) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
         if (eligible && wanted) {
             pl.rowcta = true;
             pl.ws = ws_bytes(B, V);
@@ -1135,7 +1135,8 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
         // up to 148 rows: one CTA per SM with all of its shared memory; more: two CTAs share an SM
         const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
         const int lpt = (B <= di->sms) ? 2 : 4;
-        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, lpt, budget);
+        RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, lpt, budget);
+        if (g_path_override.load() == 5) rp.quick = 0;
         rc = rowcta_launch(p, rp, lpt, st, di->smem_optin);
         if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
         else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta)");
@@ -1182,7 +1183,7 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     {   // large batches: one CTA per row, as for per-call parameters
         const int mode = g_path_override.load();
         const bool eligible = workspace_bytes - rab >= ws_bytes(B, V);
-        const bool wanted = (mode == 4) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        const bool wanted = (mode == 4 || mode == 5) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
         if (eligible && wanted) {
             pl.rowcta = true;
             pl.ws = ws_bytes(B, V);
@@ -1229,7 +1230,8 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     if (pl.rowcta) {
         const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
         const int lpt = (B <= di->sms) ? 2 : 4;
-        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, allow_cand ? 8 : 0, lpt, budget);
+        RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, allow_cand ? 8 : 0, lpt, budget);
+        if (g_path_override.load() == 5) rp.quick = 0;
         rc = rowcta_launch(p, rp, lpt, st, di->smem_optin);
         if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
         else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta, per-row)");
@@ -1487,7 +1489,7 @@ int rs_set_cluster_override(int cluster_ctas) {
 }
 
 int rs_set_path_override(int mode) {
-    return (mode >= 0 && mode <= 4) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
+    return (mode >= 0 && mode <= 5) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
 }
 
 uint64_t rs_kernel_launch_count(void) { return rs::g_launches.load(); }

@@ -66,7 +66,7 @@ def test_ids_and_states_bit_identical_to_reference_kernel(abi, ref, kind, B, V, 
     abi.set_cluster(0)
     lg = make_logits(kind, B, V, seed, torch).cuda()
     try:
-        for mode in (0, 1, 2, 3, 4):               # automatic / whole-row search only / streaming / on-chip / one CTA per row
+        for mode in (0, 1, 2, 3, 4, 5):            # automatic / whole-row search only / streaming / on-chip / one CTA per row / the same, exact search only
             abi.set_path(mode)
             s_ref, s_our = ref.setup_rand(seed, B), abi.setup_rand(seed, B)
             for call in range(3):                  # consecutive calls advance the states
@@ -100,6 +100,37 @@ def test_both_search_strategies_are_exercised(abi):
         for x, y in zip(tr, tr_b):
             assert y.path == 1 and x.left == y.left and x.rounds == y.rounds and x.idxt == y.idxt
             assert x.sum_p == y.sum_p and x.comp == y.comp and x.seqk == y.seqk and x.sgtk == y.sgtk
+
+
+def test_row_cta_integer_search_and_its_hand_over_to_exact_sums(abi, ref):
+    """The one-CTA-per-row kernel first runs the search in one warp on exact integer masses and keeps the result only
+    if no mass came within the fp32 rounding of the reference's sums of top_p.  Ordinary rows must be settled that
+    way; with top_p set to the very mass of a prefix of the sorted row the integer search must stand back and the
+    block-wide search on fp32 sums must give the reference's ids, trace for trace."""
+    B, V = 6, 32768
+    lg = make_logits("peaked", B, V, 3, torch).cuda()
+    outcome = lambda t: (t.t_ns[0] >> 16) & 0xf
+    try:
+        abi.set_path(4)
+        _, probs, tr = abi.sample(lg, abi.setup_rand(3, B), 0.8, 50, 0.9, debug=True)
+        assert all(outcome(t) == 1 and t.path == 0 for t in tr), [(outcome(t), t.path) for t in tr]
+        top = torch.sort(probs[0], descending=True).values[:3].cpu()
+        stood_back = 0
+        for top_p in (float(top[0]), float(top[0] + top[1]), float((top[0] + top[1]) + top[2])):
+            res = {}
+            for mode in (4, 5):
+                abi.set_path(mode)
+                s_ref, s_our = ref.setup_rand(5, B), abi.setup_rand(5, B)
+                want = ref.batch_sampling_temperature_topk_topp(lg, s_ref, 0.8, 50, top_p)
+                got, _, tr = abi.sample(lg, s_our, 0.8, 50, top_p, debug=True)
+                assert torch.equal(got, want) and torch.equal(s_our, s_ref), (top_p, mode)
+                res[mode] = [(t.left, t.rounds, t.sum_p, t.comp, t.seqk, t.sgtk, t.idxt) for t in tr]
+                if mode == 4:
+                    stood_back += int(outcome(tr[0]) == 0 and tr[0].path == 0)
+            assert res[4] == res[5], top_p
+        assert stood_back >= 2
+    finally:
+        abi.set_path(0)
 
 
 @pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
@@ -319,7 +350,7 @@ def test_sixteen_bit_logits_equal_reference_on_widened_logits(abi, ref, dtype):
                                             ("uniform", 160, 16380, 1.0, -1, 0.6, False)]:
             lg16 = make_logits(kind, B, V, 23, torch).to(dtype).cuda()
             lg32 = lg16.float()
-            for mode in (0, 2, 3, 4):
+            for mode in (0, 2, 3, 4, 5):
                 abi.set_path(mode)
                 s_ref, s_our = ref.setup_rand(2, B), abi.setup_rand(2, B)
                 pen_ref = torch.zeros(B, V, device="cuda") if rep else None
