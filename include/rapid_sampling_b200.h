@@ -270,9 +270,9 @@ int rs_set_cluster_override(int cluster_ctas);
 
 /* Strategy override: 0 = automatic, 1 = always search the whole row (no candidate shortcut), 2 = always the
  * streaming cluster variant, 3 = always the on-chip cluster variant when the row fits, 4 = always one CTA per row
- * (calls with a full-size workspace; other calls keep the automatic choice), 5 = as 4 with the exact block-wide search
- * only (no one-warp search on integer masses first).  Results are identical; testing / benchmarking aid.  Returns the
- * previous value. */
+ * (calls with a full-size workspace; other calls keep the automatic choice), 5 = as 4 and 6 = as 0, but with the exact
+ * search on fp32 sums only (no one-warp search on integer masses first).  Results are identical; testing / benchmarking
+ * aid.  Returns the previous value. */
 int rs_set_path_override(int mode);
 
 /* Number of sampler kernels launched through this library since it was loaded. */

@@ -29,6 +29,7 @@ struct Params {
     const struct RowArgs* rows;   // per-row parameters (ROWP kernels only), else null
     float* out_prob;         // optional B: probability of the sampled id (ROWP kernels only)
     float* out_kept;         // optional B: kept probability mass the id was drawn from (ROWP kernels only)
+    int quick;               // 1: try the one-warp search on integer masses first; 0 (test instrumentation): exact search only
 };
 
 // Normalised parameters of one row, made on the device from the caller's per-row tensors.
@@ -44,7 +45,9 @@ constexpr int kXStride = 12;                     // words between two warps' rec
 constexpr int kMboxOff = 0;                      // 2 buffers of [32 warps][kXStride] words
 constexpr int kMboxBuf = kXStride * 32 * 4;
 constexpr int kMiscOff = 2 * kMboxBuf;           // mbarriers, small scalars, 32 warp totals
-constexpr int kSlabOff = kMiscOff + 256;
+constexpr int kQuickCap = 512;                   // longest candidate list the one-warp search takes
+constexpr int kQuickOff = kMiscOff + 256;        // the row's candidates as one unordered list of (bits of p, p in units of 2^-30)
+constexpr int kSlabOff = kQuickOff + kQuickCap * 8;
 constexpr uint32_t kDefaultWaitPolls = 1u << 22;
 
 __host__ __device__ constexpr int slab_bytes(int V, int C) { return ((V / 4 + 1023) / 1024) * (1024 / C) * 16; }
@@ -110,6 +113,79 @@ __device__ __forceinline__ void slab_pass(const Row<C, SMEM>& row, int& n, const
     m[0] = my; m[1] = mz; m[2] = mw; m[3] = 0.f;
     c01 = cy | (cz << 16);
     c23 = cw;
+}
+
+// ---- the cutoff search of a whole row's candidate list in ONE warp, on integer masses ---------------------------
+// The reference's loop only ever asks whether a mass is below or above top_p (sampling.cu:598, :618-651).  `list`
+// holds every candidate of the row as (bits of p, p in units of 2^-30), in any order: the sum of the admitted
+// entries' second words is exact up to half a unit per entry and does not depend on the order.  The reference's fp32
+// value differs from the true sum by at most one rounding per addition on the longest path (`depth`: the entries of
+// one lane, 5 in the warp tree, 31 over the warps).  Outside that margin around top_p the answer is certain and the
+// loop is replayed here -- same pivots, same tests, same bracket updates -- without any exchange; inside it (unless a
+// count decides the test anyway) the verdict is 0 and the caller runs the exact search from the start.
+// Pivots at or below beta_p are answered by the set {p > beta_p}, as in the exact search on a candidate list.
+// All 32 lanes call this with the same arguments; `list` must be readable up to the next multiple of 256 entries
+// (entries from n on are overwritten with "never admitted").
+// Verdict: 1 settled (left / right / rounds are the reference's), 2 the list cannot settle the cutoff, 0 undecided.
+__device__ __forceinline__ int quick_search(uint2* list, const uint32_t n, const int lane, const int depth, const bool use_cnt,
+                                            const uint32_t top_k, const float top_p, const uint32_t beta_p, const float pmin,
+                                            const float pmax, const uint32_t V, uint32_t& left, uint32_t& right, uint32_t& rounds) {
+    constexpr unsigned FULLW = 0xffffffffu;
+    for (uint32_t i = n + (uint32_t)lane; i < ((n + 255u) & ~255u); i += 32u) list[i] = make_uint2(0u, 0u);
+    __syncwarp();
+    const uint32_t margin = (uint32_t)(depth * 66 + kQuickCap / 2 + 8);
+    const uint32_t tp_lo = __float2uint_rd(top_p * 1073741824.f), tp_hi = __float2uint_ru(top_p * 1073741824.f);
+    const uint32_t ustar = beta_p + 1u;
+    uint32_t l_left = __float_as_uint(pmin), l_right = __float_as_uint(pmax) + 1u, l_rounds = 0u;
+    uint32_t cnt_x = V;
+    bool above_x = 1.0f > top_p;        // the reference starts from mass 1
+    int verdict = 1;
+    for (;;) {
+        const bool go = use_cnt ? (cnt_x > top_k || above_x) : above_x;
+        if (!(go && l_left < l_right - 1u) || l_rounds >= 64u) break;
+        l_rounds++;
+        const uint32_t pz = (l_left + l_right) >> 1, py = (l_left + pz) >> 1, pwv = (pz + l_right) >> 1;
+        const uint32_t pv[3] = {py, pz, pwv};
+        const uint32_t e0 = max(py, ustar), e1 = max(pz, ustar), e2 = max(pwv, ustar);
+        uint32_t c0 = 0u, c1 = 0u, c2 = 0u, q0 = 0u, q1 = 0u, q2 = 0u;
+        for (uint32_t i0 = 0u; i0 < n; i0 += 256u) {
+            uint2 en[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) en[i] = list[i0 + (uint32_t)(i * 32 + lane)];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (en[i].x >= e0) { c0++; q0 += en[i].y; }
+                if (en[i].x >= e1) { c1++; q1 += en[i].y; }
+                if (en[i].x >= e2) { c2++; q2 += en[i].y; }
+            }
+        }
+        const uint32_t cnt[3] = {__reduce_add_sync(FULLW, c0), __reduce_add_sync(FULLW, c1), __reduce_add_sync(FULLW, c2)};
+        const uint32_t qm[3] = {__reduce_add_sync(FULLW, q0), __reduce_add_sync(FULLW, q1), __reduce_add_sync(FULLW, q2)};
+        bool ok[3], above[3], bad = false, unsure = false;
+#pragma unroll
+        for (int i = 0; i < 3; i++) {
+            const bool lt = qm[i] + margin < tp_lo, gt = qm[i] > tp_hi + margin;
+            const bool by_cnt = use_cnt && cnt[i] > top_k;
+            unsure = unsure || (!lt && !gt && !by_cnt);
+            above[i] = gt;
+            const bool below = pv[i] <= beta_p;
+            const bool exceeds = by_cnt || gt;
+            const bool pass = (!use_cnt || cnt[i] < top_k) && lt;
+            ok[i] = !below && pass;
+            bad = bad || (below && !exceeds);
+        }
+        if (unsure) { verdict = 0; break; }
+        if (bad) { verdict = 2; break; }
+        const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
+        const uint32_t nl = s0 ? l_left : s1 ? pv[0] : s2 ? pv[1] : pv[2];
+        const uint32_t nr = s0 ? pv[0] : s1 ? pv[1] : s2 ? pv[2] : l_right;
+        cnt_x = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
+        above_x = s0 ? above_x : s1 ? above[0] : s2 ? above[1] : above[2];
+        l_left = nl; l_right = nr;
+    }
+    if (verdict == 1 && !(l_left > beta_p)) verdict = 2;
+    left = l_left; right = l_right; rounds = l_rounds;
+    return verdict;
 }
 
 // Sanitised scaled logit with the common case (finite product) kept to a multiply and a compare.

@@ -37,7 +37,6 @@ constexpr int kOffBoxC = 256;      // 2 x [16 physical warps][8 words]
 constexpr int kOffBox = 1280;      // 2 x [4 values][32 virtual warps] floats, value-major
 constexpr int kBoxBytes = 4 * 32 * 4;
 constexpr int kOffQuick = kOffBox + 2 * kBoxBytes;   // the row's candidates as one unordered list of (bits of p, p in units of 2^-30)
-constexpr int kQuickCap = 512;
 static_assert(kOffQuick + kQuickCap * 8 <= kRowCtaFixedSmem, "fixed shared-memory area too small");
 constexpr int kStripeBytes = 16384;   // 1024 float4 groups: one group per virtual lane
 
@@ -731,7 +730,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 mine += m_own[j];
             }
             // a place for this thread's entries in the row's unordered list (short lists only)
-            const bool listed = pl.quick && ncand <= (uint32_t)kQuickCap;
+            const bool listed = p.quick && ncand <= (uint32_t)kQuickCap;
             uint32_t at = 0u;
             if (listed) {
                 uint32_t incl = (uint32_t)mine;
@@ -760,71 +759,13 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
             long_lists = __any_sync(FULL, m_max > CR);
             beta_p = __float_as_uint(beta_e / denom);
             if (listed) {
-                // ---- the whole search in warp 0, on integer masses.  The reference's loop only ever asks whether a mass
-                // is below or above top_p (sampling.cu:598, :618-651).  The sum of the admitted p in units of 2^-30 is exact
-                // up to half a unit per entry and does not depend on the order; the reference's fp32 value differs from
-                // the true sum by at most one rounding per addition on the longest path (cap in a lane, 5 in the warp
-                // tree, 31 over the warps).  Outside that margin around top_p the answer is certain and the loop is
-                // replayed here without any exchange; inside it (or when a count does not already decide), the exact
-                // search below takes over from the start.
+                // ---- first try: the whole search in warp 0, on integer masses (quick_search)
                 __syncthreads();
                 if (pw == 0) {
-                    const uint32_t n = min(*s_ncl, (uint32_t)kQuickCap);
-                    // entries up to the next multiple of 256 read as "never admitted", so that the loops need no bounds
-                    for (uint32_t i = n + (uint32_t)lane; i < ((n + 255u) & ~255u); i += 32u) qlist[i] = make_uint2(0u, 0u);
-                    __syncwarp();
-                    const uint32_t margin = (uint32_t)((cap + 38) * 66 + kQuickCap / 2 + 8);
-                    const uint32_t tp_lo = __float2uint_rd(top_p * 1073741824.f), tp_hi = __float2uint_ru(top_p * 1073741824.f);
-                    const uint32_t ustar = beta_p + 1u;
-                    uint32_t l_left = __float_as_uint(pmin), l_right = __float_as_uint(pmax) + 1u, l_rounds = 0u;
-                    uint32_t cnt_x = (uint32_t)V;
-                    bool above_x = 1.0f > top_p;        // the reference starts from mass 1
-                    int verdict = 1;                     // 1 settled, 2 the list cannot settle it, 0 uncertain
-                    for (;;) {
-                        const bool go = use_cnt ? (cnt_x > top_k || above_x) : above_x;
-                        if (!(go && l_left < l_right - 1u) || l_rounds >= 64u) break;
-                        l_rounds++;
-                        const uint32_t pz = (l_left + l_right) >> 1, py = (l_left + pz) >> 1, pwv = (pz + l_right) >> 1;
-                        const uint32_t pv[3] = {py, pz, pwv};
-                        const uint32_t e0 = max(py, ustar), e1 = max(pz, ustar), e2 = max(pwv, ustar);
-                        uint32_t c0 = 0u, c1 = 0u, c2 = 0u, q0 = 0u, q1 = 0u, q2 = 0u;
-                        for (uint32_t i0 = 0u; i0 < n; i0 += 256u) {
-                            uint2 en[8];
-#pragma unroll
-                            for (int i = 0; i < 8; i++) en[i] = qlist[i0 + (uint32_t)(i * 32 + lane)];
-#pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                if (en[i].x >= e0) { c0++; q0 += en[i].y; }
-                                if (en[i].x >= e1) { c1++; q1 += en[i].y; }
-                                if (en[i].x >= e2) { c2++; q2 += en[i].y; }
-                            }
-                        }
-                        const uint32_t cnt[3] = {__reduce_add_sync(FULL, c0), __reduce_add_sync(FULL, c1), __reduce_add_sync(FULL, c2)};
-                        const uint32_t qm[3] = {__reduce_add_sync(FULL, q0), __reduce_add_sync(FULL, q1), __reduce_add_sync(FULL, q2)};
-                        bool ok[3], above[3], bad = false, unsure = false;
-#pragma unroll
-                        for (int i = 0; i < 3; i++) {
-                            const bool lt = qm[i] + margin < tp_lo, gt = qm[i] > tp_hi + margin;
-                            const bool by_cnt = use_cnt && cnt[i] > top_k;
-                            unsure = unsure || (!lt && !gt && !by_cnt);
-                            above[i] = gt;
-                            const bool below = pv[i] <= beta_p;
-                            const bool exceeds = by_cnt || gt;
-                            const bool pass = (!use_cnt || cnt[i] < top_k) && lt;
-                            ok[i] = !below && pass;
-                            bad = bad || (below && !exceeds);
-                        }
-                        if (unsure) { verdict = 0; break; }
-                        if (bad) { verdict = 2; break; }
-                        const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
-                        const uint32_t nl = s0 ? l_left : s1 ? pv[0] : s2 ? pv[1] : pv[2];
-                        const uint32_t nr = s0 ? pv[0] : s1 ? pv[1] : s2 ? pv[2] : l_right;
-                        cnt_x = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
-                        above_x = s0 ? above_x : s1 ? above[0] : s2 ? above[1] : above[2];
-                        l_left = nl; l_right = nr;
-                    }
-                    if (verdict == 1 && !(l_left > beta_p)) verdict = 2;
-                    if (lane == 0) { s_fin[0] = l_left; s_fin[1] = l_right; s_fin[2] = l_rounds; s_fin[7] = (uint32_t)verdict; }
+                    uint32_t ql, qr, qn;
+                    const int verdict = quick_search(qlist, min(*s_ncl, (uint32_t)kQuickCap), lane, cap + 38, use_cnt, top_k, top_p, beta_p,
+                                                     pmin, pmax, (uint32_t)V, ql, qr, qn);
+                    if (lane == 0) { s_fin[0] = ql; s_fin[1] = qr; s_fin[2] = qn; s_fin[7] = (uint32_t)verdict; }
                 }
                 __syncthreads();
                 quick = (int)s_fin[7];
@@ -1129,7 +1070,6 @@ RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int 
     pl.cached = keep < 0 ? 0 : keep;
     pl.off_cache = pl.off_ring + pl.depth * pl.stage_bytes;
     pl.smem_bytes = pl.off_cache + pl.cached * kStripeBytes;
-    pl.quick = 1;
     return pl;
 }
 

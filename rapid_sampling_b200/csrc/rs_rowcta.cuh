@@ -16,7 +16,6 @@ struct RowCtaPlan {
     int stage_bytes;
     int off_cand, off_ring, off_cache;
     int smem_bytes;
-    int quick;         // 1: try the one-warp search on integer masses first (0: test instrumentation, exact search only)
 };
 
 RowCtaPlan rowcta_plan(int V, bool with_penalties, int sel_rank, int lanes_per_thread, int smem_budget);

@@ -94,6 +94,9 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     float* s_wtot = reinterpret_cast<float*>(smem + kMiscOff + 64);
     volatile uint32_t* s_res = reinterpret_cast<volatile uint32_t*>(smem + kMiscOff + 192);   // ten combined words of an exchange
     volatile int* s_fail = reinterpret_cast<volatile int*>(smem + kMiscOff + 32);             // set when a bounded wait of this CTA gave up
+    uint64_t* qbar = reinterpret_cast<uint64_t*>(smem + kMiscOff + 40);                       // counts the bytes of the unordered candidate list
+    volatile uint32_t* s_quick = reinterpret_cast<volatile uint32_t*>(smem + kMiscOff + 48);  // outcome of the one-warp search: left, right, rounds, verdict
+    uint2* qlist = reinterpret_cast<uint2*>(smem + kQuickOff);
     // A wait that ran out: the status word (and its host mirror) say so, and this CTA stops producing results --
     // its row reports id -1 and leaves the RNG state and the penalties as they were.
     auto wait_failed = [&]() {
@@ -254,6 +257,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             mbar_init(smem_addr(mbar), 1);
             mbar_init(smem_addr(xbar), 1);
             mbar_init(smem_addr(xbar + 1), 1);
+            mbar_init(smem_addr(qbar), 1);
             fence_mbar_init();
             *s_idxt = 0;
             *s_token = 0;
@@ -275,6 +279,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
         if (t == 0) {
             mbar_init(smem_addr(xbar), 1);
             mbar_init(smem_addr(xbar + 1), 1);
+            mbar_init(smem_addr(qbar), 1);
             fence_mbar_init();
             *s_idxt = 0;
             *s_token = 0;
@@ -355,6 +360,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     int nc, ns;   // candidates, and those strictly above the bound
     bool cand_ok;
     uint32_t ncand, nstrict;
+    const uint32_t* p2box = nullptr;   // the mailbox of the last second pass: word 4 = candidates of each virtual warp
     auto pass2 = [&](const bool last) -> bool {
             acc = 0.f; emin = INFINITY; emax = -INFINITY;
             nc = 0; ns = 0; csum = 0.f;
@@ -421,6 +427,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
         csum = warp_tree_sum(csum);
         const uint32_t* box = exchange(Packets<2>(), pick4(__float_as_uint(acc), __float_as_uint(emin), __float_as_uint(emax), overflow),
                                        pick4(wnc, wns, __float_as_uint(csum), 0u), 0u);
+        p2box = box;
         denom = warp_tree_sum(__uint_as_float(bx(box, 0, lane)));  // tree over the 32 warp partials (sampling.cu:29-33)
         emin = warp_min(__uint_as_float(bx(box, 1, lane)));
         emax = warp_max(__uint_as_float(bx(box, 2, lane)));
@@ -556,6 +563,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     float gtp = 0.f;         // this lane's mass above the threshold, its ties with it, its count above
     uint32_t eqk = 0, gtk = 0;
     bool done = false;
+    int quick = 0;           // outcome of the one-warp search on integer masses: 0 not settled that way, 1 settled, 2 list too short
     if (cand_ok) {
         // ===== candidate list: a few elements per lane at most =====
         const int m_own = min(nc, cap);
@@ -577,8 +585,47 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
                 if (qb > lo && qb < hi) { mn = min(mn, qb); mxv = max(mxv, qb); }
             }
         };
-        if (ncand <= 4096u) {
-            done = run_search(cand_eval, true, beta_p, use_cnt && nstrict > top_k, nstrict);
+        if (p.quick && ncand <= (uint32_t)kQuickCap) {
+            // ---- first try: the whole search in one warp of every CTA, on integer masses (quick_search).  Every
+            // CTA gets every candidate of the row: entry k of the list is the same element everywhere (the virtual
+            // warps before mine, then the lanes before me), pushed to all CTAs with stores that count their bytes on
+            // the destination's barrier.  All CTAs reach the same verdict from the same integers. ----
+            uint32_t incl = (uint32_t)m_own;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t v = __shfl_up_sync(FULL, incl, o);
+                if (lane >= o) incl += v;
+            }
+            uint32_t at = __reduce_add_sync(FULL, lane < wg ? bx(p2box, 4, lane) : 0u) + incl - (uint32_t)m_own;
+            const uint32_t qb = smem_addr(qbar), ql = smem_addr(qlist);
+            if (C > 1 && t == 0) mbar_expect_tx(qb, ncand * 8u);
+            for (int i = 0; i < m_own; i++, at++) {
+                const float q = cand_at(i);
+                const uint32_t w0 = __float_as_uint(q), w1 = __float2uint_rn(q * 1073741824.f);
+                if (C == 1) {
+                    qlist[at] = make_uint2(w0, w1);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < C; r++) st_async_v2(map_to_cta(ql + at * 8u, (uint32_t)r), w0, w1, map_to_cta(qb, (uint32_t)r));
+                }
+            }
+            if (C == 1) __syncthreads();
+            if (wl == 0) {
+                if (C > 1 && !mbar_wait_bounded(qb, 0u, p.wait_polls)) wait_failed();
+                uint32_t fl = 0u, fr = 0u, fn = 0u;
+                const int verdict = (*s_fail == 0) ? quick_search(qlist, ncand, lane, cap + 38, use_cnt, top_k, top_p, beta_p, pmin, pmax,
+                                                                  (uint32_t)V, fl, fr, fn)
+                                                   : 0;
+                if (lane == 0) { s_quick[0] = fl; s_quick[1] = fr; s_quick[2] = fn; s_quick[3] = (uint32_t)verdict; }
+            }
+            __syncthreads();
+            quick = (int)s_quick[3];
+            if (quick == 1) { left = s_quick[0]; right = s_quick[1]; rounds = s_quick[2]; }
+        }
+        if (quick == 2) {
+            // the list cannot settle the cutoff: the whole row is searched
+        } else if (ncand <= 4096u) {
+            done = (quick == 1) ? true : run_search(cand_eval, true, beta_p, use_cnt && nstrict > top_k, nstrict);
             if (done) {
                 path = 0;
                 const float thr = __uint_as_float(left);
@@ -681,7 +728,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
     // same tree value as the butterfly, and the warp values are then added in warp order.
     float sgtp;
     uint32_t seqk, sgtk;
-    if (path == 0 && !early_exit) {
+    if (path == 0 && !early_exit && quick != 1) {
         // The bracket closed (right == left + 1): the set at `right` is exactly {p > threshold}, and its count
         // and ordered mass were carried along by the search; the ties are the rest of the set at `left`.
         sgtp = conv_mass;
@@ -820,7 +867,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
                 tr.ncand = ncand;
 #pragma unroll
                 for (int i = 0; i < 10; i++) tr.t_ns[i] = ts[i];
-                tr.t_ns[0] = n_eval;
+                tr.t_ns[0] = n_eval | ((uint32_t)quick << 16);
                 p.dbg_trace[b] = tr;
             }
         }
@@ -1091,7 +1138,7 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     {
         const int mode = g_path_override.load();
         const bool eligible = workspace_bytes >= ws_bytes(B, V);
-        const bool wanted = (mode == 4 || mode == 5) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        const bool wanted = (mode == 4 || mode == 5) || ((mode == 0 || mode == 6) && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
         if (eligible && wanted) {
             pl.rowcta = true;
             pl.ws = ws_bytes(B, V);
@@ -1118,6 +1165,7 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     p.rows = nullptr;
     p.out_prob = nullptr;
     p.out_kept = nullptr;
+    p.quick = (g_path_override.load() < 5) ? 1 : 0;
     p.B = (int)B;
     p.V = (int)V;
     p.kind = penalties ? kRepetition : ((temperature == 1 && top_k == V) ? kTopP : kGeneral);
@@ -1135,8 +1183,7 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
         // up to 148 rows: one CTA per SM with all of its shared memory; more: two CTAs share an SM
         const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
         const int lpt = (B <= di->sms) ? 2 : 4;
-        RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, lpt, budget);
-        if (g_path_override.load() == 5) rp.quick = 0;
+        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, sel_rank, lpt, budget);
         rc = rowcta_launch(p, rp, lpt, st, di->smem_optin);
         if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
         else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta)");
@@ -1183,7 +1230,7 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     {   // large batches: one CTA per row, as for per-call parameters
         const int mode = g_path_override.load();
         const bool eligible = workspace_bytes - rab >= ws_bytes(B, V);
-        const bool wanted = (mode == 4 || mode == 5) || (mode == 0 && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        const bool wanted = (mode == 4 || mode == 5) || ((mode == 0 || mode == 6) && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
         if (eligible && wanted) {
             pl.rowcta = true;
             pl.ws = ws_bytes(B, V);
@@ -1216,6 +1263,7 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     p.rows = rows;
     p.out_prob = out_prob;
     p.out_kept = out_kept;
+    p.quick = (g_path_override.load() < 5) ? 1 : 0;
     p.B = (int)B;
     p.V = (int)V;
     p.kind = penalties ? kRepetition : kGeneral;   // the kernel takes kind, top_k, top_p, scale and the rank from `rows`
@@ -1230,8 +1278,7 @@ static int sample_rows_impl(const void* logits, int dtype, int64_t B, int64_t T,
     if (pl.rowcta) {
         const int budget = (B <= di->sms) ? di->smem_optin : (di->smem_sm / 2 - 1024);
         const int lpt = (B <= di->sms) ? 2 : 4;
-        RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, allow_cand ? 8 : 0, lpt, budget);
-        if (g_path_override.load() == 5) rp.quick = 0;
+        const RowCtaPlan rp = rowcta_plan((int)V, penalties != nullptr, allow_cand ? 8 : 0, lpt, budget);
         rc = rowcta_launch(p, rp, lpt, st, di->smem_optin);
         if (rc == RS_OK) g_launches.fetch_add(1, std::memory_order_relaxed);
         else if (rc == RS_ERR_CUDA) return cuda_fail(cudaGetLastError(), "launch(rowcta, per-row)");
@@ -1311,6 +1358,7 @@ static int sample_static_impl(const float* logits, int64_t B, int64_t T, int64_t
     p.rows = nullptr;
     p.out_prob = nullptr;
     p.out_kept = nullptr;
+    p.quick = (g_path_override.load() < 5) ? 1 : 0;
     p.B = (int)B;
     p.V = (int)V;
     p.kind = penalties ? kRepetition : ((temperature == 1 && top_k == V) ? kTopP : kGeneral);
@@ -1489,7 +1537,7 @@ int rs_set_cluster_override(int cluster_ctas) {
 }
 
 int rs_set_path_override(int mode) {
-    return (mode >= 0 && mode <= 5) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
+    return (mode >= 0 && mode <= 6) ? rs::g_path_override.exchange(mode) : rs::g_path_override.load();
 }
 
 uint64_t rs_kernel_launch_count(void) { return rs::g_launches.load(); }

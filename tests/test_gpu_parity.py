@@ -66,7 +66,7 @@ def test_ids_and_states_bit_identical_to_reference_kernel(abi, ref, kind, B, V, 
     abi.set_cluster(0)
     lg = make_logits(kind, B, V, seed, torch).cuda()
     try:
-        for mode in (0, 1, 2, 3, 4, 5):            # automatic / whole-row search only / streaming / on-chip / one CTA per row / the same, exact search only
+        for mode in (0, 1, 2, 3, 4, 5, 6):         # automatic / whole-row search only / streaming / on-chip / one CTA per row / 4 and 0 with the exact search only
             abi.set_path(mode)
             s_ref, s_our = ref.setup_rand(seed, B), abi.setup_rand(seed, B)
             for call in range(3):                  # consecutive calls advance the states
@@ -350,7 +350,7 @@ def test_sixteen_bit_logits_equal_reference_on_widened_logits(abi, ref, dtype):
                                             ("uniform", 160, 16380, 1.0, -1, 0.6, False)]:
             lg16 = make_logits(kind, B, V, 23, torch).to(dtype).cuda()
             lg32 = lg16.float()
-            for mode in (0, 2, 3, 4, 5):
+            for mode in (0, 2, 3, 4, 5, 6):
                 abi.set_path(mode)
                 s_ref, s_our = ref.setup_rand(2, B), abi.setup_rand(2, B)
                 pen_ref = torch.zeros(B, V, device="cuda") if rep else None
