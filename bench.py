@@ -507,7 +507,9 @@ def main():
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--path-mode", type=int, default=0, choices=[0, 1, 2, 3, 4],
+    ap.add_argument("--ordinary-launch", action="store_true",
+                    help="launch the sampler kernels without programmatic stream serialization (rs_set_dependent_launch(0))")
+    ap.add_argument("--path-mode", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6],
                     help="force a kernel variant (rs_set_path_override): 1 whole-row search, 2 streaming cluster, 3 on-chip cluster, "
                          "4 one CTA per row; for profiling one variant on a workload the planner would give to another")
     ap.add_argument("--per-row", action="store_true", help="ours only: per-row temperature / top_k / top_p tensors (rs_sample_rows)")
@@ -587,6 +589,10 @@ def main():
     f_plain = ext.batch_sampling_temperature_topk_topp_any if lowp else ext.batch_sampling_temperature_topk_topp
     f_rep = ext.batch_sampling_repetition_temperature_topk_topp_any if lowp else ext.batch_sampling_repetition_temperature_topk_topp
 
+    if a.impl == "ours" and a.ordinary_launch:
+        from rapid_sampling_b200 import abi
+        abi.load().rs_set_dependent_launch(0)
+        base["config"]["ordinary_launch"] = True
     if a.impl == "ours" and a.path_mode:
         from rapid_sampling_b200 import abi
         abi.load().rs_set_path_override(a.path_mode)

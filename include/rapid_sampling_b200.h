@@ -264,6 +264,13 @@ uint32_t rs_set_wait_polls(uint32_t polls);
  */
 int rs_selftest_bounded_wait(void* workspace_device, uint32_t polls, void* stream);
 
+/* The sampler kernels are launched with programmatic stream serialization: a kernel may be scheduled while its
+ * predecessor in the stream still runs, and waits on the device (before it touches any global memory) until that
+ * predecessor is complete and its writes are visible.  Between back-to-back sampler calls this hides the launch latency.
+ * Only grids of at most half the GPU's SMs are launched this way (larger ones are better placed on an empty GPU).
+ * 0 switches to ordinary launches, 1 (default) back; any other value only reads.  Returns the previous setting. */
+int rs_set_dependent_launch(int on);
+
 /* Forces the thread-block-cluster width (1, 2, 4, 8 or 16) used per row; 0 restores the automatic
  * choice.  Benchmarking aid; returns the previous value. */
 int rs_set_cluster_override(int cluster_ctas);

@@ -18,7 +18,7 @@ RS_DTYPE_F32, RS_DTYPE_F16, RS_DTYPE_BF16 = 0, 1, 2
 RS_STATIC_SCRATCH_FLOATS = 4194304
 
 SYMBOLS = ["rs_setup_rand", "rs_workspace_bytes", "rs_sample", "rs_sample_debug", "rs_sample_host", "rs_sample_typed", "rs_sample_static_scratch", "rs_rows_workspace_bytes", "rs_sample_rows",
-           "rs_device_status", "rs_clear_status", "rs_set_status_mirror", "rs_set_wait_polls", "rs_selftest_bounded_wait", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_fast_layout", "rs_vp_stage", "rs_vp_tile_begin", "rs_vp_tile_max", "rs_status_string",
+           "rs_device_status", "rs_clear_status", "rs_set_status_mirror", "rs_set_wait_polls", "rs_set_dependent_launch", "rs_selftest_bounded_wait", "rs_set_cluster_override", "rs_set_path_override", "rs_kernel_launch_count", "rs_vp_workspace_bytes", "rs_vp_layout", "rs_vp_fast_layout", "rs_vp_stage", "rs_vp_tile_begin", "rs_vp_tile_max", "rs_status_string",
            "rs_last_cuda_error", "rs_version"]
 
 
@@ -79,6 +79,7 @@ def load():
     L.rs_set_wait_polls.argtypes = [C.c_uint32]
     L.rs_set_wait_polls.restype = C.c_uint32
     L.rs_selftest_bounded_wait.argtypes = [vp, C.c_uint32, vp]
+    L.rs_set_dependent_launch.argtypes = [C.c_int]
     L.rs_set_cluster_override.argtypes = [C.c_int]
     L.rs_set_path_override.argtypes = [C.c_int]
     L.rs_kernel_launch_count.restype = C.c_uint64

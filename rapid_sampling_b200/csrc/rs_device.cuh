@@ -111,6 +111,13 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
 }
+// Programmatic dependent launch (kernels launched with cudaLaunchAttributeProgrammaticStreamSerialization).
+// wait: returns once every kernel this one depends on has completed and its memory operations are visible (at once
+// for an ordinary launch).  may_launch: lets the next kernel of the stream be scheduled early; it runs up to its own
+// wait while this one is still working.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));

@@ -21,6 +21,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstring>
 #include <mutex>
 #include <type_traits>
 
@@ -102,6 +103,9 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     const int b = blockIdx.x;
     const int V = p.V, V4 = V >> 2;
     const int K = (V4 + kLanes - 1) >> 10;   // stripes of 1024 float4 groups
+    // programmatic dependent launch: nothing in global memory is touched before the predecessor is complete and visible
+    grid_dependents_may_launch();
+    grid_dependency_wait();
     int a_kind = p.kind, a_top_k = p.top_k, a_sel_rank = p.sel_rank;
     float a_scale = p.scale, a_top_p = p.top_p;
     if (p.rows) {   // this row's own normalised parameters
@@ -1074,27 +1078,37 @@ RowCtaPlan rowcta_plan(int V, bool rep, int sel_rank, int lanes_per_thread, int 
 }
 
 template <int LPT, bool REP, int D, int NH, bool LOWP>
-static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t stream, int smem_optin, bool* attr_done) {
+static int rowcta_launch_t(const Params& p, const RowCtaPlan& pl, cudaStream_t stream, int smem_optin, bool* attr_done, bool dependent) {
     auto kern = rowcta_kernel<LPT, REP, D, NH, LOWP>;
     if (!*attr_done) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_optin) != cudaSuccess) return RS_ERR_CUDA;
         *attr_done = true;
     }
-    kern<<<(unsigned)p.B, kLanes / LPT, (size_t)pl.smem_bytes, stream>>>(p, pl);
-    return cudaGetLastError() == cudaSuccess ? RS_OK : RS_ERR_CUDA;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3((unsigned)p.B, 1, 1);
+    cfg.blockDim = dim3(kLanes / LPT, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)pl.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // the kernel waits for its predecessor itself
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = dependent ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, p, pl) == cudaSuccess ? RS_OK : RS_ERR_CUDA;
 }
 
 template <bool LOWP>
 static int rowcta_launch_d(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, bool rep, cudaStream_t stream, int smem_optin,
-                           bool* attr_done) {
+                           bool* attr_done, bool dependent) {
     if (lanes_per_thread == 2)
-        return rep ? rowcta_launch_t<2, true, 3, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 0)
-                   : rowcta_launch_t<2, false, 4, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 1);
-    return rep ? rowcta_launch_t<4, true, 5, 2, LOWP>(p, pl, stream, smem_optin, attr_done + 2)
-               : rowcta_launch_t<4, false, 4, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 3);
+        return rep ? rowcta_launch_t<2, true, 3, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 0, dependent)
+                   : rowcta_launch_t<2, false, 4, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 1, dependent);
+    return rep ? rowcta_launch_t<4, true, 5, 2, LOWP>(p, pl, stream, smem_optin, attr_done + 2, dependent)
+               : rowcta_launch_t<4, false, 4, 1, LOWP>(p, pl, stream, smem_optin, attr_done + 3, dependent);
 }
 
-int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin) {
+int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin, bool dependent) {
     static std::mutex mu;
     static bool attr_done[64][8] = {};
     int dev = 0;
@@ -1102,8 +1116,8 @@ int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, c
     const bool rep = p.penalties != nullptr;
     if (pl.depth != rowcta_depth(rep, lanes_per_thread) || pl.smem_bytes > smem_optin) return RS_ERR_LIMIT;
     std::lock_guard<std::mutex> lk(mu);
-    if (p.dtype == RS_DTYPE_F32) return rowcta_launch_d<false>(p, pl, lanes_per_thread, rep, stream, smem_optin, attr_done[dev]);
-    return rowcta_launch_d<true>(p, pl, lanes_per_thread, rep, stream, smem_optin, attr_done[dev] + 4);
+    if (p.dtype == RS_DTYPE_F32) return rowcta_launch_d<false>(p, pl, lanes_per_thread, rep, stream, smem_optin, attr_done[dev], dependent);
+    return rowcta_launch_d<true>(p, pl, lanes_per_thread, rep, stream, smem_optin, attr_done[dev] + 4, dependent);
 }
 
 }  // namespace rs

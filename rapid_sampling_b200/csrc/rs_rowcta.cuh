@@ -20,6 +20,7 @@ struct RowCtaPlan {
 
 RowCtaPlan rowcta_plan(int V, bool with_penalties, int sel_rank, int lanes_per_thread, int smem_budget);
 // lanes_per_thread: 2 (512 threads per row; batches that leave an SM to one row) or 4 (256 threads; two rows per SM)
-int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin);
+// dependent: launch with programmatic stream serialization (the kernel waits for its predecessor itself)
+int rowcta_launch(const Params& p, const RowCtaPlan& pl, int lanes_per_thread, cudaStream_t stream, int smem_optin, bool dependent);
 
 }  // namespace rs
