@@ -126,7 +126,10 @@ __device__ __forceinline__ void slab_pass(const Row<C, SMEM>& row, int& n, const
 // Pivots at or below beta_p are answered by the set {p > beta_p}, as in the exact search on a candidate list.
 // All 32 lanes call this with the same arguments; `list` must be readable up to the next multiple of 256 entries
 // (entries from n on are overwritten with "never admitted").
+// FREEZE: once the sets at `left` and at `right` differ by at most one entry, the remaining rounds are replayed from the
+// carried values without reading the list (pays where rounds are many; costs registers).
 // Verdict: 1 settled (left / right / rounds are the reference's), 2 the list cannot settle the cutoff, 0 undecided.
+template <bool FREEZE>
 __device__ __forceinline__ int quick_search(uint2* list, const uint32_t n, const int lane, const int depth, const bool use_cnt,
                                             const uint32_t top_k, const float top_p, const uint32_t beta_p, const float pmin,
                                             const float pmax, const uint32_t V, uint32_t& left, uint32_t& right, uint32_t& rounds) {
@@ -137,51 +140,95 @@ __device__ __forceinline__ int quick_search(uint2* list, const uint32_t n, const
     const uint32_t tp_lo = __float2uint_rd(top_p * 1073741824.f), tp_hi = __float2uint_ru(top_p * 1073741824.f);
     const uint32_t ustar = beta_p + 1u;
     uint32_t l_left = __float_as_uint(pmin), l_right = __float_as_uint(pmax) + 1u, l_rounds = 0u;
-    uint32_t cnt_x = V;
-    bool above_x = 1.0f > top_p;        // the reference starts from mass 1
+    // what the loop carries: the count at `left` and whether its mass is above top_p (the reference starts from the
+    // whole row and mass 1); kept beside it for the replay below: the same for `right` (nothing lies above pmax)
+    uint32_t cnt_x = V, cnt_r = 0u;
+    bool gt_x = 1.0f > top_p, lt_x = 1.0f < top_p, gt_r = false, lt_r = 0.0f < top_p;
+    bool have_x = false;                 // cnt_x counts list entries (left came from an evaluated pivot)
+    bool frozen = false;                 // at most one entry is left in [max(left, u*), right): no more scans
+    uint32_t v_bits = 0u;                // that entry (0: none; every evaluation point is above 0)
     int verdict = 1;
     for (;;) {
-        const bool go = use_cnt ? (cnt_x > top_k || above_x) : above_x;
+        const bool go = use_cnt ? (cnt_x > top_k || gt_x) : gt_x;
         if (!(go && l_left < l_right - 1u) || l_rounds >= 64u) break;
         l_rounds++;
         const uint32_t pz = (l_left + l_right) >> 1, py = (l_left + pz) >> 1, pwv = (pz + l_right) >> 1;
         const uint32_t pv[3] = {py, pz, pwv};
-        const uint32_t e0 = max(py, ustar), e1 = max(pz, ustar), e2 = max(pwv, ustar);
-        uint32_t c0 = 0u, c1 = 0u, c2 = 0u, q0 = 0u, q1 = 0u, q2 = 0u;
-        for (uint32_t i0 = 0u; i0 < n; i0 += 256u) {
-            uint2 en[8];
+        const uint32_t ev[3] = {max(py, ustar), max(pz, ustar), max(pwv, ustar)};
+        uint32_t cnt[3];
+        bool lt[3], gt[3], unsure = false;
+        if (FREEZE && !frozen && have_x && cnt_x - cnt_r <= 1u) {
+            // The sets at `left` and at `right` differ by at most one entry, v: an evaluation point at or below v sees
+            // the set of `left`, one above v the set of `right`; the remaining rounds need no data.
+            frozen = true;
+            if (cnt_x != cnt_r) {
+                uint32_t m = 0u;
+                for (uint32_t i0 = 0u; i0 < n; i0 += 256u) {
 #pragma unroll
-            for (int i = 0; i < 8; i++) en[i] = list[i0 + (uint32_t)(i * 32 + lane)];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (en[i].x >= e0) { c0++; q0 += en[i].y; }
-                if (en[i].x >= e1) { c1++; q1 += en[i].y; }
-                if (en[i].x >= e2) { c2++; q2 += en[i].y; }
+                    for (int i = 0; i < 8; i++) {
+                        const uint32_t e = list[i0 + (uint32_t)(i * 32 + lane)].x;
+                        m = (e < l_right) ? max(m, e) : m;
+                    }
+                }
+                v_bits = __reduce_max_sync(FULLW, m);
             }
         }
-        const uint32_t cnt[3] = {__reduce_add_sync(FULLW, c0), __reduce_add_sync(FULLW, c1), __reduce_add_sync(FULLW, c2)};
-        const uint32_t qm[3] = {__reduce_add_sync(FULLW, q0), __reduce_add_sync(FULLW, q1), __reduce_add_sync(FULLW, q2)};
-        bool ok[3], above[3], bad = false, unsure = false;
+        if (FREEZE && frozen) {
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                const bool at_x = ev[i] <= v_bits;
+                cnt[i] = at_x ? cnt_x : cnt_r;
+                lt[i] = at_x ? lt_x : lt_r;
+                gt[i] = at_x ? gt_x : gt_r;
+            }
+        } else {
+            uint32_t c0 = 0u, c1 = 0u, c2 = 0u, q0 = 0u, q1 = 0u, q2 = 0u;
+            for (uint32_t i0 = 0u; i0 < n; i0 += 256u) {
+                uint2 en[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) en[i] = list[i0 + (uint32_t)(i * 32 + lane)];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (en[i].x >= ev[0]) { c0++; q0 += en[i].y; }
+                    if (en[i].x >= ev[1]) { c1++; q1 += en[i].y; }
+                    if (en[i].x >= ev[2]) { c2++; q2 += en[i].y; }
+                }
+            }
+            cnt[0] = __reduce_add_sync(FULLW, c0); cnt[1] = __reduce_add_sync(FULLW, c1); cnt[2] = __reduce_add_sync(FULLW, c2);
+            const uint32_t qm[3] = {__reduce_add_sync(FULLW, q0), __reduce_add_sync(FULLW, q1), __reduce_add_sync(FULLW, q2)};
+#pragma unroll
+            for (int i = 0; i < 3; i++) {
+                lt[i] = qm[i] + margin < tp_lo;
+                gt[i] = qm[i] > tp_hi + margin;
+                unsure = unsure || (!lt[i] && !gt[i] && !(use_cnt && cnt[i] > top_k));
+            }
+        }
+        if (unsure) { verdict = 0; break; }
+        bool ok[3], bad = false;
 #pragma unroll
         for (int i = 0; i < 3; i++) {
-            const bool lt = qm[i] + margin < tp_lo, gt = qm[i] > tp_hi + margin;
-            const bool by_cnt = use_cnt && cnt[i] > top_k;
-            unsure = unsure || (!lt && !gt && !by_cnt);
-            above[i] = gt;
             const bool below = pv[i] <= beta_p;
-            const bool exceeds = by_cnt || gt;
-            const bool pass = (!use_cnt || cnt[i] < top_k) && lt;
+            const bool exceeds = (use_cnt && cnt[i] > top_k) || gt[i];
+            const bool pass = (!use_cnt || cnt[i] < top_k) && lt[i];
             ok[i] = !below && pass;
             bad = bad || (below && !exceeds);
         }
-        if (unsure) { verdict = 0; break; }
         if (bad) { verdict = 2; break; }
         const bool s0 = ok[0], s1 = !s0 && ok[1], s2 = !s0 && !s1 && ok[2];
         const uint32_t nl = s0 ? l_left : s1 ? pv[0] : s2 ? pv[1] : pv[2];
         const uint32_t nr = s0 ? pv[0] : s1 ? pv[1] : s2 ? pv[2] : l_right;
-        cnt_x = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
-        above_x = s0 ? above_x : s1 ? above[0] : s2 ? above[1] : above[2];
+        const uint32_t ncx = s0 ? cnt_x : s1 ? cnt[0] : s2 ? cnt[1] : cnt[2];
+        const bool ngx = s0 ? gt_x : s1 ? gt[0] : s2 ? gt[1] : gt[2];
         l_left = nl; l_right = nr;
+        cnt_x = ncx; gt_x = ngx;
+        if (FREEZE) {
+            const bool nlx = s0 ? lt_x : s1 ? lt[0] : s2 ? lt[1] : lt[2];
+            const uint32_t ncr = s0 ? cnt[0] : s1 ? cnt[1] : s2 ? cnt[2] : cnt_r;
+            const bool ngr = s0 ? gt[0] : s1 ? gt[1] : s2 ? gt[2] : gt_r;
+            const bool nlr = s0 ? lt[0] : s1 ? lt[1] : s2 ? lt[2] : lt_r;
+            have_x = have_x || !s0;
+            lt_x = nlx; cnt_r = ncr; gt_r = ngr; lt_r = nlr;
+        }
     }
     if (verdict == 1 && !(l_left > beta_p)) verdict = 2;
     left = l_left; right = l_right; rounds = l_rounds;

@@ -767,7 +767,7 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 __syncthreads();
                 if (pw == 0) {
                     uint32_t ql, qr, qn;
-                    const int verdict = quick_search(qlist, min(*s_ncl, (uint32_t)kQuickCap), lane, cap + 38, use_cnt, top_k, top_p, beta_p,
+                    const int verdict = quick_search<false>(qlist, min(*s_ncl, (uint32_t)kQuickCap), lane, cap + 38, use_cnt, top_k, top_p, beta_p,
                                                      pmin, pmax, (uint32_t)V, ql, qr, qn);
                     if (lane == 0) { s_fin[0] = ql; s_fin[1] = qr; s_fin[2] = qn; s_fin[7] = (uint32_t)verdict; }
                 }

@@ -321,8 +321,36 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             if (SMEM) row.st(s, v);
         }
     } else {
+        int s = 0;
+        if (SMEM) {
+            // Eight groups at a time with ONE test for Inf / NaN products per batch (x * 0 is NaN exactly for those): a
+            // branch per group would end the basic block there and leave a lone warp waiting out every instruction.
+            for (; s + 8 <= Kt; s += 8) {
+                float4 v[8];
+                float pr[8], tm = tmax;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float4 l = bulk_load ? row.ld(s + j) : ldrow4((s + j) * kLanes + tg);
+                    v[j] = make_float4(l.x * a_scale, l.y * a_scale, l.z * a_scale, l.w * a_scale);
+                    pr[j] = fmaf(v[j].w, 0.f, fmaf(v[j].z, 0.f, fmaf(v[j].y, 0.f, v[j].x * 0.f)));
+                    tm = fmaxf(fmaxf(fmaxf(tm, v[j].x), fmaxf(v[j].y, v[j].z)), v[j].w);
+                }
+                const float probe = ((pr[0] + pr[1]) + (pr[2] + pr[3])) + ((pr[4] + pr[5]) + (pr[6] + pr[7]));
+                if (probe != probe) {
+                    tm = tmax;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        v[j] = sanitize4(v[j]);
+                        tm = fmaxf(fmaxf(fmaxf(tm, v[j].x), fmaxf(v[j].y, v[j].z)), v[j].w);
+                    }
+                }
+                tmax = tm;
+#pragma unroll
+                for (int j = 0; j < 8; j++) row.st(s + j, v[j]);
+            }
+        }
 #pragma unroll 8
-        for (int s = 0; s < Kt; s++) {
+        for (; s < Kt; s++) {
             float4 v = bulk_load ? row.ld(s) : ldrow4(s * kLanes + tg);
             v = scaled4(v, a_scale);
             tmax = fmaxf(fmaxf(fmaxf(tmax, v.x), fmaxf(v.y, v.z)), v.w);
@@ -655,7 +683,7 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             if (wl == 0) {
                 if (C > 1 && !mbar_wait_bounded(qb, 0u, p.wait_polls)) wait_failed();
                 uint32_t fl = 0u, fr = 0u, fn = 0u;
-                const int verdict = (*s_fail == 0) ? quick_search(qlist, ncand, lane, cap + 38, use_cnt, top_k, top_p, beta_p, pmin, pmax,
+                const int verdict = (*s_fail == 0) ? quick_search<true>(qlist, ncand, lane, cap + 38, use_cnt, top_k, top_p, beta_p, pmin, pmax,
                                                                   (uint32_t)V, fl, fr, fn)
                                                    : 0;
                 if (lane == 0) { s_quick[0] = fl; s_quick[1] = fr; s_quick[2] = fn; s_quick[3] = (uint32_t)verdict; }
