@@ -273,15 +273,43 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                 request(Yes(), Pen());
                 wait_stage();
                 const unsigned char* st = ring + (size_t)cslot * kStage;
+                if (FULLK) {   // the groups of a stage together, with one test for Inf / NaN products (see stream_x)
+                    float4 l[SL], q[SL], v[SL];
+                    float probe = 0.f;
 #pragma unroll
-                for (int jj = 0; jj < SL; jj++) {
-                    const int j = h * SL + jj;
-                    if (FULLK || tail_ok[j]) {
-                        float4 v = keep ? raw4(own + (size_t)(j * NT + t) * 16) : raw4(st + (size_t)(jj * NT + t) * 16);
-                        if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
-                        else v = scaled4(v, a_scale);
-                        tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
-                        if (keep) reinterpret_cast<float4*>(own)[j * NT + t] = v;
+                    for (int jj = 0; jj < SL; jj++) {
+                        const int j = h * SL + jj;
+                        l[jj] = keep ? raw4(own + (size_t)(j * NT + t) * 16) : raw4(st + (size_t)(jj * NT + t) * 16);
+                        if (REP) {
+                            q[jj] = reinterpret_cast<const float4*>(st + kPart)[jj * NT + t];
+                            v[jj] = make_float4((l[jj].x - q[jj].x) * a_scale, (l[jj].y - q[jj].y) * a_scale, (l[jj].z - q[jj].z) * a_scale,
+                                                (l[jj].w - q[jj].w) * a_scale);
+                        } else {
+                            v[jj] = make_float4(l[jj].x * a_scale, l[jj].y * a_scale, l[jj].z * a_scale, l[jj].w * a_scale);
+                        }
+                        probe += fmaf(v[jj].w, 0.f, fmaf(v[jj].z, 0.f, fmaf(v[jj].y, 0.f, v[jj].x * 0.f)));
+                    }
+                    if (probe != probe) {
+#pragma unroll
+                        for (int jj = 0; jj < SL; jj++) v[jj] = REP ? scaled4_rep(l[jj], q[jj], a_scale) : scaled4(l[jj], a_scale);
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < SL; jj++) {
+                        const int j = h * SL + jj;
+                        tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v[jj].x), fmaxf(v[jj].y, v[jj].z)), v[jj].w);
+                        if (keep) reinterpret_cast<float4*>(own)[j * NT + t] = v[jj];
+                    }
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < SL; jj++) {
+                        const int j = h * SL + jj;
+                        if (tail_ok[j]) {
+                            float4 v = keep ? raw4(own + (size_t)(j * NT + t) * 16) : raw4(st + (size_t)(jj * NT + t) * 16);
+                            if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
+                            else v = scaled4(v, a_scale);
+                            tmax[j] = fmaxf(fmaxf(fmaxf(tmax[j], v.x), fmaxf(v.y, v.z)), v.w);
+                            if (keep) reinterpret_cast<float4*>(own)[j * NT + t] = v;
+                        }
                     }
                 }
                 cslot = (cslot + 1 == D) ? 0 : cslot + 1;
@@ -356,7 +384,10 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
     };
     // One pass over the row as scaled logits x, stripes in ascending order (every lane's chain order): the kept
     // stripes from shared memory, the rest through the copy pipeline (which begin_pass(NC, 1, ...) has started).
-    auto stream_x = [&](auto&& fn) {
+    // fn(j, k, v) gets one group; the groups of a full stripe's stage go to fn_batch(h, k, v[SL]) together, scaled with
+    // ONE test for Inf / NaN products per stage (x * 0 is NaN exactly for those): a branch per group would end the
+    // basic block there, and the few warps of a row would wait out every dependent instruction of every group.
+    auto stream_x = [&](auto&& fn, auto&& fn_batch) {
         int cslot = 0;
         auto stripe = [&](auto full_tag, const int k) {
             constexpr bool FULLK = decltype(full_tag)::value;
@@ -370,16 +401,44 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
                     wait_stage();
                     cslot = (cslot + 1 == D) ? 0 : cslot + 1;
                 }
+                if (FULLK) {
+                    float4 v[SL];
+                    if (kept) {
 #pragma unroll
-                for (int jj = 0; jj < SL; jj++) {
-                    const int j = h * SL + jj;
-                    if (FULLK || tail_ok[j]) {
-                        float4 v = kept ? reinterpret_cast<const float4*>(own)[j * NT + t] : raw4(st + (size_t)(jj * NT + t) * 16);
-                        if (!kept) {
-                            if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
-                            else v = scaled4(v, a_scale);
+                        for (int jj = 0; jj < SL; jj++) v[jj] = reinterpret_cast<const float4*>(own)[(h * SL + jj) * NT + t];
+                    } else {
+                        float4 l[SL], q[SL];
+                        float probe = 0.f;
+#pragma unroll
+                        for (int jj = 0; jj < SL; jj++) {
+                            l[jj] = raw4(st + (size_t)(jj * NT + t) * 16);
+                            if (REP) {
+                                q[jj] = reinterpret_cast<const float4*>(st + kPart)[jj * NT + t];
+                                v[jj] = make_float4((l[jj].x - q[jj].x) * a_scale, (l[jj].y - q[jj].y) * a_scale, (l[jj].z - q[jj].z) * a_scale,
+                                                    (l[jj].w - q[jj].w) * a_scale);
+                            } else {
+                                v[jj] = make_float4(l[jj].x * a_scale, l[jj].y * a_scale, l[jj].z * a_scale, l[jj].w * a_scale);
+                            }
+                            probe += fmaf(v[jj].w, 0.f, fmaf(v[jj].z, 0.f, fmaf(v[jj].y, 0.f, v[jj].x * 0.f)));
                         }
-                        fn(j, k, v);
+                        if (probe != probe) {   // rare: the exact formulas, group by group
+#pragma unroll
+                            for (int jj = 0; jj < SL; jj++) v[jj] = REP ? scaled4_rep(l[jj], q[jj], a_scale) : scaled4(l[jj], a_scale);
+                        }
+                    }
+                    fn_batch(h, k, v);
+                } else {
+#pragma unroll
+                    for (int jj = 0; jj < SL; jj++) {
+                        const int j = h * SL + jj;
+                        if (tail_ok[j]) {
+                            float4 v = kept ? reinterpret_cast<const float4*>(own)[j * NT + t] : raw4(st + (size_t)(jj * NT + t) * 16);
+                            if (!kept) {
+                                if (REP) v = scaled4_rep(v, reinterpret_cast<const float4*>(st + kPart)[jj * NT + t], a_scale);
+                                else v = scaled4(v, a_scale);
+                            }
+                            fn(j, k, v);
+                        }
                     }
                 }
             }
@@ -391,7 +450,45 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
         emin = INFINITY; emax = -INFINITY; csum = 0.f; ns = 0;
 #pragma unroll
         for (int j = 0; j < LPT; j++) { acc[j] = 0.f; nc[j] = 0; }
-        stream_x([&](const int j, const int, const float4 v) { pass2_group(j, v); });
+        stream_x([&](const int j, const int, const float4 v) { pass2_group(j, v); },
+                 [&](const int h, const int, float4 (&v)[SL]) {
+                     // the groups of one stage: every lane's sum in its own order, one test for candidates
+                     float hi[SL], hi_all = 0.f;
+#pragma unroll
+                     for (int jj = 0; jj < SL; jj++) {
+                         const int j = h * SL + jj;
+                         v[jj].x = exp2f(v[jj].x - mx);
+                         v[jj].y = exp2f(v[jj].y - mx);
+                         v[jj].z = exp2f(v[jj].z - mx);
+                         v[jj].w = exp2f(v[jj].w - mx);
+                         float em = 0.f;
+                         em += v[jj].x; em += v[jj].y; em += v[jj].z; em += v[jj].w;
+                         acc[j] += em;
+                         hi[jj] = fmaxf(fmaxf(v[jj].x, v[jj].y), fmaxf(v[jj].z, v[jj].w));
+                         emin = fminf(fminf(emin, fminf(v[jj].x, v[jj].y)), fminf(v[jj].z, v[jj].w));
+                         emax = fmaxf(emax, hi[jj]);
+                         hi_all = fmaxf(hi_all, hi[jj]);
+                     }
+                     if (hi_all >= beta_e) {
+#pragma unroll
+                         for (int jj = 0; jj < SL; jj++) {
+                             const int j = h * SL + jj;
+                             if (hi[jj] >= beta_e) {
+                                 const float e4[4] = {v[jj].x, v[jj].y, v[jj].z, v[jj].w};
+#pragma unroll
+                                 for (int q = 0; q < 4; q++) {
+                                     if (e4[q] >= beta_e) {
+                                         if (nc[j] < cap) cand[nc[j] * kLanes + j * NT + t] = e4[q];
+                                         nc[j]++;
+                                         ns += (e4[q] > beta_e) ? 1 : 0;
+                                     }
+                                 }
+                                 csum += (v[jj].x >= beta_e ? v[jj].x : 0.f) + (v[jj].y >= beta_e ? v[jj].y : 0.f) +
+                                         (v[jj].z >= beta_e ? v[jj].z : 0.f) + (v[jj].w >= beta_e ? v[jj].w : 0.f);
+                             }
+                         }
+                     }
+                 });
         stamp(4);
         float* box = box_of(phase);
         uint32_t* boxc = boxc_of(phase);
@@ -798,10 +895,14 @@ __global__ void __launch_bounds__(kLanes / LPT, (LPT >= 4 ? 2 : 1)) rowcta_kerne
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
             begin_pass(NC, 1, Yes(), Pen());
-            stream_x([&](const int j, const int k, float4 v) {
+            auto write_p = [&](const int j, const int k, float4 v) {
                 v.x = exp2f(v.x - mx) / denom; v.y = exp2f(v.y - mx) / denom;
                 v.z = exp2f(v.z - mx) / denom; v.w = exp2f(v.w - mx) / denom;
                 row.slab[(size_t)k * kLanes + j * NT + t] = v;
+            };
+            stream_x(write_p, [&](const int h, const int k, float4 (&v)[SL]) {
+#pragma unroll
+                for (int jj = 0; jj < SL; jj++) write_p(h * SL + jj, k, v[jj]);
             });
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
