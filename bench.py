@@ -37,11 +37,11 @@ MIN_E2E_STEPS = 200
 EXTRA_CALLS = 200             # calls per side for the other workloads reported beside the headline
 # Per-launch DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of the sampler kernel, copied from the ncu
 # capture named beside it; a workload without a capture of the current kernel has no entry.
-PROFILED_TRAFFIC = {"C1": (2.210e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md"),
-                    "C2": (1.153e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md"),
+PROFILED_TRAFFIC = {"C1": (2.214e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md"),
+                    "C2": (1.168e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md"),
                     "C3": (39.02e6, "profiles/sampler_kernel_C3_load_paths.md"),
-                    "C4": (216.8e6, "profiles/rowcta_kernel_C4_C3.md"),
-                    "C5": (505.0e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md")}
+                    "C4": (219.4e6, "profiles/rowcta_kernel_C4_C3.md"),
+                    "C5": (513.3e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md")}
 
 
 def workload(name):

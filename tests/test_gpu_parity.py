@@ -133,6 +133,32 @@ def test_row_cta_integer_search_and_its_hand_over_to_exact_sums(abi, ref):
         abi.set_path(0)
 
 
+def test_back_to_back_calls_under_dependent_launch_equal_the_reference_chain(abi, ref):
+    """Small grids are launched with programmatic stream serialization: call n+1 may be set up while call n runs and
+    must not touch states or penalties before call n is complete.  A chain of 60 calls, each depending on the states
+    and penalties the previous one wrote, queued without any host synchronisation, must end bit-equal to the reference's
+    chain -- with the early launch on, and with ordinary launches."""
+    B, V = 3, 65536
+    lgs = [make_logits("normal3", B, V, 40 + i, torch).cuda() for i in range(4)]
+    L = abi.L
+    prev = L.rs_set_dependent_launch(-1)
+    try:
+        for on in (1, 0):
+            L.rs_set_dependent_launch(on)
+            pen_ref, pen_our = torch.zeros(B, V, device="cuda"), torch.zeros(B, V, device="cuda")
+            s_ref, s_our = ref.setup_rand(9, B), abi.setup_rand(9, B)
+            want, got = [], []
+            for i in range(60):
+                want.append(ref.batch_sampling_repetition_temperature_topk_topp(lgs[i % 4], pen_ref, s_ref, 0.1, 0.1, 0.95, 0.8, 50, 0.9))
+            for i in range(60):
+                got.append(abi.sample(lgs[i % 4], s_our, 0.8, 50, 0.9, penalties=pen_our, presence=0.1, repetition=0.1, decay=0.95))
+            torch.cuda.synchronize()
+            assert torch.equal(torch.stack(got), torch.stack(want)), on
+            assert torch.equal(pen_our, pen_ref) and torch.equal(s_our, s_ref), on
+    finally:
+        L.rs_set_dependent_launch(prev)
+
+
 @pytest.mark.parametrize("cluster", [1, 2, 4, 8, 16])
 def test_every_cluster_width_gives_the_same_ids(abi, ref, cluster):
     try:
