@@ -1221,7 +1221,13 @@ static int sample_impl(const void* logits, int dtype, int64_t B, int64_t T, int6
     {
         const int mode = g_path_override.load();
         const bool eligible = workspace_bytes >= ws_bytes(B, V);
-        const bool wanted = (mode == 4 || mode == 5) || ((mode == 0 || mode == 6) && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch);
+        // A call that is known to search the whole row -- a top_k too large for the candidate bound, or no cutoff at
+        // all -- stays with the cluster kernel: 1024 threads per row carry the full-row rounds better than 256.  So
+        // does a call without a top_k whose top_p is large: its kept set may be a good part of the row (N(0, 3^2)
+        // logits: 4 % at top_p 0.9), which overflows this kernel's 6 entries per lane but not the cluster kernel's 32.
+        const bool wide = V > 8192 && (sel_rank == 0 || (top_k == V && top_p > 0.5));   // (short rows: a whole-row search is cheap)
+        const bool wanted = (mode == 4 || mode == 5) ||
+                            ((mode == 0 || mode == 6) && g_cluster_override.load() == 0 && !pl.smem && B >= kRowCtaMinBatch && !wide);
         if (eligible && wanted) {
             pl.rowcta = true;
             pl.ws = ws_bytes(B, V);

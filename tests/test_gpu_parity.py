@@ -42,6 +42,9 @@ MATRIX = [
     ("uniform", 100, 32768, 1.0, -1, 0.9, 20),     # flat rows, streaming variant: the lowered bound takes in the whole row
     ("uniform4", 90, 16384, 1.0, -1, 0.1, 21),     # long candidate lists that shrink as the bracket rises
     ("coarse", 80, 32768, 1.0, -1, 0.7, 22),       # the same with heavy ties
+    ("normal3", 130, 65536, 1.0, -1, 0.9, 23),     # one CTA per row: the kept set (~4 % of the row) overflows the lanes' shared-memory lists
+    ("normal3", 20, 151936, 1.0, -1, 0.7, 24),     # the same with a ragged last stripe
+    ("uniform4", 160, 32768, 1.0, -1, 0.3, 25),    # ... and lists that spill widely
 ]
 
 
