@@ -131,7 +131,7 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def cpu_port_baseline(w, budget_s=12.0, max_calls=64):
+def cpu_port_baseline(w, budget_s=12.0, max_calls=4096):
     """Times the CPU restatement of the reference (oracle/sampler_oracle.c) on this host: whole calls of the
     workload's shape, rows spread over the host cores, until the budget is used."""
     import numpy as np
