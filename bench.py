@@ -507,6 +507,7 @@ def main():
     ap.add_argument("--config", default="C2", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="time the plain Python launch loop instead of one replay of a CUDA graph of the K calls")
     ap.add_argument("--ordinary-launch", action="store_true",
                     help="launch the sampler kernels without programmatic stream serialization (rs_set_dependent_launch(0))")
     ap.add_argument("--path-mode", type=int, default=0, choices=[0, 1, 2, 3, 4, 5, 6],
@@ -624,15 +625,45 @@ def main():
     clocks.start()
 
     # ---- timed region: exactly K steps, device-timed, max over ranks -------------------------------
+    # The K calls are recorded once into a CUDA graph and replayed: the timed region then holds the K sampler launches
+    # and nothing of the host (with several ranks on one host the Python launch loops compete for its cores).
+    # --eager, the reference kernel, or a failed capture time the plain loop instead.
+    graph = None
     n0 = launches()
+    if a.impl == "ours" and not a.eager:
+        try:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for i in range(3):      # the stream's workspace exists before the capture starts
+                    call(pool[i % pool_n])
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            n0 = launches()
+            graph = torch.cuda.CUDAGraph()
+            keep = []
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(K):
+                    keep.append(call(pool[i % pool_n]))
+            captured = launches() - n0
+            graph.replay()              # one untimed replay
+            torch.cuda.synchronize()
+        except Exception as exc:        # noqa: BLE001 -- any capture problem: time the plain loop
+            graph = None
+            base["config"]["graph_capture_failed"] = repr(exc)[:200]
+            n0 = launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sync_all()
     e0.record()
-    for i in range(K):
-        call(pool[i % pool_n])
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(K):
+            call(pool[i % pool_n])
     e1.record()
     torch.cuda.synchronize()
-    gpu_launches = launches() - n0
+    gpu_launches = captured if graph is not None else launches() - n0
+    base["config"]["launch"] = ("one replay of a CUDA graph holding the %d calls" % K) if graph is not None else "eager loop"
     total_ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([total_ms], device=dev)
