@@ -200,15 +200,44 @@ def sampler_call(ext, w, states, pen):
     return lambda lg: ext.batch_sampling_temperature_topk_topp(lg, states, w["temperature"], w["top_k"], w["top_p"])
 
 
-def time_calls(call, pool, n, torch, warm=5):
-    """(ms per call over n back-to-back calls, median us of per-call event pairs)."""
+def graph_of_calls(call, pool, n, torch):
+    """n calls recorded into one CUDA graph (after three calls on the capture stream, so that the stream's workspace
+    exists); None if the capture fails."""
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(3):
+                call(pool[i % len(pool)])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        keep = []
+        with torch.cuda.graph(g, stream=side):
+            for i in range(n):
+                keep.append(call(pool[i % len(pool)]))
+        g.replay()
+        torch.cuda.synchronize()
+        g._keep = keep
+        return g
+    except Exception:   # noqa: BLE001
+        return None
+
+
+def time_calls(call, pool, n, torch, warm=5, graph=False):
+    """(ms per call over n back-to-back calls -- one replay of a CUDA graph of the n calls if `graph` --, median us of
+    per-call event pairs)."""
     for i in range(warm):
         call(pool[i % len(pool)])
     torch.cuda.synchronize()
+    g = graph_of_calls(call, pool, n, torch) if graph else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(n):
-        call(pool[i % len(pool)])
+    if g is not None:
+        g.replay()
+    else:
+        for i in range(n):
+            call(pool[i % len(pool)])
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / n
@@ -260,7 +289,7 @@ def other_workloads(ext, ref, dev, torch, names=("C1", "C3", "C4", "C5")):
         pool = make_pool(w, dev, torch, max_sets=(2 if name == "C5" else 256))
         pen = torch.zeros(w["B"], w["V"], device=dev) if w["rep"] else None
         st = setup_rand_rows(w["seed"], 0, w["B"])
-        ms, med = time_calls(sampler_call(ext, w, st, pen), pool, EXTRA_CALLS, torch)
+        ms, med = time_calls(sampler_call(ext, w, st, pen), pool, EXTRA_CALLS, torch, graph=True)
         row = {"median_us": med, "ms_per_call": ms, "rows_per_s": w["B"] / (ms * 1e-3), "calls": EXTRA_CALLS,
                "roofline_frac": alg_bytes(w) / (ms * 1e-3) / 1e9 / peak, "algorithmic_bytes": alg_bytes(w)}
         if ref is not None:
@@ -306,13 +335,20 @@ def multi_gpu_extras(ext, rank, world, dev, torch, dist, calls=100):
             torch.cuda.synchronize()
             dist.barrier()
             torch.cuda.synchronize()
+            g = graph_of_calls(call, pool, calls, torch)     # the timed region holds the launches, not the host's loop
+            dist.barrier()
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for i in range(calls):
-                call(pool[i % len(pool)])
+            if g is not None:
+                g.replay()
+            else:
+                for i in range(calls):
+                    call(pool[i % len(pool)])
             e1.record()
             torch.cuda.synchronize()
             ms = max_over_ranks(e0.elapsed_time(e1)) / calls
+            del g
             total_rows = w["B"] * world if mode == "weak" else w["B"]
             out["%s_%s" % (name, mode)] = {"rows_per_gpu": wl["B"], "total_rows": total_rows, "ms_per_call": ms,
                                            "rows_per_s": total_rows / (ms * 1e-3), "collectives_on_data_path": 0}
