@@ -347,10 +347,13 @@ def multi_gpu_extras(ext, rank, world, dev, torch, dist, calls=100):
                     call(pool[i % len(pool)])
             e1.record()
             torch.cuda.synchronize()
-            ms = max_over_ranks(e0.elapsed_time(e1)) / calls
+            mine = e0.elapsed_time(e1) / calls
+            ms = max_over_ranks(mine)
+            fastest = -max_over_ranks(-mine)
             del g
             total_rows = w["B"] * world if mode == "weak" else w["B"]
             out["%s_%s" % (name, mode)] = {"rows_per_gpu": wl["B"], "total_rows": total_rows, "ms_per_call": ms,
+                                           "ms_per_call_fastest_rank": fastest,
                                            "rows_per_s": total_rows / (ms * 1e-3), "collectives_on_data_path": 0}
             del pool, pen
             torch.cuda.empty_cache()
