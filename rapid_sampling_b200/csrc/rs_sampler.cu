@@ -269,16 +269,18 @@ __global__ void __launch_bounds__(kLanes / C, ctas_per_sm_by_registers(C, SMEM))
             *s_fail = 0;
         }
         __syncthreads();
-        if (wl == 0 && bulk_load) {
+        if (bulk_load) {
+            // One copy per stripe, issued by as many threads as there are stripes: a warp issues its lanes' copies one
+            // after the other (64 copies from one warp took 1.9 us), so they are spread over all warps of the CTA.
             const int kfull = V4 >> 10, rem = V4 & 1023;
             const int vl = min(max(rem - (int)crank * L, 0), L);
             const uint32_t bar = smem_addr(mbar);
-            if (lane == 0) mbar_expect_tx(bar, (uint32_t)(kfull * L + vl) * 16u);
-            __syncwarp();
+            if (t == 0) mbar_expect_tx(bar, (uint32_t)(kfull * L + vl) * 16u);
             const float4* src = reinterpret_cast<const float4*>(lrow) + crank * L;
             const uint32_t dst = smem_addr(row.slab);
-            for (int k = lane; k < kfull; k += 32) bulk_g2s(dst + k * L * 16, src + k * kLanes, L * 16, bar);
-            if (lane == 0 && vl > 0) bulk_g2s(dst + kfull * L * 16, src + kfull * kLanes, vl * 16, bar);
+            for (int k = lane * WPC + wl; k < kfull; k += L)      // consecutive stripes go to different warps
+                bulk_g2s(dst + k * L * 16, src + k * kLanes, L * 16, bar);
+            if (t == L - 1 && vl > 0) bulk_g2s(dst + kfull * L * 16, src + kfull * kLanes, vl * 16, bar);
         }
     } else {
         if (t == 0) {
