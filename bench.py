@@ -41,7 +41,7 @@ PROFILED_TRAFFIC = {"C1": (2.214e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md
                     "C2": (1.168e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md"),
                     "C3": (39.02e6, "profiles/sampler_kernel_C3_load_paths.md"),
                     "C4": (219.4e6, "profiles/rowcta_kernel_C4_C3.md"),
-                    "C5": (513.3e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md")}
+                    "C5": (526.6e6, "profiles/sampler_kernel_C1_C2_C5_cluster.md")}
 
 
 def workload(name):
