@@ -754,7 +754,41 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t[0])
         e2e = {"value": world * B * ke / dt, "unit": "rows/s", "h2d_bytes_per_step": B * V * esz, "d2h_bytes_per_step": 4 * B,
-               "steps": ke, "ms_per_step": dt / ke * 1e3}
+               "steps": ke, "ms_per_step": dt / ke * 1e3, "api": "torch: pinned tensor -> copy_ -> sampling call -> .cpu()"}
+        if a.impl == "ours" and a.dtype == "f32" and not a.per_row:
+            # the same step through the C ABI's host-buffer entry point: one call copies the pinned host logits in,
+            # samples, copies the ids back and synchronises the stream
+            import ctypes as C
+            from rapid_sampling_b200 import abi as rs_abi
+            L = rs_abi.load()
+            wsb = max(int(L.rs_workspace_bytes(B, V)), 256 + 4 * B * V)
+            ws = torch.zeros(wsb, dtype=torch.uint8, device=dev)
+            out_dev = torch.empty(B, dtype=torch.int32, device=dev)
+            out_host = torch.empty(B, dtype=torch.int32).pin_memory()
+            stream_h = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            pen_ptr = pen.data_ptr() if pen is not None else None
+
+            def host_step(i):
+                rc = L.rs_sample_host(host_pool[i % host_n].data_ptr(), B, 1, V, pen_ptr, states.data_ptr(), out_host.data_ptr(),
+                                      float(w["temperature"]), int(w["top_k"]), float(w["top_p"]), 0.1, 0.1, 0.95,
+                                      stage.data_ptr(), out_dev.data_ptr(), ws.data_ptr(), wsb, stream_h)
+                if rc != 0:
+                    raise RuntimeError("rs_sample_host: %s" % rs_abi.status_string(rc))
+            for i in range(3):
+                host_step(i)
+            sync_all()
+            t0 = time.perf_counter()
+            for i in range(ke):
+                host_step(i)
+            dt_c = time.perf_counter() - t0
+            if world > 1:
+                t = torch.tensor([dt_c], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                dt_c = float(t[0])
+            e2e = {"value": world * B * ke / dt_c, "unit": "rows/s", "h2d_bytes_per_step": B * V * 4, "d2h_bytes_per_step": 4 * B,
+                   "steps": ke, "ms_per_step": dt_c / ke * 1e3,
+                   "api": "rs_sample_host (C ABI): pinned host logits in, ids out on the host, stream synchronised, per call",
+                   "torch_api": {"value": world * B * ke / dt, "ms_per_step": dt / ke * 1e3}}
     clk = clocks.stop()
 
     # ---- beside the headline, outside its timed region --------------------------------------------------
