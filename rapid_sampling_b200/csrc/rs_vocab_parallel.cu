@@ -969,7 +969,7 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
             if (c->penalties) {
                 const long long tot = (long long)B * n;
                 const int* idsrc = (round == 1) ? (const int*)(ws + l.total + vpf_layout(B, c->world, vpf_subblocks(B, n)).ids)
-                                                : (const int*)(ws + l.ids);   // round 1: ids of the fast protocol
+                                                : (const int*)(ws + l.ids);   // argument `round` == 1 selects the ids of the fast protocol
                 vp_penalty_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(
                     c->penalties, (int)n, (int)B, idsrc, (long long)c->col0, (float)c->presence_penalty,
                     (float)c->repetition_penalty, (float)c->penalty_decay,
