@@ -648,9 +648,10 @@ __device__ __forceinline__ void f_block_sums30(float (&v)[30], float* sh /* [32]
     for (int i = 0; i < 30; i++) v[i] = sh[32 * 32 + i];
 }
 
+// gath / gath_cnt: the lists and counts of all ranks as ONE all-gather delivered them: rank r's block starts r * rstride
+// words on, its lists first ([B][S][seg][2]), its counts ([B][S]) behind them.
 __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, int world, int seg, const float* stat1, const float* stat2,
-                                                                const uint32_t* gath /* [world][B][S][seg][2] */,
-                                                                const uint32_t* gath_cnt /* [world][B][S] */, float top_k,
+                                                                const uint32_t* gath, const uint32_t* gath_cnt, size_t rstride, float top_k,
                                                                 float top_p, int use_p, const unsigned char* states,
                                                                 int* ids, int* valid) {
     __shared__ float sh[32 * 32 + 32];
@@ -668,7 +669,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
         uint32_t run = 0;
         int bad = 0;
         for (int i = 0; i < nseg; i++) {
-            const uint32_t c = gath_cnt[((size_t)(i / S) * B + b) * S + (i % S)];
+            const uint32_t c = gath_cnt[(size_t)(i / S) * rstride + (size_t)b * S + (i % S)];
             if (c > (uint32_t)seg) bad = 1;
             s_segoff[i] = run;
             run += min(c, (uint32_t)seg);
@@ -683,7 +684,7 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     const uint32_t q = (M + kVpThreads - 1) / kVpThreads;
     const uint32_t p0 = min((uint32_t)t * q, M), p1 = min(p0 + q, M);
     auto entry_in = [&](int i, uint32_t pos, float& pr, uint32_t& col) {     // pos lies in segment i
-        const uint32_t* e = gath + ((((size_t)(i / S) * B + b) * S + (i % S)) * seg + (pos - s_segoff[i])) * 2;
+        const uint32_t* e = gath + (size_t)(i / S) * rstride + ((((size_t)b * S) + (i % S)) * seg + (pos - s_segoff[i])) * 2;
         pr = __uint_as_float(e[0]) / denom;
         col = e[1];
     };
@@ -821,9 +822,10 @@ static VpfLayout vpf_layout(long long B, int world, int S) {
     l.stat1 = take((size_t)B * S);
     l.stat2 = take((size_t)B * S * kFStat2);
     l.send = take((size_t)B * lmax * 2);                 // S segments of lmax / S entries per row
-    l.send_cnt = take((size_t)B * S);                    // one count per segment
-    l.gath = take((size_t)world * B * lmax * 2);
-    l.gath_cnt = take((size_t)world * B * S);
+    l.send_cnt = take((size_t)B * S);                    // one count per segment, directly behind the lists:
+    const size_t block = o - l.send;                     // the two travel as one block in one all-gather
+    l.gath = take((size_t)world * block);                // rank r's block at gath + r * block
+    l.gath_cnt = l.gath + (l.send_cnt - l.send);         // rank 0's counts; rank r's are r * block further on
     l.ids = take(B);
     l.valid = take(B + 1);   // per-row flags, then one flag for the whole call
     l.total = o;
@@ -1019,7 +1021,7 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
                     attr_done[dev] = true;
                 }
                 vpf_finish_kernel<<<grid, kVpThreads, (size_t)lmax * c->world * sizeof(float), st>>>((int)B, S, c->world, lmax / S, fw + f.stat1, fw + f.stat2, uw + f.gath,
-                                                               uw + f.gath_cnt, fk, fp, use_p, (const unsigned char*)c->states,
+                                                               uw + f.gath_cnt, f.gath - f.send /* one rank's block */, fk, fp, use_p, (const unsigned char*)c->states,
                                                                (int*)(uw + f.ids), (int*)(uw + f.valid));
             } else
                 vpf_advance_kernel<<<(unsigned)((B + 127) / 128), 128, 0, st>>>((unsigned char*)c->states, (int)B,

@@ -96,8 +96,13 @@ class VocabParallelSampler:
         self.f_stat2 = self.ws[f[1]:f[1] + B * S * f[10]]
         self.f_send = self.ws[f[2]:f[2] + B * Lmax * 2]
         self.f_send_cnt = self.ws[f[3]:f[3] + B * S]          # one count per (row, sub-block) segment
-        self.f_gath = self.ws[f[4]:f[4] + world * B * Lmax * 2]
-        self.f_gath_cnt = self.ws[f[5]:f[5] + world * B * S]
+        # lists and counts lie back to back and travel as ONE block in one all-gather; rank r's block lands r blocks on
+        block = f[4] - f[2]
+        self.f_send_block = self.ws[f[2]:f[2] + block]
+        self.f_gath_block = self.ws[f[4]:f[4] + world * block]
+        per_rank = self.f_gath_block.view(world, block)
+        self.f_gath = per_rank[:, :B * Lmax * 2]              # (world, B * Lmax * 2) view
+        self.f_gath_cnt = per_rank[:, f[3] - f[2]:f[3] - f[2] + B * S]
         self.f_ids = self.ws[f[6]:f[6] + B].view(torch.int32)
         self.f_valid = self.ws[f[7]:f[7] + B].view(torch.int32)
         self.f_all_valid = self.ws[f[7] + B:f[7] + B + 1].view(torch.int32)   # cleared if any row could not be settled
@@ -151,8 +156,7 @@ class VocabParallelSampler:
         self._reduce(self.f_stat2, dist.ReduceOp.SUM)
         c.stage("f_extract")
         c.stage("f_compact")
-        self._gather(self.f_gath, self.f_send)
-        self._gather(self.f_gath_cnt, self.f_send_cnt)
+        self._gather(self.f_gath_block, self.f_send_block)
         c.stage("f_finish")
         c.stage("f_advance")
         if penalties is not None:

@@ -32,8 +32,7 @@ def emulated_sample(samplers, shards, states, temp, k, p, pens=None, fast=True):
         fstep("f_extract")
         fstep("f_compact")
         for s in samplers:          # the all-gather
-            s.f_gath.copy_(torch.cat([x.f_send for x in samplers]))
-            s.f_gath_cnt.copy_(torch.cat([x.f_send_cnt for x in samplers]))
+            s.f_gath_block.copy_(torch.cat([x.f_send_block for x in samplers]))
         fstep("f_finish")
         before = [st.clone() for st in states]
         fstep("f_advance")            # applied by the device only if every row was settled
@@ -310,8 +309,7 @@ def test_lm_head_tile_hook_matches_the_max_pass(abi):
         for s in hook_s:
             s.compute.stage("f_extract")
         for s in hook_s:
-            s.f_gath.copy_(torch.cat([x.f_send for x in hook_s]))
-            s.f_gath_cnt.copy_(torch.cat([x.f_send_cnt for x in hook_s]))
+            s.f_gath_block.copy_(torch.cat([x.f_send_block for x in hook_s]))
         for name, rnd in (("f_finish", 0), ("f_advance", 0), ("penalty", 1)):
             for s in hook_s:
                 s.compute.stage(name, rnd)
