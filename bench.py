@@ -394,7 +394,7 @@ def multi_gpu_extras(ext, rank, world, dev, torch, dist, calls=100):
     out["C5_vocab_parallel"] = {"columns_per_gpu": s.V_local, "ms_per_call": ms, "ms_per_call_host_check_every_call": ms_sync,
                                 "rows_per_s": B / (ms * 1e-3), "protocol": s.last_protocol, "last_call_repeated": redone,
                                 "ids_identical_on_all_ranks": bool(int(lo[0]) == int(hi[0])),
-                                "collectives_per_call": "2 all-reduces + 2 all-gathers (NCCL)"}
+                                "collectives_per_call": "2 all-reduces + 1 all-gather (NCCL)"}
     s.release_graphs()
     return out
 
