@@ -707,40 +707,64 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
             s_pr[pos] = pr;
         }
     }
+    // The rounds only look at the candidates that still lie in [left, right): those at or above `right` are in every
+    // later set (their count and mass are carried), those below `left` in none.  A thread owns at most 32 positions
+    // (M <= 32768), so a bit mask names its live ones; three quarters and more drop out per round.  Once nothing is left
+    // inside the bracket every further pivot sees the set of `right`, passes, and `left` stays: the loop ends there.
+    // (Lists of more than 32768 entries -- more than 16 ranks -- keep every position live and carry nothing.)
+    const bool masked = q <= 32u;
+    uint32_t live = 0u;
+    float left_cnt, base_cnt = 0.f, base_mass = 0.f;
     {
         float v[2] = {0.f, 0.f};
         for (uint32_t pos = p0; pos < p1; pos++) {
             const float pr = s_pr[pos];
-            if (__float_as_uint(pr) >= left) { v[0] += 1.f; v[1] += pr; }
+            if (__float_as_uint(pr) >= left) { v[0] += 1.f; v[1] += pr; if (masked) live |= 1u << (pos - p0); }
         }
         f_block_sums<2>(v, sh);
         const bool okl = (v[0] < top_k) && (v[1] < top_p);
         if (okl) ok_row = false;
+        left_cnt = v[0];
     }
-    for (int round = 0; round < RS_VP_ROUNDS && right - left > 1u; round++) {
+    for (int round = 0; round < RS_VP_ROUNDS && right - left > 1u && left_cnt > base_cnt; round++) {
         uint32_t piv[kVpPivots];
         vp_pivots(left, right, piv);
         float v[30];
 #pragma unroll
         for (int j = 0; j < 30; j++) v[j] = 0.f;
-        for (uint32_t pos = p0; pos < p1; pos++) {
-            const float pr = s_pr[pos];
+        auto tally = [&](const float pr) {
             const uint32_t pb = __float_as_uint(pr);
 #pragma unroll
             for (int j = 0; j < kVpPivots; j++)
                 if (pb >= piv[j]) { v[2 * j] += 1.f; v[2 * j + 1] += pr; }
+        };
+        if (masked) {
+            for (uint32_t m = live; m; m &= m - 1u) tally(s_pr[p0 + (uint32_t)(__ffs(m) - 1)]);
+        } else {
+            for (uint32_t pos = p0; pos < p1; pos++) tally(s_pr[pos]);
         }
         f_block_sums30(v, sh);
         uint32_t nl = left, nr = right;
+        float ncl = left_cnt, nbc = base_cnt, nbm = base_mass;
         bool found = false;
 #pragma unroll
         for (int j = 0; j < kVpPivots; j++) {
-            const bool okj = (v[2 * j] < top_k) && (v[2 * j + 1] < top_p);
-            if (!okj) nl = piv[j];
-            else if (!found) { nr = piv[j]; found = true; }
+            const float cj = base_cnt + v[2 * j], mj = base_mass + v[2 * j + 1];
+            const bool okj = (cj < top_k) && (mj < top_p);
+            if (!okj) { nl = piv[j]; ncl = cj; }
+            else if (!found) { nr = piv[j]; nbc = cj; nbm = mj; found = true; }
         }
-        left = nl;
-        right = nr;
+        left = nl; right = nr;
+        left_cnt = ncl;
+        if (!masked) continue;      // every position stays live: the sums are whole sums, nothing is carried
+        base_cnt = nbc; base_mass = nbm;
+        uint32_t keep = 0u;
+        for (uint32_t m = live; m; m &= m - 1u) {
+            const int i = __ffs(m) - 1;
+            const uint32_t pb = __float_as_uint(s_pr[p0 + (uint32_t)i]);
+            if (pb >= left && pb < right) keep |= 1u << i;
+        }
+        live = keep;
     }
     const float thr = __uint_as_float(left);
     float tl[3] = {0.f, 0.f, 0.f};
