@@ -665,11 +665,14 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     const float bound = f_bound_e(stat2, S, b, denom, top_k, top_p);
     bool ok_row = bound > 0.f;
     const int nseg = world * S;
+    // the segment counts are fetched by as many threads at once, then prefixed by one
+    if (t < nseg) s_segoff[t + 1] = gath_cnt[(size_t)(t / S) * rstride + (size_t)b * S + (t % S)];
+    __syncthreads();
     if (t == 0) {
         uint32_t run = 0;
         int bad = 0;
         for (int i = 0; i < nseg; i++) {
-            const uint32_t c = gath_cnt[(size_t)(i / S) * rstride + (size_t)b * S + (i % S)];
+            const uint32_t c = s_segoff[i + 1];
             if (c > (uint32_t)seg) bad = 1;
             s_segoff[i] = run;
             run += min(c, (uint32_t)seg);
@@ -699,12 +702,22 @@ __global__ void __launch_bounds__(kVpThreads) vpf_finish_kernel(int B, int S, in
     const uint32_t beta_p = __float_as_uint(bound / denom);
     uint32_t left = beta_p + 1u, right = 0x3f800001u;
     {
+        // one look-up and division per candidate (the rounds read shared memory); eight loads in flight at a time
         int i = 0;
-        for (uint32_t pos = p0; pos < p1; pos++) {      // one look-up and division per candidate; the rounds read shared memory
-            while (i + 1 < nseg && pos >= s_segoff[i + 1]) i++;
-            float pr; uint32_t col;
-            entry_in(i, pos, pr, col);
-            s_pr[pos] = pr;
+        for (uint32_t base = p0; base < p1; base += 8u) {
+            uint32_t raw[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const uint32_t pos = base + (uint32_t)u;
+                raw[u] = 0u;
+                if (pos < p1) {
+                    while (i + 1 < nseg && pos >= s_segoff[i + 1]) i++;
+                    raw[u] = gath[(size_t)(i / S) * rstride + ((((size_t)b * S) + (i % S)) * seg + (pos - s_segoff[i])) * 2];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (base + (uint32_t)u < p1) s_pr[base + (uint32_t)u] = __uint_as_float(raw[u]) / denom;
         }
     }
     // The rounds only look at the candidates that still lie in [left, right): those at or above `right` are in every
@@ -1004,6 +1017,8 @@ int rs_vp_stage(const rs_vp_call* c, int32_t stage, int32_t round) {
             break;
         case RS_VPF_MAX: case RS_VPF_SUM: case RS_VPF_EXTRACT: case RS_VPF_COMPACT: case RS_VPF_FINISH: case RS_VPF_ADVANCE: {
             const int S = vpf_subblocks(B, n);
+            // the finishing kernel's segment table and its live-position masks are sized for 64 segments of a row
+            if ((long long)c->world * S > kFMaxSub * 8) return RS_ERR_LIMIT;
             const VpfLayout f = vpf_layout(B, c->world, S);
             const int lmax = f_lmax(c->world);
             float* fw = ws + l.total;

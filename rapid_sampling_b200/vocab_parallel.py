@@ -92,6 +92,8 @@ class VocabParallelSampler:
         L.rs_vp_fast_layout(B, self.V_local, world, fo)
         f = [int(x) for x in fo]
         S, Lmax = f[8], f[9]
+        if world * S > 64:     # the fast protocol's finishing kernel holds 64 segments per row: larger groups run the staged one
+            self.fast = False
         self.f_stat1 = self.ws[f[0]:f[0] + B * S]
         self.f_stat2 = self.ws[f[1]:f[1] + B * S * f[10]]
         self.f_send = self.ws[f[2]:f[2] + B * Lmax * 2]
